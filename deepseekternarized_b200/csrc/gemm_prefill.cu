@@ -1,0 +1,576 @@
+// Prefill grouped ternary GEMM for sm_100a: tcgen05 MMA with TMEM accumulators, TMA-fed activations,
+// warp-specialised dequantisation of packed trits into fp16 shared-memory tiles.
+//
+// Problem (per expert e, rows ra..rb of the expert-sorted activations):
+//     out[m, n] = row_scale[m] * sum_k x[m, k] * W_e[n, k],   W_e[n, k] = sum_i scale_i[e, n, k/128] * trit_i[e, n, k]
+//
+// Mapping ("swap AB"): the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), up to 256
+// token rows are the MMA N dimension (TMEM columns), so tiles stay full when an expert has few rows.
+// Both operands are fp16, K-major, 128-byte swizzled, 64 K-elements per pipeline stage:
+//   A (weights)      written by 8 dequant warps: packed trits (tiled layout, see layout_kernels.cu) ->
+//                    scale * trit, exact in fp16 -> st.shared in the canonical SWIZZLE_128B layout
+//   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA), 32-row boxes
+//   D (accumulator)  fp32 in TMEM, two buffers of 256 columns so the epilogue of one tile overlaps the
+//                    MMAs of the next
+// bf16 activations are converted once to fp16 with a power-of-two factor per row (exact for every
+// element within 2^-22 of the row's absolute maximum); the factor comes back through row_scale.
+// tcgen05 kind::f16 refuses an fp16 A with a bf16 B (illegal instruction), hence the conversion.
+//
+// Warp roles (448 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer for B           warp 1      MMA issuer, owns the TMEM allocation
+//   warps 2-5   epilogue (TMEM -> registers -> global)    warps 6-13  dequant producers for A
+//
+// Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all
+// roles leave their loops, the CTA frees TMEM and the kernel records DST_ERR_TIMEOUT in the status word.
+#include <cuda.h>
+
+#include "dst_common.cuh"
+
+namespace dst {
+namespace {
+
+constexpr int PF_THREADS = 448;
+constexpr int PF_TN = 256;            // token rows per tile (TMEM columns per accumulator buffer)
+constexpr int PF_BOX = 32;            // token rows per TMA box
+constexpr int PF_A_BYTES = 128 * 128; // one A stage: 128 weight rows x 64 fp16
+constexpr int PF_B_BYTES = PF_TN * 128;
+constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_B_BYTES;
+constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
+constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
+
+__device__ int g_device_status = 0;
+
+struct PrefillParams {
+  const uint8_t* tiled[DST_MAX_TERMS];
+  const __half* scale[DST_MAX_TERMS];
+  int n_terms;
+  const float* row_scale;
+  const int64_t* offsets;
+  void* out;
+  int out_dtype, accumulate;
+  int E, T, N, K, G, NT, S, kstages;
+};
+
+// ------------------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > PF_WAIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  // K-major, SWIZZLE_128B: start address >> 4, LBO unused (1), SBO = 1024 B (8 rows x 128 B), version 1.
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+#define TMEM_LD_32(v, taddr)                                                                                              \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                  \
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"   \
+               "%28,%29,%30,%31}, [%32];"                                                                                 \
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),          \
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),    \
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),  \
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])   \
+               : "r"(taddr))
+#define TMEM_LD_16(v, taddr)                                                                                             \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"  \
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),         \
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])    \
+               : "r"(taddr))
+
+// ------------------------------------------------------------------------------------------ tile walk
+// Tiles are numbered expert-major, then token tile, then weight-row tile (fastest), so the CTAs that run
+// at the same time share an expert's activation rows and packed weights in L2. Every role walks the
+// same sequence with its own copy of this state.
+struct TileWalker {
+  const int64_t* offsets;
+  int E, T, NT;
+  int e = -1, mt_count = 0;
+  long long before = 0;
+  int64_t ra = 0, rb = 0;
+  __device__ bool seek(long long t, int& e_out, int& nt, int& row0, int& rows) {
+    while (e < 0 || t >= before + (long long)mt_count * NT) {
+      if (e >= 0) before += (long long)mt_count * NT;
+      if (++e >= E) return false;
+      row_range(offsets, e, T, ra, rb);
+      mt_count = (int)((rb - ra + PF_TN - 1) / PF_TN);
+    }
+    const long long local = t - before;
+    const int mt = (int)(local / NT);
+    nt = (int)(local - (long long)mt * NT);
+    row0 = (int)ra + mt * PF_TN;
+    rows = (int)(rb - row0 < PF_TN ? rb - row0 : PF_TN);
+    e_out = e;
+    return true;
+  }
+};
+
+// ------------------------------------------------------------------------------------------ dequant
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// TQ2, tiled word format: trit 2j in bits [2j, 2j+1], trit 2j+1 in bits [16+2j, 17+2j] (digit u = t + 1).
+// (w & (0x00030003 << 2j')) | 0x64006400 is the fp16 pair 1024 + u * 4^j'; one fused multiply-add maps it
+// to u - 1 exactly; one multiply applies the group scale exactly.
+template <bool FIRST>
+__device__ __forceinline__ void tq2_word(uint32_t w, __half2 s2, __half2* acc /* 8 */) {
+  const uint32_t magic = 0x64006400u;
+  const uint32_t w2 = w >> 10;
+  const __half2 m0 = __floats2half2_rn(1.f, 1.f), m1 = __floats2half2_rn(0.25f, 0.25f), m2 = __floats2half2_rn(0.0625f, 0.0625f),
+                m3 = __floats2half2_rn(0.015625f, 0.015625f), m4 = __floats2half2_rn(0.00390625f, 0.00390625f);
+  const __half2 a0 = __floats2half2_rn(-1025.f, -1025.f), a1 = __floats2half2_rn(-257.f, -257.f), a2 = __floats2half2_rn(-65.f, -65.f),
+                a3 = __floats2half2_rn(-17.f, -17.f), a4 = __floats2half2_rn(-5.f, -5.f);
+  __half2 t[8];
+  t[0] = __hfma2(bits_h2((w & 0x00030003u) | magic), m0, a0);
+  t[1] = __hfma2(bits_h2((w & 0x000C000Cu) | magic), m1, a1);
+  t[2] = __hfma2(bits_h2((w & 0x00300030u) | magic), m2, a2);
+  t[3] = __hfma2(bits_h2((w & 0x00C000C0u) | magic), m3, a3);
+  t[4] = __hfma2(bits_h2((w & 0x03000300u) | magic), m4, a4);
+  t[5] = __hfma2(bits_h2((w2 & 0x00030003u) | magic), m0, a0);
+  t[6] = __hfma2(bits_h2((w2 & 0x000C000Cu) | magic), m1, a1);
+  t[7] = __hfma2(bits_h2((w2 & 0x00300030u) | magic), m2, a2);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = FIRST ? __hmul2(t[j], s2) : __hfma2(t[j], s2, acc[j]);
+}
+
+// TQ1: the thread needs the 32 trits [tau, tau + 32) of its row-superblock, tau = 32 q. They start at
+// trit `o` of byte b0 = tau / 5. Bytes go through a shared-memory table of unscaled fp16 trits in two
+// alignments (first trit in the low or the high half of a pair), so pairs never need re-alignment:
+// entry even = (v0,v1)(v2,v3)(v4,0), entry odd = (0,v0)(v1,v2)(v3,v4). Byte i lands at pair index
+// floor((5 i - o) / 2); neighbouring bytes share one pair, merged with OR.
+template <int O, bool FIRST>
+__device__ __forceinline__ void tq1_decode(uint32_t lo, uint32_t hi, uint32_t lut_addr, __half2 s2, __half2* acc /* 16 */) {
+  uint32_t out[16];
+#pragma unroll
+  for (int h = 0; h < 16; ++h) out[h] = 0u;
+  constexpr int NB = (O + 32 + 4) / 5;  // bytes touched: 7, or 8 when O == 4
+#pragma unroll
+  for (int i = 0; i < NB; ++i) {
+    const uint32_t src = i < 4 ? lo : hi;
+    const int sh = 8 * (i & 3) - 7;
+    const uint32_t idx = (sh >= 0 ? (src >> (sh >= 0 ? sh : 0)) : (src << 7)) & 0x7F80u;
+    const int p = 5 * i - O;                       // position of the byte's first trit
+    const int odd = ((p % 2) + 2) % 2;             // first trit lands in the high half
+    const int h0 = (p - odd) / 2;                  // floor(p / 2), exact for negative p too
+    uint32_t t0, t1, t2, t3;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t0), "=r"(t1), "=r"(t2), "=r"(t3) : "r"(lut_addr + idx + odd * 32768u));
+    (void)t3;
+    if (h0 >= 0 && h0 < 16) out[h0] |= t0;
+    if (h0 + 1 >= 0 && h0 + 1 < 16) out[h0 + 1] |= t1;
+    if (h0 + 2 >= 0 && h0 + 2 < 16) out[h0 + 2] |= t2;
+  }
+#pragma unroll
+  for (int h = 0; h < 16; ++h) acc[h] = FIRST ? __hmul2(bits_h2(out[h]), s2) : __hfma2(bits_h2(out[h]), s2, acc[h]);
+}
+
+template <bool FIRST>
+__device__ __forceinline__ void tq1_dispatch(int o, uint32_t lo, uint32_t hi, uint32_t lut_addr, __half2 s2, __half2* acc) {
+  switch (o) {
+    case 0: tq1_decode<0, FIRST>(lo, hi, lut_addr, s2, acc); break;
+    case 1: tq1_decode<1, FIRST>(lo, hi, lut_addr, s2, acc); break;
+    case 2: tq1_decode<2, FIRST>(lo, hi, lut_addr, s2, acc); break;
+    case 3: tq1_decode<3, FIRST>(lo, hi, lut_addr, s2, acc); break;
+    default: tq1_decode<4, FIRST>(lo, hi, lut_addr, s2, acc); break;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
+template <int FMT, int NSTAGE>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* lut = smem + NSTAGE * PF_STAGE_BYTES;  // TQ1 only
+  __shared__ uint64_t bar_full[NSTAGE], bar_empty[NSTAGE], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    abort_s = 0;
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1 + 8);  // TMA producer's expect_tx arrive + one arrive per dequant warp
+      mbar_init(smem_u32(&bar_empty[s]), 1);     // tcgen05.commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_tfull[a]), 1);   // tcgen05.commit after the tile's last MMA
+      mbar_init(smem_u32(&bar_tempty[a]), 4);  // one arrive per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (FMT == 1) {
+    // table of unscaled fp16 trits: [alignment][byte value][replica] x 16 B
+    for (int i = tid; i < 2 * 256 * 8; i += PF_THREADS) {
+      const int odd = i >> 11, v = (i >> 3) & 255;
+      const uint32_t f = tq1_fields((uint32_t)v);
+      uint32_t h[6];
+#pragma unroll
+      for (int d = 0; d < 5; ++d) {
+        const int t = (int)((f >> (2 * d)) & 3u) - 1;
+        h[d + 1] = t > 0 ? 0x3C00u : (t < 0 ? 0xBC00u : 0u);
+      }
+      h[0] = 0u;
+      uint4 ent;
+      if (odd) ent = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), 0u);
+      else ent = make_uint4(h[1] | (h[2] << 16), h[3] | (h[4] << 16), h[5], 0u);
+      *reinterpret_cast<uint4*>(lut + (size_t)i * 16) = ent;
+    }
+  }
+  __syncwarp();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+
+  TileWalker walk;
+  walk.offsets = p.offsets;
+  walk.E = p.E;
+  walk.T = p.T;
+  walk.NT = p.NT;
+  int e, nt, row0, rows;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (activations)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+        const int boxes = (rows + PF_BOX - 1) / PF_BOX;
+        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_arrive_expect_tx(full, (uint32_t)boxes * PF_BOX * 128u);
+          const uint32_t dst = smem_u32(smem + s * PF_STAGE_BYTES + PF_A_BYTES);
+          for (int b = 0; b < boxes; ++b) tma_load_2d(dst + b * PF_BOX * 128, &xmap, ks * 64, row0 + b * PF_BOX, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x, ++tile) {
+        const uint32_t a = tile & 1u;
+        if (!mbar_wait(smem_u32(&bar_tempty[a]), ((tile >> 1) & 1u) ^ 1u, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t n_eff = (uint32_t)((rows + 15) & ~15);
+        // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+        const uint32_t idesc = (1u << 4) | ((n_eff >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t d_tmem = tmem + a * PF_TN;
+        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait(smem_u32(&bar_full[s]), (it / NSTAGE) & 1u, abort_flag)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + s * PF_STAGE_BYTES), sb = sa + PF_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs have read it
+        }
+        if (ok) umma_commit(smem_u32(&bar_tfull[a]));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t tile = 0;
+    for (long long t = blockIdx.x; walk.seek(t, e, nt, row0, rows); t += gridDim.x, ++tile) {
+      const uint32_t a = tile & 1u;
+      if (!mbar_wait(smem_u32(&bar_tfull[a]), (tile >> 1) & 1u, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int n = nt * 128 + q * 32 + lane;
+      const bool n_ok = n < p.N;
+      const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + a * PF_TN;
+      const int n_eff = (rows + 15) & ~15;
+      for (int c0 = 0; c0 < n_eff; c0 += 32) {
+        uint32_t v[32];
+        if (c0 + 32 <= n_eff) {
+          TMEM_LD_32(v, taddr0 + c0);
+        } else {
+          TMEM_LD_16(v, taddr0 + c0);
+#pragma unroll
+          for (int j = 16; j < 32; ++j) v[j] = 0u;
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int m = c0 + j;
+          if (m < rows && n_ok) {
+            float val = __uint_as_float(v[j]);
+            if (p.row_scale) val *= p.row_scale[row0 + m];
+            const int64_t o = (int64_t)(row0 + m) * p.N + n;
+            if (p.out_dtype == DST_OUT_BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(val);
+            else if (p.out_dtype == DST_OUT_F16) static_cast<__half*>(p.out)[o] = __float2half_rn(val);
+            else static_cast<float*>(p.out)[o] = p.accumulate ? static_cast<float*>(p.out)[o] + val : val;
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[a]));
+    }
+  } else {
+    // ------------------------------------------------------------------ dequant producers (weights)
+    const int td = tid - 192;
+    const int r = td & 127, hh = td >> 7;
+    const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+      const int n = nt * 128 + r;
+      const bool n_ok = n < p.N;
+      const int64_t srow = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.G;
+      const int64_t tile_base = (((int64_t)e * p.NT + nt) * p.S) * 8192 + (int64_t)r * 64;
+      for (int ks = 0; ks < p.kstages; ++ks, ++it) {
+        const int s = it % NSTAGE;
+        __half2 acc[16];
+        const int g = ks >> 1;  // 64-trit stage -> 128-trit scale group
+        if (FMT == 2) {
+          const int64_t off = tile_base + (int64_t)(ks >> 2) * 8192 + (ks & 3) * 16 + hh * 8;
+#pragma unroll
+          for (int i = 0; i < DST_MAX_TERMS; ++i) {
+            if (i < p.n_terms) {
+              const uint2 w = *reinterpret_cast<const uint2*>(p.tiled[i] + off);
+              const __half sc = n_ok ? p.scale[i][srow + g] : __float2half(0.f);
+              const __half2 s2 = __half2half2(sc);
+              if (i == 0) {
+                tq2_word<true>(w.x, s2, acc);
+                tq2_word<true>(w.y, s2, acc + 8);
+              } else {
+                tq2_word<false>(w.x, s2, acc);
+                tq2_word<false>(w.y, s2, acc + 8);
+              }
+            }
+          }
+        } else {
+          const int sb = ks / 5, qq = (ks - sb * 5) * 2 + hh;  // 32-trit slot 0..9 inside the 320-trit superblock
+          const int tau = qq * 32, b0 = tau / 5, o = tau - b0 * 5;
+          const int wi = b0 >> 2, sh = (b0 & 3) * 8;
+          const int64_t off = tile_base + (int64_t)sb * 8192;
+#pragma unroll
+          for (int i = 0; i < DST_MAX_TERMS; ++i) {
+            if (i < p.n_terms) {
+              const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.tiled[i] + off);
+              const uint32_t w0 = wp[wi], w1 = wi + 1 < 16 ? wp[wi + 1] : 0u, w2 = wi + 2 < 16 ? wp[wi + 2] : 0u;
+              const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
+              const __half sc = n_ok ? p.scale[i][srow + g] : __float2half(0.f);
+              const __half2 s2 = __half2half2(sc);
+              if (i == 0) tq1_dispatch<true>(o, lo, hi, lut_addr, s2, acc);
+              else tq1_dispatch<false>(o, lo, hi, lut_addr, s2, acc);
+            }
+          }
+        }
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        uint8_t* arow = smem + s * PF_STAGE_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int chunk = hh * 4 + c;
+          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(h2_bits(acc[4 * c]), h2_bits(acc[4 * c + 1]), h2_bits(acc[4 * c + 2]), h2_bits(acc[4 * c + 3]));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // give copies and MMAs still in flight time to land before shared memory and TMEM are released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+  if (tid == 0 && abort_s) atomicExch(&g_device_status, DST_ERR_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------ activation conversion
+// bf16 (or fp16) rows -> fp16 rows scaled by 2^-e with e = floor(log2(absmax)) - 7, so every row's
+// largest magnitude lies in [128, 256); row_scale_out[m] = 2^e * row_scale_in[m].
+template <typename XT>
+__global__ void convert_rows_kernel(const XT* __restrict__ x, int64_t K, const float* __restrict__ rs_in, __half* __restrict__ y,
+                                    float* __restrict__ rs_out) {
+  __shared__ float red[32];
+  const int64_t m = blockIdx.x;
+  const XT* row = x + m * K;
+  float amax = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf((float)row[k]));
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  amax = red[0];
+  int ex = 0;
+  if (amax > 0.f && isfinite(amax)) {
+    (void)frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
+    ex -= 8;                  // amax * 2^-ex in [128, 256)
+  }
+  const float down = ldexpf(1.f, -ex);
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) y[m * K + k] = __float2half_rn((float)row[k] * down);
+  if (threadIdx.x == 0) rs_out[m] = ldexpf(1.f, ex) * (rs_in ? rs_in[m] : 1.f);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+template <int FMT, int NSTAGE>
+int launch_fmt(const CUtensorMap& map, const PrefillParams& p, long long tiles_upper, cudaStream_t st) {
+  const size_t smem = 1024 + (size_t)NSTAGE * PF_STAGE_BYTES + (FMT == 1 ? PF_LUT_BYTES : 0);
+  DST_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<FMT, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int dev = 0, sms = 148;
+  DST_CUDA_TRY(cudaGetDevice(&dev));
+  DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int grid = (int)(tiles_upper < sms ? (tiles_upper < 1 ? 1 : tiles_upper) : sms);
+  prefill_kernel<FMT, NSTAGE><<<grid, PF_THREADS, smem, st>>>(map, p);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+}  // namespace
+
+size_t prefill_workspace_bytes(int act_dtype, int64_t T, int64_t K) {
+  (void)act_dtype;  // fp16 activations are re-scaled per row as well, so every input type is converted
+  return (size_t)T * (size_t)K * 2 + (((size_t)T * 4 + 255) & ~(size_t)255) + 256;
+}
+
+bool prefill_supports(const GemmArgs& a) {
+  return a.weight_layout == DST_LAYOUT_TILED && a.group == 128 && a.K % 128 == 0 && a.scale_dtype == DST_SCALE_F16 &&
+         (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) && a.workspace != nullptr &&
+         a.workspace_bytes >= prefill_workspace_bytes(a.act_dtype, a.T, a.K) && a.T < (int64_t(1) << 30) &&
+         a.N <= (int64_t(1) << 22) && encode_fn() != nullptr;
+}
+
+int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
+  if (a.T == 0 || a.N == 0 || a.E == 0) return DST_OK;
+  if (!prefill_supports(a)) return DST_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return DST_ERR_ALIGNMENT;
+  for (int i = 0; i < a.terms.n; ++i)
+    if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 1) != 0)
+      return DST_ERR_ALIGNMENT;
+
+  // 1. activations -> fp16 rows + per-row power-of-two factor, in the workspace
+  __half* xh = static_cast<__half*>(a.workspace);
+  float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + (((size_t)a.T * a.K * 2 + 255) & ~(size_t)255));
+  if (a.act_dtype == DST_ACT_BF16)
+    convert_rows_kernel<__nv_bfloat16><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.x), a.K, a.row_scale, xh, rs);
+  else
+    convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale, xh, rs);
+  DST_CUDA_TRY(cudaGetLastError());
+
+  // 2. tensor map over the fp16 rows: [T, K], box 64 x 32, 128-byte swizzle, zero fill outside
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.T};
+  const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
+  const cuuint32_t box[2] = {64, PF_BOX};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+
+  PrefillParams p;
+  for (int i = 0; i < DST_MAX_TERMS; ++i) {
+    p.tiled[i] = i < a.terms.n ? a.terms.packed[i] : nullptr;
+    p.scale[i] = i < a.terms.n ? static_cast<const __half*>(a.terms.scale[i]) : nullptr;
+  }
+  p.n_terms = a.terms.n;
+  p.row_scale = rs;
+  p.offsets = a.offsets;
+  p.out = a.out;
+  p.out_dtype = a.out_dtype;
+  p.accumulate = a.accumulate;
+  p.E = (int)a.E;
+  p.T = (int)a.T;
+  p.N = (int)a.N;
+  p.K = (int)a.K;
+  p.G = (int)a.G;
+  p.NT = (int)cdiv64(a.N, 128);
+  p.S = (int)tiled_superblocks(a.fmt, a.K);
+  p.kstages = (int)(a.K / 64);
+  const long long tiles_upper = ((long long)cdiv64(a.T, PF_TN) + a.E) * p.NT;
+  return a.fmt == DST_FMT_TQ2 ? launch_fmt<2, 4>(map, p, tiles_upper, stream) : launch_fmt<1, 3>(map, p, tiles_upper, stream);
+}
+
+}  // namespace dst
+
+extern "C" int dst_check_device_status(dst_stream_t stream) {
+  DST_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int st = 0;
+  DST_CUDA_TRY(cudaMemcpyFromSymbol(&st, dst::g_device_status, sizeof(int)));
+  if (st != 0) {
+    const int zero = 0;
+    DST_CUDA_TRY(cudaMemcpyToSymbol(dst::g_device_status, &zero, sizeof(int)));
+    return DST_ERR_TIMEOUT;
+  }
+  return DST_OK;
+}

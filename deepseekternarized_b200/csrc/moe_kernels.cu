@@ -1,0 +1,348 @@
+// The small kernels around the expert GEMMs of a MoE layer: router (softmax + top-k), stable routing
+// sort, row gather, SwiGLU and the per-token combine. Semantics follow the reference's V4 MoE layer
+// (boilerplate/engine/model.py:376-422) and routing sort (boilerplate/kernels/ternary_cuda.py:114-118).
+#include "dst_common.cuh"
+
+namespace dst {
+namespace {
+
+// ------------------------------------------------------------------------------------------ router
+// One warp per token. Scores are the fp32 softmax of the E logits; the k largest are picked by k
+// rounds of warp arg-max (equal scores: lower expert id wins), then renormalised.
+constexpr int ROUTE_MAX_PER_LANE = 32;  // E <= 1024
+
+__global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E, int top_k, float route_scale,
+                             float* __restrict__ weights, int32_t* __restrict__ ids) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float* row = logits + t * E;
+  float v[ROUTE_MAX_PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+    const int e = j * 32 + lane;
+    v[j] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+    const int e = j * 32 + lane;
+    v[j] = e < E ? expf(v[j] - mx) : -1.f;  // -1 marks "not a candidate"
+    if (e < E) sum += v[j];
+  }
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  const float inv = 1.f / sum;
+  float wsel[8];
+  int isel[8];
+  float wsum = 0.f;
+  for (int r = 0; r < top_k; ++r) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+      const int e = j * 32 + lane;
+      if (v[j] > best) {  // ascending e within a lane: first maximum is the lowest id
+        best = v[j];
+        bi = e;
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+      if (j * 32 + lane == bi) v[j] = -1.f;
+    wsel[r] = best * inv;  // the softmax score
+    isel[r] = bi;
+    wsum += wsel[r];
+  }
+  if (lane == 0) {
+    const float d = top_k > 1 ? 1.f / (wsum + 1e-20f) : 1.f;
+    for (int r = 0; r < top_k; ++r) {
+      weights[t * top_k + r] = (top_k > 1 ? wsel[r] * d : wsel[r]) * route_scale;
+      ids[t * top_k + r] = isel[r];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ routing sort
+// Stable counting sort in three steps over chunks of SORT_CHUNK consecutive ids, one warp per chunk:
+//   1. per-chunk histogram               hist[c][e]
+//   2. one block: offsets[e] and the start of every (chunk, expert) run, in place in hist
+//   3. per chunk, in input order: warp match on the expert id gives each entry its rank among equal
+//      ids of the same 32-entry step; a per-expert cursor in shared memory carries across steps.
+constexpr int SORT_CHUNK = 1024;
+
+template <typename IdT>
+__global__ void sort_hist_kernel(const IdT* __restrict__ ids, int64_t n, int E, int32_t* __restrict__ hist,
+                                 int32_t* __restrict__ bad_count) {
+  extern __shared__ int32_t sh[];
+  for (int e = threadIdx.x; e < E; e += 32) sh[e] = 0;
+  __syncwarp();
+  const int64_t c = blockIdx.x, i0 = c * SORT_CHUNK;
+  int bad = 0;
+  for (int s = 0; s < SORT_CHUNK; s += 32) {
+    const int64_t i = i0 + s + threadIdx.x;
+    if (i < n) {
+      const int64_t e = (int64_t)ids[i];
+      if (e >= 0 && e < E) atomicAdd(&sh[e], 1);
+      else ++bad;
+    }
+  }
+  __syncwarp();
+  for (int e = threadIdx.x; e < E; e += 32) hist[c * E + e] = sh[e];
+  if (bad && bad_count) atomicAdd(bad_count, bad);
+}
+
+__global__ void sort_scan_kernel(int32_t* __restrict__ hist, int64_t chunks, int E, int64_t* __restrict__ offsets) {
+  // thread e: total of expert e; then an exclusive scan over experts; then run starts per chunk.
+  extern __shared__ int64_t tot[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int64_t s = 0;
+    for (int64_t c = 0; c < chunks; ++c) s += hist[c * E + e];
+    tot[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int64_t run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int64_t v = tot[e];
+      tot[e] = run;
+      offsets[e] = run;
+      run += v;
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int64_t run = tot[e];
+    for (int64_t c = 0; c < chunks; ++c) {
+      const int32_t v = hist[c * E + e];
+      hist[c * E + e] = (int32_t)run;  // total rows < 2^31
+      run += v;
+    }
+  }
+}
+
+template <typename IdT>
+__global__ void sort_place_kernel(const IdT* __restrict__ ids, int64_t n, int E, const int32_t* __restrict__ hist,
+                                  int64_t* __restrict__ order) {
+  extern __shared__ int32_t cur[];
+  const int lane = threadIdx.x;
+  const int64_t c = blockIdx.x, i0 = c * SORT_CHUNK;
+  for (int e = lane; e < E; e += 32) cur[e] = hist[c * E + e];
+  __syncwarp();
+  for (int s = 0; s < SORT_CHUNK; s += 32) {
+    const int64_t i = i0 + s + lane;
+    int64_t e = i < n ? (int64_t)ids[i] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned active = __ballot_sync(0xffffffffu, ok);
+    if (ok) {
+      const unsigned peers = __match_any_sync(active, (int)e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int leader = __ffs(peers) - 1;
+      int base = 0;
+      if (lane == leader) {
+        base = cur[e];
+        cur[e] = base + __popc(peers);
+      }
+      base = __shfl_sync(peers, base, leader);
+      order[base + rank] = i;
+    }
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------------ gather
+// dst[p, :] = src[order[p] / top_k, :], 16-byte vectors where the row length allows.
+__global__ void gather_rows_kernel(const uint16_t* __restrict__ src, const int64_t* __restrict__ order, int64_t n_rows,
+                                   int64_t K, int top_k, uint16_t* __restrict__ dst) {
+  const int64_t p = blockIdx.x;
+  if (p >= n_rows) return;
+  const int64_t t = order[p] / top_k;
+  const uint16_t* s = src + t * K;
+  uint16_t* d = dst + p * K;
+  if ((K & 7) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(s);
+    uint4* d4 = reinterpret_cast<uint4*>(d);
+    for (int64_t i = threadIdx.x; i < K / 8; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < K; i += blockDim.x) d[i] = s[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ swiglu
+// gu[p, 0:I] = gate (bf16), gu[p, I:2I] = up (bf16); h = bf16(w * silu(gate) * up), fp32 in between.
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route_weights,
+                              const int64_t* __restrict__ order, int64_t n_rows, int64_t inter, float limit,
+                              __nv_bfloat16* __restrict__ h) {
+  const int64_t p = blockIdx.x;
+  if (p >= n_rows) return;
+  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const __nv_bfloat16* g = gu + p * 2 * inter;
+  const __nv_bfloat16* u = g + inter;
+  for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) {
+    float gate = __bfloat162float(g[i]), up = __bfloat162float(u[i]);
+    if (limit > 0.f) {
+      up = fminf(fmaxf(up, -limit), limit);
+      gate = fminf(gate, limit);
+    }
+    const float sg = gate / (1.f + expf(-gate));
+    float v = sg * up;
+    if (route_weights) v = w * v;
+    h[p * inter + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// ----------------------------------------------------------------------------------------- combine
+__global__ void invert_order_kernel(const int64_t* __restrict__ order, int64_t n, int64_t* __restrict__ inv) {
+  const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (p < n) {
+    const int64_t f = order[p];
+    if (f >= 0 && f < n) inv[f] = p;
+  }
+}
+
+// One block per token: its top_k rows of `down`, visited in increasing expert id, summed in fp32.
+__global__ void combine_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv,
+                               const int32_t* __restrict__ ids, int top_k, int64_t hidden,
+                               __nv_bfloat16* __restrict__ y) {
+  const int64_t t = blockIdx.x;
+  int64_t pos[8];
+  int eid[8];
+  for (int s = 0; s < top_k; ++s) {
+    pos[s] = inv[t * top_k + s];
+    eid[s] = ids[t * top_k + s];
+  }
+  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
+    const int e = eid[i];
+    const int64_t p = pos[i];
+    int j = i - 1;
+    while (j >= 0 && eid[j] > e) {
+      eid[j + 1] = eid[j];
+      pos[j + 1] = pos[j];
+      --j;
+    }
+    eid[j + 1] = e;
+    pos[j + 1] = p;
+  }
+  for (int64_t c = threadIdx.x * 2; c < hidden; c += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    if (c + 1 < hidden && (hidden & 1) == 0) {
+      for (int s = 0; s < top_k; ++s) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(down + pos[s] * hidden + c);
+        a0 += __bfloat162float(v.x);
+        a1 += __bfloat162float(v.y);
+      }
+      *reinterpret_cast<__nv_bfloat162*>(y + t * hidden + c) = __floats2bfloat162_rn(a0, a1);
+    } else {
+      for (int cc = 0; cc < 2 && c + cc < hidden; ++cc) {
+        float acc = 0.f;
+        for (int s = 0; s < top_k; ++s) acc += __bfloat162float(down[pos[s] * hidden + c + cc]);
+        y[t * hidden + c + cc] = __float2bfloat16_rn(acc);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace dst
+
+using namespace dst;
+
+extern "C" int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
+                                      float* weights, int32_t* ids, dst_stream_t stream) {
+  if (T < 0 || E <= 0 || top_k <= 0) return DST_ERR_BAD_ARG;
+  if (E > 32 * ROUTE_MAX_PER_LANE || top_k > 8 || top_k > E) return DST_ERR_UNSUPPORTED;
+  if (T == 0) return DST_OK;
+  if (!logits || !weights || !ids) return DST_ERR_BAD_ARG;
+  const int warps = 4;
+  route_kernel<<<(unsigned)cdiv64(T, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, T, (int)E, top_k, route_scale, weights, ids);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" size_t dst_sort_workspace_bytes(int64_t n, int64_t E) {
+  if (n < 0 || E <= 0) return 0;
+  const int64_t chunks = cdiv64(n > 0 ? n : 1, SORT_CHUNK);
+  return (size_t)(chunks * E) * sizeof(int32_t);
+}
+
+extern "C" int dst_sort_by_expert(const void* ids, int ids_are_i32, int64_t n, int64_t E, int64_t* order,
+                                  int64_t* offsets, int32_t* bad_count, void* workspace, dst_stream_t stream) {
+  if (n < 0 || E <= 0 || !offsets) return DST_ERR_BAD_ARG;
+  if (E > 4096 || n > 0x7fffffff) return DST_ERR_BAD_SHAPE;  // per-expert tables live in shared memory
+  auto st = static_cast<cudaStream_t>(stream);
+  if (bad_count) DST_CUDA_TRY(cudaMemsetAsync(bad_count, 0, sizeof(int32_t), st));
+  if (n == 0) {
+    DST_CUDA_TRY(cudaMemsetAsync(offsets, 0, (size_t)(E + 1) * sizeof(int64_t), st));
+    return DST_OK;
+  }
+  if (!ids || !order || !workspace) return DST_ERR_BAD_ARG;
+  const int64_t chunks = cdiv64(n, SORT_CHUNK);
+  int32_t* hist = static_cast<int32_t*>(workspace);
+  const size_t sh32 = (size_t)E * sizeof(int32_t);
+  if (ids_are_i32)
+    sort_hist_kernel<int32_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int32_t*>(ids), n, (int)E, hist, bad_count);
+  else
+    sort_hist_kernel<int64_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int64_t*>(ids), n, (int)E, hist, bad_count);
+  DST_CUDA_TRY(cudaGetLastError());
+  sort_scan_kernel<<<1, 512, (size_t)E * sizeof(int64_t), st>>>(hist, chunks, (int)E, offsets);
+  DST_CUDA_TRY(cudaGetLastError());
+  if (ids_are_i32)
+    sort_place_kernel<int32_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int32_t*>(ids), n, (int)E, hist, order);
+  else
+    sort_place_kernel<int64_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int64_t*>(ids), n, (int)E, hist, order);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_gather_rows(const void* src, const int64_t* order, int64_t n_rows, int64_t K, int top_k,
+                               void* dst_, dst_stream_t stream) {
+  if (n_rows < 0 || K <= 0 || top_k <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!src || !order || !dst_) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  gather_rows_kernel<<<(unsigned)n_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(src), order, n_rows, K, top_k, static_cast<uint16_t*>(dst_));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_swiglu(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
+                          int64_t inter, float limit, void* h_bf16, dst_stream_t stream) {
+  if (n_rows < 0 || inter <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!gu_bf16 || !h_bf16) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  swiglu_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu_bf16), route_weights, order, n_rows, inter, limit,
+      static_cast<__nv_bfloat16*>(h_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
+                           int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream) {
+  if (T < 0 || top_k <= 0 || top_k > 8 || hidden <= 0) return DST_ERR_BAD_ARG;
+  if (T == 0) return DST_OK;
+  if (!down_bf16 || !order || !ids || !inv || !y_bf16) return DST_ERR_BAD_ARG;
+  if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t n = T * top_k;
+  invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
+  DST_CUDA_TRY(cudaGetLastError());
+  combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
+                                             static_cast<__nv_bfloat16*>(y_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}

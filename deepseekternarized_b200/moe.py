@@ -1,0 +1,229 @@
+"""The MoE routed-expert layer on B200: single GPU and expert-parallel over NCCL.
+
+Semantics are the reference's V4 MoE layer (``boilerplate/engine/model.py:376-422``) with
+softmax scores, renormalised top-k, ``route_scale`` and optional SwiGLU clamp, no shared expert:
+
+    weights, ids = route(x)                                   # model.py:389-405
+    for experts in increasing id over their tokens:           # model.py:415-420
+        h = bf16(weight * silu(w1(x)) * w3(x))                # w1/w3 outputs rounded to bf16, model.py:376-386
+        y[token] += w2(h)                                     # bf16 output, fp32 accumulation
+    y = bf16(y)
+
+where the reference loops over experts in Python (three ``TernaryLinear`` calls each), this layer
+sorts the (token, slot) pairs by expert once and runs two grouped ternary GEMMs over all experts
+(gate and up stacked into one [2I, hidden] weight per expert).
+
+Expert parallelism (``ExpertParallelMoE``): expert ``e`` lives on rank ``e // (E / world)`` (the
+partition of the vendored official model, ``third_party/deepseek_v41_inference/model.py:869-872``),
+every rank routes its own tokens, rows travel to the owning rank with one all-to-all each way
+(row counts are exchanged first), and each token's k results are summed in increasing expert id,
+so the output equals the single-GPU layer's.
+
+The compute steps go through an ``ops`` object. ``B200Ops`` is the only implementation in the
+package and launches the CUDA library; it raises without a GPU. Tests drive the same host logic on
+CPU ranks (gloo) by passing their own ops object built on the test oracle.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .kernels import ternary_b200 as kb
+
+
+@dataclass
+class ExpertWeights:
+    """Stacked routed-expert weights of one rank.
+
+    w13_packed[i] [E, 2I, Kp(hidden)] uint8: rows 0..I-1 are w1 (gate), rows I..2I-1 are w3 (up)
+    w13_scale[i]  [E, 2I, hidden/group] fp16
+    w2_packed[i]  [E, hidden, Kp(I)] uint8,  w2_scale[i] [E, hidden, I/group] fp16
+    One list entry per stacked term (Mode C k terms; Mode D one).
+    """
+
+    w13_packed: list
+    w13_scale: list
+    w2_packed: list
+    w2_scale: list
+    hidden: int
+    inter: int
+    group: int
+    fmt: str
+
+    @property
+    def n_experts(self) -> int:
+        return self.w13_packed[0].size(0)
+
+    def prepare(self, drop_canonical: bool = True) -> "ExpertWeights":
+        """Re-layout the packed weights once into the tiled device layout the fast kernels read
+        (the reference copies weights to the device at this point, ``boilerplate/ternary/ops.py:41-45``)."""
+        if not isinstance(self.w13_packed[0], kb.TiledWeights) and kb.fast_path_covers(self.hidden, self.group, self.w13_scale[0].dtype) \
+                and kb.fast_path_covers(self.inter, self.group, self.w2_scale[0].dtype):
+            w13 = [kb.tile_weights(p, self.fmt, self.hidden) for p in self.w13_packed]
+            w2 = [kb.tile_weights(p, self.fmt, self.inter) for p in self.w2_packed]
+            if not drop_canonical:
+                self.canonical = (self.w13_packed, self.w2_packed)
+            self.w13_packed, self.w2_packed = w13, w2
+        return self
+
+    def packed_bytes(self) -> int:
+        raw = [getattr(t, "data", t) for ts in (self.w13_packed, self.w13_scale, self.w2_packed, self.w2_scale) for t in ts]
+        return sum(t.numel() * t.element_size() for t in raw)
+
+
+class B200Ops:
+    """The CUDA implementation of the layer's steps (``libdst_b200.so`` through ctypes)."""
+
+    def __init__(self, algo: str = "auto"):
+        self.algo = algo
+
+    @staticmethod
+    def _lib():
+        return kb._require("auto")
+
+    def route(self, logits: torch.Tensor, top_k: int, route_scale: float):
+        lib = self._lib()
+        logits = logits.float().contiguous()
+        T, E = logits.shape
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        with torch.cuda.device(logits.device):
+            _lib.check(lib.dst_route_softmax_topk(logits.data_ptr(), T, E, top_k, ctypes.c_float(route_scale), w.data_ptr(),
+                                                  ids.data_ptr(), kb._stream(logits)))
+        return w, ids
+
+    def sort(self, ids: torch.Tensor, n_experts: int):
+        return kb.sort_by_expert(ids.reshape(-1), n_experts)
+
+    def gather(self, x: torch.Tensor, order: torch.Tensor, top_k: int) -> torch.Tensor:
+        lib = self._lib()
+        x = x.contiguous()
+        out = torch.empty(order.numel(), x.size(1), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(lib.dst_gather_rows(x.data_ptr(), order.data_ptr(), order.numel(), x.size(1), top_k, out.data_ptr(),
+                                           kb._stream(x)))
+        return out
+
+    def gemm(self, x, offsets, packed, scales, K, group, fmt) -> torch.Tensor:
+        return kb.grouped_ternary_gemm_bf16(x, offsets, packed, scales, K, group, fmt, out_dtype=torch.bfloat16,
+                                            algo=self.algo, validate_offsets=False)
+
+    def swiglu(self, gu: torch.Tensor, row_weights: torch.Tensor | None, order: torch.Tensor | None, inter: int,
+               limit: float) -> torch.Tensor:
+        lib = self._lib()
+        h = torch.empty(gu.size(0), inter, dtype=torch.bfloat16, device=gu.device)
+        with torch.cuda.device(gu.device):
+            _lib.check(lib.dst_swiglu(gu.data_ptr(), row_weights.data_ptr() if row_weights is not None else None,
+                                      order.data_ptr() if order is not None else None, gu.size(0), inter,
+                                      ctypes.c_float(limit), h.data_ptr(), kb._stream(gu)))
+        return h
+
+    def combine(self, down: torch.Tensor, order: torch.Tensor, ids: torch.Tensor, T: int, top_k: int) -> torch.Tensor:
+        lib = self._lib()
+        hidden = down.size(1)
+        inv = torch.empty(T * top_k, dtype=torch.int64, device=down.device)
+        y = torch.empty(T, hidden, dtype=torch.bfloat16, device=down.device)
+        ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        with torch.cuda.device(down.device):
+            _lib.check(lib.dst_combine(down.data_ptr(), order.data_ptr(), ids32.data_ptr(), T, top_k, hidden, inv.data_ptr(),
+                                       y.data_ptr(), kb._stream(down)))
+        return y
+
+
+class MoELayer:
+    """Single-device routed-expert layer over ``ExpertWeights``."""
+
+    def __init__(self, weights: ExpertWeights, top_k: int, route_scale: float = 1.0, swiglu_limit: float = 0.0, ops=None):
+        self.w, self.top_k, self.route_scale, self.swiglu_limit = weights, top_k, route_scale, swiglu_limit
+        self.ops = ops if ops is not None else B200Ops()
+
+    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order) -> torch.Tensor:
+        """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows."""
+        w = self.w
+        gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
+        h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit)
+        return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """x [T, hidden] bf16, router logits [T, E] f32 -> y [T, hidden] bf16."""
+        T = x.size(0)
+        weights, ids = self.ops.route(logits, self.top_k, self.route_scale)
+        order, offsets = self.ops.sort(ids, self.w.n_experts)
+        xs = self.ops.gather(x, order, self.top_k)
+        down = self.experts_forward(xs, offsets, weights.reshape(-1), order)
+        return self.ops.combine(down, order, ids, T, self.top_k)
+
+    __call__ = forward
+
+
+def expert_owner_split(n_experts: int, world: int) -> int:
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split evenly over {world} ranks")
+    return n_experts // world
+
+
+class ExpertParallelMoE:
+    """Expert-parallel layer: this rank holds experts [rank * E/W, (rank + 1) * E/W) and its own tokens.
+
+    Per step: route -> sort by (global) expert -> gather rows -> all-to-all of per-expert counts ->
+    all-to-all of rows and routing weights -> local sort by expert -> grouped GEMMs -> inverse
+    all-to-all -> per-token combine. ``weights`` holds only the local experts.
+    """
+
+    def __init__(self, weights: ExpertWeights, n_experts_total: int, top_k: int, group=None, route_scale: float = 1.0,
+                 swiglu_limit: float = 0.0, ops=None):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.pg = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.E = n_experts_total
+        self.El = expert_owner_split(n_experts_total, self.world)
+        if weights.n_experts != self.El:
+            raise ValueError(f"rank holds {weights.n_experts} experts, expected {self.El}")
+        self.local = MoELayer(weights, top_k, route_scale, swiglu_limit, ops)
+        self.ops = self.local.ops
+        self.top_k = top_k
+        self.last_dispatch_rows = 0
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        dist, W, El = self.dist, self.world, self.El
+        T = x.size(0)
+        weights, ids = self.ops.route(logits, self.top_k, self.local.route_scale)
+        order, offsets = self.ops.sort(ids, self.E)  # sorted by global expert = by owner rank, then local expert
+        xs = self.ops.gather(x, order, self.top_k)
+        row_w = weights.reshape(-1)[order].contiguous()
+
+        counts = offsets.diff().to(torch.int64).contiguous()  # [E] rows per global expert
+        recv_counts = torch.empty_like(counts)  # [W * El]: rows from each source rank per local expert
+        dist.all_to_all_single(recv_counts, counts, group=self.pg)
+        send_split = counts.view(W, El).sum(1)
+        recv_split = recv_counts.view(W, El).sum(1)
+        splits = torch.stack([send_split, recv_split]).cpu()  # the one host sync of the step
+        send_l, recv_l = splits[0].tolist(), splits[1].tolist()
+        R = int(sum(recv_l))
+        self.last_dispatch_rows = R
+
+        xr = torch.empty(R, x.size(1), dtype=xs.dtype, device=x.device)
+        wr = torch.empty(R, dtype=torch.float32, device=x.device)
+        dist.all_to_all_single(xr, xs, recv_l, send_l, group=self.pg)
+        dist.all_to_all_single(wr, row_w, recv_l, send_l, group=self.pg)
+
+        # received rows are ordered (source rank, local expert): sort them by local expert
+        local_ids = torch.arange(El, device=x.device, dtype=torch.int64).repeat(W).repeat_interleave(recv_counts.view(-1), output_size=R)
+        order2, offsets2 = self.ops.sort(local_ids, El)
+        xs2 = self.ops.gather(xr, order2, 1)
+        down2 = self.local.experts_forward(xs2, offsets2, wr, order2)
+        back = torch.empty_like(down2)
+        back[order2] = down2  # undo the local sort: row p of down2 is received row order2[p]
+
+        down = torch.empty(xs.size(0), back.size(1), dtype=back.dtype, device=x.device)
+        dist.all_to_all_single(down, back, send_l, recv_l, group=self.pg)
+        return self.ops.combine(down, order, ids, T, self.top_k)
+
+    __call__ = forward

@@ -1,0 +1,119 @@
+"""Ternary linear layers (Mode C with k terms, Mode D with k = 1) on B200: the surface of the
+reference's ``boilerplate/ternary/ops.py`` (``quant_act_int8``, ``PackedTerm``, ``TernaryLinear``).
+
+The engines hold one ``TernaryLinear`` per weight (reference ``engine/model.py:361-370``,
+``engine/standard.py:37-42``) and call it with activations of any leading shape. Here every call
+is one CUDA launch that sums all stacked terms; ``act="bf16"`` feeds bf16 activations with fp16
+group scales and fp32 accumulation, ``act="int8"`` quantises per token first (one more kernel) and
+follows the reference's int8 contract. There is no CPU or dequantised fallback.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from ..kernels import ternary_b200 as kb
+from .pack import unpack
+
+
+def quant_act_int8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token absmax int8: x ~= q * s, q in [-127, 127] (reference ``ops.py:20-25``), one kernel."""
+    lib = kb._require("auto")
+    if not x.is_cuda:
+        raise RuntimeError("B200 ternary kernel unavailable for CPU tensors")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.size(-1))
+    if x2.dtype not in (torch.float32, torch.bfloat16):
+        x2 = x2.float()
+    x2 = x2.contiguous()
+    q = torch.empty(x2.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(x2.size(0), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.dst_quant_act_int8(x2.data_ptr(), int(x2.dtype == torch.float32), x2.size(0), x2.size(1),
+                                          q.data_ptr(), s.data_ptr(), kb._stream(x2)))
+    return q.view(*lead, -1), s.view(lead)
+
+
+@dataclass
+class PackedTerm:
+    """One term of a stacked ternary weight (reference ``ops.py:28-31``)."""
+
+    packed: torch.Tensor  # [N, ceil(K / per_byte)] uint8
+    scale: torch.Tensor  # [N, G] fp16/bf16 as stored
+
+
+class TernaryLinear:
+    """Drop-in for the reference class (``ops.py:34-86``): same constructor, same call.
+
+    ``backend`` accepts "auto", "b200" or "cuda"; anything else (the reference's "cpp"/"torch")
+    raises, since this package has no CPU path. Weights are copied to the activation's device once
+    and kept there, as the reference's ``_on`` does (``ops.py:41-45``); scales stay in their stored
+    16-bit type (fp16 -> fp32 is exact, so reading fp16 in the kernel equals the reference's upcast,
+    ``ops.py:37``).
+    """
+
+    def __init__(self, terms: list[PackedTerm], K: int, fmt: str, group: int, act: str = "int8", backend: str = "auto",
+                 algo: str = "auto"):
+        kb._fmt_code(fmt)
+        if act not in ("int8", "bf16"):
+            raise ValueError(f"unknown activation mode {act!r}")
+        if backend not in kb.BACKENDS:
+            raise RuntimeError(f"backend {backend!r} is unavailable in this package (no CPU path)")
+        self.terms, self.K, self.fmt, self.group, self.act = terms, K, fmt, group, act
+        self.backend, self.algo = backend, algo
+        self._dev = None
+
+    def _on(self, device):
+        """([packed], [scale [1,N,G]]) on ``device``, copied once and kept. Shapes the fast kernels cover
+        (group 128, K % 128 == 0, fp16 scales, bf16 activations) are kept in the tiled device layout,
+        everything else as the canonical ``[1, N, Kp]`` bytes."""
+        if self._dev is None or self._dev[0] != device:
+            packed = [t.packed.to(device).contiguous()[None] for t in self.terms]
+            scales = []
+            for t in self.terms:
+                s = t.scale.to(device)
+                if s.dtype not in (torch.float16, torch.float32, torch.bfloat16):
+                    s = s.float()
+                scales.append(s.contiguous()[None])
+            if len({s.dtype for s in scales}) > 1:
+                scales = [s.float() for s in scales]
+            if self.act == "bf16" and self.algo != "generic" and kb.fast_path_covers(self.K, self.group, scales[0].dtype):
+                packed = [kb.tile_weights(p, self.fmt, self.K) for p in packed]
+            self._dev = (device, packed, scales)
+        return self._dev[1], self._dev[2]
+
+    @property
+    def out_features(self) -> int:
+        return self.terms[0].packed.size(0)
+
+    def dequantized(self) -> torch.Tensor:
+        """fp32 [N, K] ``sum_i unpack(packed_i) * scale_i`` (reference ``ops.py:51-58``), built with the unpack kernel."""
+        dev = self._dev[0] if self._dev is not None else "cuda"
+        packed, scales = self._on(torch.device(dev))
+        w = None
+        for p, s in zip(packed, scales):
+            p = p.untile() if isinstance(p, kb.TiledWeights) else p
+            d = unpack(p[0], self.fmt, self.K).float() * s[0].float().repeat_interleave(self.group, -1)[:, : self.K]
+            w = d if w is None else w + d
+        return w
+
+    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("B200 ternary kernel unavailable for CPU tensors (this backend has no CPU path)")
+        shape = x.shape
+        x2 = x.reshape(-1, self.K)
+        packed, scales = self._on(x2.device)
+        if self.act == "int8":
+            q, s = quant_act_int8(x2)
+            lib = kb._require(self.backend)
+            out = torch.empty(x2.size(0), self.out_features, dtype=torch.float32, device=x2.device)
+            kb._grouped(lib, q, s, None, packed, scales, self.K, self.group, self.fmt, out, False, self.algo)
+        else:
+            xa = x2 if x2.dtype in (torch.bfloat16, torch.float16) else x2.bfloat16()
+            od = out_dtype if out_dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+            out = kb.grouped_ternary_gemm_bf16(xa, None, packed, scales, self.K, self.group, self.fmt, out_dtype=od,
+                                               algo=self.algo, backend=self.backend)
+        return out.view(*shape[:-1], -1).to(out_dtype)

@@ -1,0 +1,198 @@
+/*
+ * dst_b200.h - C ABI of the B200 (sm_100a) ternary expert-GEMM library (libdst_b200.so).
+ *
+ * The library replaces ONE path of the reference project Vedant-Sood/DeepSeekTernarized
+ * ("Boilerplate"): the Mode C/D ternary linear and the MoE routed-expert GEMM. Every entry point
+ * takes plain pointers and sizes, launches on the CUDA stream it is given and returns a status
+ * code; nothing here allocates device memory unless its comment says so. All device pointers must
+ * belong to the device that is current when the call is made.
+ *
+ * Formats (reference: boilerplate/ternary/pack.py:1-17). A trit t in {-1,0,+1} is stored as the
+ * digit u = t + 1. Weights are [N, K] row-major, K contiguous; each row is packed on its own and
+ * padded to a whole byte with digit 1 (t = 0).
+ *   fmt 2 = TQ2: byte = u0 | u1<<2 | u2<<4 | u3<<6      -> ceil(K/4) bytes per row
+ *   fmt 1 = TQ1: byte = u0 + 3 u1 + 9 u2 + 27 u3 + 81 u4 -> ceil(K/5) bytes per row (values 243..255
+ *                decode to five zeros)
+ * Scales: one per output row per `group` consecutive K entries, [N, ceil(K/group)].
+ * Stacked (Mode C) weights are `n_terms` such (packed, scale) pairs; their products are summed.
+ */
+#ifndef DST_B200_H
+#define DST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A CUDA stream handle (cudaStream_t / CUstream) passed as an opaque pointer; NULL = default stream. */
+typedef void* dst_stream_t;
+
+/* Status codes. The Python shim maps them to the exception types the reference raises:
+ * BAD_ARG/BAD_SHAPE/UNSUPPORTED/ALIGNMENT -> RuntimeError (the reference's TORCH_CHECK failures,
+ * boilerplate/kernels/csrc/ternary_cuda_kernel.cu:109-141), BAD_OFFSETS -> ValueError("offsets ...")
+ * (boilerplate/kernels/ternary_cuda.py:94-97). */
+enum {
+  DST_OK = 0,
+  DST_ERR_BAD_ARG = 1,     /* null pointer, K <= 0, group <= 0, fmt not 1/2, bad enum value */
+  DST_ERR_BAD_SHAPE = 2,   /* sizes inconsistent with each other or beyond documented bounds */
+  DST_ERR_BAD_OFFSETS = 3, /* offsets not nondecreasing from 0 to T */
+  DST_ERR_UNSUPPORTED = 4, /* the requested kernel does not cover this shape (see each entry) */
+  DST_ERR_ALIGNMENT = 5,   /* a pointer misses the alignment the requested kernel needs */
+  DST_ERR_CUDA = 6,        /* a CUDA runtime call failed; see dst_last_cuda_error() */
+  DST_ERR_TIMEOUT = 7      /* a bounded device-side wait expired (reported by dst_check_device_status) */
+};
+
+enum { DST_FMT_TQ1 = 1, DST_FMT_TQ2 = 2 };           /* boilerplate/kernels/ternary_cuda.py:46-49 */
+enum { DST_SCALE_F16 = 0, DST_SCALE_F32 = 1, DST_SCALE_BF16 = 2 };
+enum { DST_OUT_F32 = 0, DST_OUT_BF16 = 1, DST_OUT_F16 = 2 };
+enum { DST_ACT_BF16 = 0, DST_ACT_F16 = 1, DST_ACT_I8 = 2 };
+/* Kernel choice. AUTO picks DECODE for few rows per expert, PREFILL for many, and GENERIC for
+ * shapes the two fast kernels do not cover. */
+enum { DST_ALGO_AUTO = 0, DST_ALGO_GENERIC = 1, DST_ALGO_DECODE = 2, DST_ALGO_PREFILL = 3 };
+/* Weight layout: CANONICAL is the reference's [E, N, packed_cols]; TILED is the device layout built
+ * once by dst_tile_weights (below), which the two fast kernels read. */
+enum { DST_LAYOUT_CANONICAL = 0, DST_LAYOUT_TILED = 1 };
+
+#define DST_MAX_TERMS 4
+#define DST_MAX_EXPERTS 65535 /* the reference's bound, ternary_cuda_kernel.cu:128 */
+
+int dst_abi_version(void);
+const char* dst_status_string(int status);
+/* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
+const char* dst_last_cuda_error(void);
+
+/* ceil(K / 4) for TQ2, ceil(K / 5) for TQ1; -1 for a bad fmt or K <= 0.
+ * Replaces boilerplate/ternary/pack.py:30-31 (packed_cols). */
+int64_t dst_packed_cols(int fmt, int64_t K);
+
+/* Device pack: int8 trits [N, K] -> uint8 [N, packed_cols]. Trits outside {-1,0,1} -> DST_ERR_BAD_ARG
+ * is NOT detected on the device; the caller guarantees the range, as the reference's packer does.
+ * Replaces boilerplate/ternary/pack.py:34-45,54-59,77-78 (_digits, pack_tq2, pack_tq1, pack). */
+int dst_pack(const int8_t* trits, int64_t N, int64_t K, int fmt, uint8_t* packed, dst_stream_t stream);
+
+/* Device unpack: uint8 [N, packed_cols] -> int8 trits [N, K], bit-exact with the reference table
+ * (TQ1 bytes 243..255 -> 0; a TQ2 field of 3 -> +2, as the reference's shift-and-mask gives).
+ * Replaces boilerplate/ternary/pack.py:48-51,62-74,81-82 (unpack_tq2, tq1_lut, unpack_tq1, unpack). */
+int dst_unpack(const uint8_t* packed, int64_t N, int64_t K, int fmt, int8_t* trits, dst_stream_t stream);
+
+/*
+ * Tiled device layout: tiled[e][n / 128][sb][n % 128][64 bytes], a superblock sb being 64 bytes of one
+ * row (256 trits in TQ2, 320 in TQ1). Rows are padded to a multiple of 128 and K to whole superblocks
+ * with zero trits. TQ1 bytes keep their base-3 value; TQ2 32-bit words are bit-permuted so that the
+ * low and the high half hold the even and the odd trits of 16 consecutive ones. dst_tiled_bytes gives
+ * the buffer size (-1 on bad arguments); dst_untile_weights restores the canonical bytes bit for bit.
+ * `tiled` must be 16-byte aligned. The conversion is the one-time copy the reference makes when a
+ * linear first meets a device (boilerplate/ternary/ops.py:41-45, TernaryLinear._on).
+ */
+int64_t dst_tiled_bytes(int fmt, int64_t E, int64_t N, int64_t K);
+int dst_tile_weights(const uint8_t* canonical, int64_t E, int64_t N, int64_t K, int fmt, uint8_t* tiled,
+                     dst_stream_t stream);
+int dst_untile_weights(const uint8_t* tiled, int64_t E, int64_t N, int64_t K, int fmt, uint8_t* canonical,
+                       dst_stream_t stream);
+
+/* Per-token absmax int8 quantisation: s = max(absmax/127, 1e-8), q = clamp(rint(x/s), -127, 127).
+ * x is bf16 or f32 ([M, K]); q int8 [M, K]; s f32 [M].
+ * Replaces boilerplate/ternary/ops.py:20-25 (quant_act_int8). */
+int dst_quant_act_int8(const void* x, int x_is_f32, int64_t M, int64_t K, int8_t* q, float* s,
+                       dst_stream_t stream);
+
+/*
+ * The ternary grouped GEMM.
+ *
+ *   out[t, n] (+)= row_scale[t] * sum_{i < n_terms} sum_g scale_i[e(t), n, g]
+ *                                  * sum_{k in group g} x[t, k] * trit_i[e(t), n, k]
+ *
+ * Rows of x are sorted by expert: expert e owns rows offsets[e] .. offsets[e+1]. A plain linear is
+ * the case E = 1 with offsets = NULL.
+ *
+ *   out          [T, N], type out_dtype; overwritten, or accumulated into when accumulate != 0
+ *                (f32 only), which is how the reference sums Mode C terms (ternary/ops.py:71-79).
+ *   x            [T, K] activations of type act_dtype (bf16 for the Mode C/D north-star path; int8
+ *                for the reference's CUDA contract, boilerplate/kernels/ternary_cuda.py:3-9).
+ *   row_scale    [T] f32 or NULL (= 1). For int8 activations this is x_scale.
+ *   offsets      device int64 [E+1], or NULL when E == 1.
+ *   offsets_host optional host copy of the same E+1 values. When given it is validated exactly as
+ *                the reference does (ternary_cuda_kernel.cu:129-139) before anything is launched;
+ *                when NULL the kernels clamp every row range to [0, T] instead.
+ *   weight_layout DST_LAYOUT_CANONICAL or DST_LAYOUT_TILED
+ *   packed       n_terms device pointers, each [E, N, packed_cols] uint8 (canonical) or a buffer of
+ *                dst_tiled_bytes(fmt, E, N, K) bytes made by dst_tile_weights (tiled)
+ *   scales       n_terms device pointers, each [E, N, ceil(K/group)] of scale_dtype
+ *   algo         DST_ALGO_*; a fast kernel asked for explicitly returns DST_ERR_UNSUPPORTED /
+ *                DST_ERR_ALIGNMENT when it does not cover the call (AUTO falls back to GENERIC).
+ *   workspace    device scratch of at least dst_gemm_workspace_bytes(...) bytes, 256-byte aligned, or
+ *                NULL. The prefill kernel keeps the fp16 copy of the activations and the per-row
+ *                factors there; it is free again when the launched work has finished.
+ *
+ * Fast-kernel coverage: tiled weights, group == 128, K % 128 == 0, fp16 scales, bf16 or f16
+ * activations. GENERIC reads canonical weights only.
+ * Bounds: E <= DST_MAX_EXPERTS, K <= 2^24, N <= 2^24, T <= 2^31 - 1.
+ *
+ * Replaces the native entry ternary_grouped_gemm (boilerplate/kernels/csrc/ternary_cuda.cpp:7-10,
+ * ternary_cuda_kernel.cu:106-152) and the CPU entry ternary_gemm it shadows
+ * (boilerplate/kernels/csrc/boilerplate_cpu.cpp:80-128).
+ */
+int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate, const void* x, int act_dtype,
+                             const float* row_scale, const int64_t* offsets, const int64_t* offsets_host,
+                             const void* const* packed, int weight_layout, const void* const* scales,
+                             int n_terms, int scale_dtype, int64_t E, int64_t T, int64_t N, int64_t K,
+                             int64_t group, int fmt, int algo, void* workspace, size_t workspace_bytes,
+                             dst_stream_t stream);
+
+/* Scratch bytes dst_ternary_grouped_gemm needs for `algo` (AUTO: the largest any kernel may need). */
+size_t dst_gemm_workspace_bytes(int algo, int act_dtype, int64_t T, int64_t K);
+
+/*
+ * Routing sort: flattened expert ids [n] (int64 or int32) -> the stable order that sorts them by
+ * expert and offsets[E+1] (int64). Ids outside [0, E) are counted in *bad_count (device int32, may
+ * be NULL) and dropped. Runs three small kernels; `workspace` must hold dst_sort_workspace_bytes(n, E).
+ * Replaces boilerplate/kernels/ternary_cuda.py:114-118 (sort_by_expert).
+ */
+size_t dst_sort_workspace_bytes(int64_t n, int64_t E);
+int dst_sort_by_expert(const void* ids, int ids_are_i32, int64_t n, int64_t E, int64_t* order,
+                       int64_t* offsets, int32_t* bad_count, void* workspace, dst_stream_t stream);
+
+/*
+ * Router: softmax over E logits per token, top-k by score (ties: lower expert id first), weights
+ * renormalised by (sum + 1e-20) and multiplied by route_scale.
+ * logits [T, E] f32 -> weights [T, k] f32, ids [T, k] int32. E <= 1024, k <= 8.
+ * Replaces boilerplate/engine/model.py:389-405 (route) for score_func = "softmax", no bias.
+ */
+int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
+                           float* weights, int32_t* ids, dst_stream_t stream);
+
+/*
+ * Gather token rows into expert-sorted order: dst[p, :] = src[order[p] / top_k, :] (16-bit elements,
+ * bf16 stays bf16). Replaces the x[idx] gathers of boilerplate/engine/model.py:418-419.
+ */
+int dst_gather_rows(const void* src, const int64_t* order, int64_t n_rows, int64_t K, int top_k,
+                    void* dst, dst_stream_t stream);
+
+/*
+ * SwiGLU between the up and down projections, reference rounding points included:
+ * gate/up are the bf16 outputs of w1/w3 laid out as gu[p, 0:I] = gate, gu[p, I:2I] = up;
+ * h = bf16( weight[order[p]] * silu(gate) * up ), with optional clamps (limit > 0: up to +-limit,
+ * gate to <= limit). Replaces boilerplate/engine/model.py:376-386 (swiglu, up to the w2 call).
+ */
+int dst_swiglu(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
+               int64_t inter, float limit, void* h_bf16, dst_stream_t stream);
+
+/*
+ * Combine: y[t, :] = bf16( sum over the token's top_k slots, in increasing expert id, of
+ * down[pos(t, slot), :] ), fp32 accumulation; `order` is the routing sort's order and `ids` the
+ * flattened expert ids [T * top_k]. Replaces the `y[idx] += ...` accumulation and the final cast of
+ * boilerplate/engine/model.py:413-422. `inv` is an int64 [T * top_k] scratch the call fills.
+ */
+int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
+                int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
+
+/* Reads (and clears) the device-side status word that bounded waits in the tcgen05 kernel write when
+ * they give up. Synchronises `stream`. Returns DST_OK or DST_ERR_TIMEOUT. */
+int dst_check_device_status(dst_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DST_B200_H */

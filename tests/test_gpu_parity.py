@@ -1,0 +1,319 @@
+"""GPU parity: the CUDA library, called through the C ABI by the drop-in modules, against the CPU
+oracle and the reference-generated golden fixtures. Bit-exact for packing, sorting and int8
+quantisation; for GEMM outputs the north-star tolerance (relative Frobenius error <= 2e-3, cosine
+>= 0.99999 against the fp64 dequantized product) plus the reference's own allclose bounds
+(rtol 1e-4, atol 1e-3: tests/test_ternary.py:98, tests/test_ternary_cuda.py:80 of the reference)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.helpers import bf16_numpy, bf16_tensor, check_gemm, make_experts, make_terms, stack_experts
+
+pytestmark = pytest.mark.gpu
+FMT = {1: "tq1", 2: "tq2"}
+DEV = "cuda"
+
+
+def fast_algos(K, group, scale_dtype=np.float16):
+    """Kernels that must accept a shape: the fast ones cover group 128, K % 128 == 0, fp16 scales."""
+    ok = group == 128 and K % 128 == 0 and scale_dtype == np.float16
+    return ["generic", "auto"] + (["prefill"] if ok else [])
+
+
+@pytest.fixture(scope="module")
+def kb():
+    from deepseekternarized_b200.kernels import ternary_b200
+
+    assert ternary_b200.ext() is not None, "CUDA library not loaded: no fallback exists"
+    return ternary_b200
+
+
+# ------------------------------------------------------------------------------------------ format
+@pytest.mark.parametrize("fmt", ["tq2", "tq1"])
+@pytest.mark.parametrize("K", [1, 4, 5, 7, 128, 131, 640])
+def test_pack_unpack_bit_exact(golden, fmt, K):
+    from deepseekternarized_b200.ternary import pack as P
+
+    g = golden("format")
+    t, p = g[f"trits_{fmt}_{K}"], g[f"packed_{fmt}_{K}"]
+    got = P.pack(torch.from_numpy(t).to(DEV), fmt)
+    assert got.dtype == torch.uint8 and tuple(got.shape) == (9, P.packed_cols(fmt, K))
+    assert np.array_equal(got.cpu().numpy(), p)
+    assert np.array_equal(P.unpack(torch.from_numpy(p).to(DEV), fmt, K).cpu().numpy(), t)
+
+
+def test_tq1_every_pattern_and_every_byte(golden):
+    from deepseekternarized_b200.ternary import pack as P
+
+    g = golden("format")
+    p = P.pack(torch.from_numpy(g["tq1_patterns"]).to(DEV), "tq1")
+    assert np.array_equal(p.cpu().numpy(), g["tq1_patterns_packed"])
+    assert p.unique().numel() == 243 and int(p.max()) < 243
+    assert np.array_equal(P.unpack(p, "tq1", 5).cpu().numpy(), g["tq1_patterns"])
+    assert np.array_equal(P.tq1_lut().cpu().numpy(), g["tq1_lut"])
+    allb = torch.arange(256, dtype=torch.uint8, device=DEV).view(256, 1)
+    assert np.array_equal(P.unpack(allb, "tq1", 5).cpu().numpy(), g["unpack_all_bytes_tq1"])
+    assert np.array_equal(P.unpack(allb, "tq2", 4).cpu().numpy(), g["unpack_all_bytes_tq2"])
+
+
+@pytest.mark.parametrize("fmt,N,K", [("tq1", 4096, 4096), ("tq2", 2048, 4096), ("tq1", 333, 4097), ("tq2", 0, 64)])
+def test_pack_roundtrip_large_and_empty(fmt, N, K):
+    from deepseekternarized_b200.ternary import pack as P
+
+    t = O.synth_trits(np.random.default_rng(N + K), (N, K))
+    p = P.pack(torch.from_numpy(t).to(DEV), fmt)
+    assert np.array_equal(p.cpu().numpy(), O.pack(t, fmt))
+    assert np.array_equal(P.unpack(p, fmt, K).cpu().numpy(), t)
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+@pytest.mark.parametrize("E,N,K", [(1, 128, 256), (3, 70, 4160), (2, 300, 4096), (1, 5, 7), (4, 2048, 2048)])
+def test_tiled_layout_roundtrip_bit_exact(kb, fmt, E, N, K):
+    """canonical -> tiled -> canonical restores every byte, also for rows and K that need padding and for
+    byte values the packer never writes."""
+    rng = np.random.default_rng(E * N + K)
+    Kp = O.packed_cols(fmt, K)
+    p = rng.integers(0, 256, (E, N, Kp), dtype=np.uint8)
+    tw = kb.tile_weights(torch.from_numpy(p).to(DEV), fmt, K)
+    assert tw.data.numel() == E * -(-N // 128) * -(-K // (256 if fmt == "tq2" else 320)) * 8192
+    assert np.array_equal(tw.untile().cpu().numpy(), p)
+
+
+# ------------------------------------------------------------------------------------------ linear, bf16 acts
+def test_bf16_linear_against_reference_golden(golden, kb):
+    from deepseekternarized_b200.ternary.ops import PackedTerm, TernaryLinear
+
+    g = golden("linear_f32")
+    for c in range(int(g["n_cases"])):
+        K, group, N, M, k_terms, code = (int(v) for v in g[f"c{c}_meta"])
+        fmt = FMT[code]
+        x = O.from_bf16_bits(g[f"c{c}_x_bits"])
+        terms = [(g[f"c{c}_packed{i}"], g[f"c{c}_scale{i}"]) for i in range(k_terms)]
+        for algo in fast_algos(K, group):
+            lin = TernaryLinear([PackedTerm(torch.from_numpy(p), torch.from_numpy(s)) for p, s in terms], K, fmt, group,
+                                act="bf16", backend="b200", algo=algo)
+            xt = bf16_tensor(x, DEV).view(-1, K)
+            y = lin(xt.view(1, -1, K), out_dtype=torch.float32)
+            assert tuple(y.shape) == (1, M, N)
+            y = y.view(M, N).cpu().numpy()
+            np.testing.assert_allclose(y, g[f"c{c}_y_f32"], rtol=1e-4, atol=1e-3, err_msg=f"case {c} {algo}")
+            check_gemm(y, x, terms, K, group, fmt)
+            ybf = lin(xt)  # default bf16 output: at most the last bit may differ from the reference's rounding
+            ref_bf = O.from_bf16_bits(g[f"c{c}_y_bf16_bits"])
+            assert O.rel_fro(bf16_numpy(ybf), ref_bf) < 2e-3
+            deq = lin.dequantized().cpu().numpy()
+            assert np.allclose(deq, O.dequantized(terms, K, group, fmt), rtol=1e-6, atol=0)
+
+
+@pytest.mark.parametrize("case", range(5))
+def test_baseline_shapes_against_oracle_and_golden(golden, kb, case):
+    """BASELINE configs 0 and 1 (single TQ2 / TQ1 linears, K = 4096): seeded inputs rebuilt here, the
+    reference output known through its strided sample in the fixture."""
+    g = golden("baseline_shapes")
+    code, N, K, M = (int(v) for v in g[f"c{case}_meta"])
+    fmt = FMT[code]
+    rng = np.random.default_rng(6000 + case)
+    t = O.synth_trits(rng, (N, K))
+    s = O.synth_scales(rng, (N, K // 128))
+    x = O.synth_acts(rng, (M, K))
+    p = O.pack(t, fmt)
+    for algo in fast_algos(K, 128):
+        y = kb.ternary_gemm_bf16(bf16_tensor(x, DEV), [torch.from_numpy(p).to(DEV)], [torch.from_numpy(s).to(DEV)], K, 128,
+                                 fmt, algo=algo).cpu().numpy()
+        np.testing.assert_allclose(y.reshape(-1)[::61], g[f"c{case}_sample"], rtol=1e-4, atol=1e-3)
+        check_gemm(y, x, [(p, s)], K, 128, fmt)
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+@pytest.mark.parametrize("M", [1, 4, 8, 32])
+@pytest.mark.parametrize("N", [2048, 11008])
+def test_config1_decode_sweep_tq1_equals_tq2_on_same_trits(kb, fmt, M, N):
+    K = 4096
+    rng = np.random.default_rng(N + M)
+    t = O.synth_trits(rng, (N, K))
+    s = O.synth_scales(rng, (N, K // 128))
+    x = O.synth_acts(rng, (M, K))
+    xt = bf16_tensor(x, DEV)
+    st = torch.from_numpy(s).to(DEV)
+    y = {}
+    for f in ("tq1", "tq2"):
+        y[f] = kb.ternary_gemm_bf16(xt, [torch.from_numpy(O.pack(t, f)).to(DEV)], [st], K, 128, f).cpu().numpy()
+    check_gemm(y[fmt], x, [(O.pack(t, fmt), s)], K, 128, fmt)
+    assert O.rel_fro(y["tq1"], y["tq2"]) < 1e-5  # same trits, same arithmetic: formats agree far inside the tolerance
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+@pytest.mark.parametrize("M", [1, 8, 64])
+def test_config3_stacked_k2_decode(kb, fmt, M):
+    for (N, K) in [(2048, 4096), (4096, 2048)]:
+        rng = np.random.default_rng(M + N)
+        terms = make_terms(rng, N, K, 128, fmt, k_terms=2)
+        x = O.synth_acts(rng, (M, K))
+        for algo in fast_algos(K, 128):
+            y = kb.ternary_gemm_bf16(bf16_tensor(x, DEV), [torch.from_numpy(p).to(DEV) for p, _ in terms],
+                                     [torch.from_numpy(s).to(DEV) for _, s in terms], K, 128, fmt, algo=algo).cpu().numpy()
+            check_gemm(y, x, terms, K, 128, fmt)
+            want = O.ternary_linear(x, terms, K, 128, fmt, out_bf16=False)
+            np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-3)
+
+
+def test_accumulate_row_scale_and_output_types(kb):
+    rng = np.random.default_rng(5)
+    N, K, M, fmt = 96, 384, 5, "tq1"
+    terms = make_terms(rng, N, K, 128, fmt, 1)
+    x = O.synth_acts(rng, (M, K))
+    rs = rng.random(M).astype(np.float32) + 0.5
+    p, s = [torch.from_numpy(terms[0][0]).to(DEV)], [torch.from_numpy(terms[0][1]).to(DEV)]
+    base = O.gemm_f32(x, terms[0][0], terms[0][1].astype(np.float32), K, 128, fmt)
+    for algo in fast_algos(K, 128):
+        out = torch.full((M, N), 2.0, device=DEV)
+        kb.ternary_gemm_bf16(bf16_tensor(x, DEV), p, s, K, 128, fmt, row_scale=torch.from_numpy(rs).to(DEV), out=out,
+                             accumulate=True, algo=algo)
+        np.testing.assert_allclose(out.cpu().numpy(), 2.0 + base * rs[:, None], rtol=1e-4, atol=1e-3)
+        for dt in (torch.bfloat16, torch.float16):
+            y = kb.ternary_gemm_bf16(bf16_tensor(x, DEV), p, s, K, 128, fmt, out_dtype=dt, algo=algo)
+            assert y.dtype == dt and O.rel_fro(y.float().cpu().numpy(), base) < 4e-3
+
+
+# ------------------------------------------------------------------------------------------ int8 contract
+def test_int8_contract_against_reference_golden(golden, kb):
+    from deepseekternarized_b200.ternary.ops import quant_act_int8
+
+    g = golden("linear_i8")
+    for c in range(int(g["n_cases"])):
+        K, group, N, M, code = (int(v) for v in g[f"c{c}_meta"])
+        fmt = FMT[code]
+        q, xs = quant_act_int8(torch.from_numpy(g[f"c{c}_x_f32"]).to(DEV))
+        assert np.array_equal(q.cpu().numpy(), g[f"c{c}_q"]) and np.array_equal(xs.cpu().numpy(), g[f"c{c}_xs"])
+        got = kb.ternary_gemm(q, xs, torch.from_numpy(g[f"c{c}_packed"]).to(DEV), torch.from_numpy(g[f"c{c}_scale_f32"]).to(DEV),
+                              K, group, fmt, backend="cuda")
+        np.testing.assert_allclose(got.cpu().numpy(), g[f"c{c}_y_ref"], rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_grouped_and_routing_sort_against_reference_golden(golden, kb, fmt):
+    g = golden("grouped")
+    ids = torch.from_numpy(g[f"{fmt}_ids"]).to(DEV)
+    order, offsets = kb.sort_by_expert(ids, 6)
+    assert np.array_equal(order.cpu().numpy(), g[f"{fmt}_order"]) and np.array_equal(offsets.cpu().numpy(), g[f"{fmt}_offsets"])
+    rows = (order // 2).cpu()
+    q, xs = torch.from_numpy(g[f"{fmt}_q"])[rows].to(DEV), torch.from_numpy(g[f"{fmt}_xs"])[rows].to(DEV)
+    packed, scale = torch.from_numpy(g[f"{fmt}_packed"]).to(DEV), torch.from_numpy(g[f"{fmt}_scale_f32"]).to(DEV)
+    for offs in (offsets, offsets.cpu(), offsets.cpu().tolist()):
+        out = kb.grouped_ternary_gemm(q, xs, offs, packed, scale, 192, 64, fmt)
+        np.testing.assert_allclose(out.cpu().numpy(), g[f"{fmt}_out"], rtol=1e-5, atol=1e-4)
+    with pytest.raises(ValueError, match="offsets"):
+        kb.grouped_ternary_gemm(q, xs, [0, 9], packed, scale, 192, 64, fmt)
+    with pytest.raises(ValueError, match="offsets"):
+        kb.grouped_ternary_gemm(q, xs, torch.tensor([0, 5, 4, 9, 12, 15, 18], device=DEV), packed, scale, 192, 64, fmt)
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+@pytest.mark.parametrize("T", [1, 3, 37])
+def test_reference_cuda_parity_shapes(kb, fmt, T):
+    """The shapes of the reference's own (never run) CUDA test, tests/test_ternary_cuda.py:69-87:
+    N not a multiple of any tile, K not a multiple of the group, one empty expert."""
+    E, N, K, group = 5, 70, 4160, 128
+    rng = np.random.default_rng(7 + T)
+    t = O.synth_trits(rng, (E, N, K), p_zero=1 / 3)
+    packed = np.stack([O.pack(t[e], fmt) for e in range(E)])
+    scales = (rng.random((E, N, -(-K // group))).astype(np.float16).astype(np.float32) + np.float32(0.01))
+    counts = np.array([T, 0, 2 * T, 1, T])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    R = int(offsets[-1])
+    q, xs = O.quant_act_int8(rng.standard_normal((R, K)).astype(np.float32))
+    want = O.grouped_gemm_i8(q, xs, offsets, packed, scales, K, group, fmt)
+    got = kb.grouped_ternary_gemm(torch.from_numpy(q).to(DEV), torch.from_numpy(xs).to(DEV), offsets, torch.from_numpy(packed).to(DEV),
+                                  torch.from_numpy(scales).to(DEV), K, group, fmt, backend="cuda")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-3)
+    # the same shapes on the bf16 path, fp16 scales
+    x = O.synth_acts(rng, (R, K))
+    s16 = scales.astype(np.float16)
+    want = O.grouped_gemm_f32(x, offsets, packed, s16.astype(np.float32), K, group, fmt)
+    got = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, [torch.from_numpy(packed).to(DEV)],
+                                       [torch.from_numpy(s16).to(DEV)], K, group, fmt)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=2e-3)
+
+
+def test_native_entry_rejects_malformed_tensors(kb):
+    """tests/test_kernel_security.py:19-38 of the reference, against this backend: every malformed
+    argument raises RuntimeError before any launch."""
+    def args():
+        return dict(x=torch.ones(1, 5, dtype=torch.int8, device=DEV), x_scale=torch.ones(1, device=DEV),
+                    packed=torch.ones(2, 2, dtype=torch.uint8, device=DEV), w_scale=torch.ones(2, 2, device=DEV), K=5, group=3, fmt="tq2")
+    kb.ternary_gemm(**args())
+    bad = [("K", 0), ("K", 2**62), ("group", 0), ("x", torch.ones(1, 4, dtype=torch.int8, device=DEV)),
+           ("packed", torch.ones(2, 1, dtype=torch.uint8, device=DEV)), ("packed", torch.ones(2, 2, device=DEV)),
+           ("w_scale", torch.ones(2, 1, device=DEV)), ("w_scale", torch.ones(1, 2, device=DEV)), ("x_scale", torch.ones(0, device=DEV)),
+           ("packed", torch.ones(2, 2, dtype=torch.uint8)), ("packed", torch.ones(2, 4, dtype=torch.uint8, device=DEV)[:, ::2].t())]
+    for key, value in bad:
+        a = args()
+        a[key] = value
+        with pytest.raises(RuntimeError):
+            kb.ternary_gemm(**a)
+    with pytest.raises(ValueError):
+        kb.ternary_gemm(**{**args(), "fmt": "tq0"})
+
+
+# ------------------------------------------------------------------------------------------ MoE layer
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_moe_layer_against_reference_golden(golden, fmt):
+    from deepseekternarized_b200.moe import B200Ops, ExpertWeights, MoELayer
+
+    g = golden("moe_layer")
+    T, hidden, inter, E, topk, group, k_terms = (int(v) for v in g[f"{fmt}_meta"])
+    x = O.from_bf16_bits(g[f"{fmt}_x_bits"])
+    experts = [tuple([(g[f"{fmt}_e{e}_{wn}_packed{i}"], g[f"{fmt}_e{e}_{wn}_scale{i}"]) for i in range(k_terms)]
+                     for wn in ("w1", "w2", "w3")) for e in range(E)]
+    logits = torch.from_numpy(x @ g[f"{fmt}_gate_w"].T).to(DEV)
+    ops = B200Ops()
+    w, ids = ops.route(logits, topk, 1.0)
+    assert np.array_equal(ids.cpu().numpy(), g[f"{fmt}_route_indices"])
+    np.testing.assert_allclose(w.cpu().numpy(), g[f"{fmt}_route_weights"], rtol=1e-5, atol=1e-7)
+    ew = ExpertWeights(*stack_experts(experts, k_terms, DEV), hidden, inter, group, fmt)
+    y = MoELayer(ew, topk)(bf16_tensor(x, DEV), logits)
+    want = O.from_bf16_bits(g[f"{fmt}_y_bits"])
+    assert O.rel_fro(bf16_numpy(y), want) < 2e-3
+
+
+@pytest.mark.parametrize("fmt,k_terms", [("tq1", 1), ("tq2", 2)])
+def test_moe_layer_steps_against_oracle(fmt, k_terms):
+    """A mid-sized layer (T=300, 16 experts, top-6): every step against the oracle."""
+    from deepseekternarized_b200.moe import B200Ops, ExpertWeights, MoELayer
+
+    T, hidden, inter, E, topk, group = 300, 512, 256, 16, 6, 128
+    rng = np.random.default_rng(11)
+    experts = make_experts(rng, E, hidden, inter, group, fmt, k_terms)
+    x = O.synth_acts(rng, (T, hidden))
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    logits[:, 3] = -40.0  # an empty expert
+    ops = B200Ops()
+    w, ids = ops.route(torch.from_numpy(logits).to(DEV), topk, 1.0)
+    w_ref, idx_ref = O.route_from_logits(logits, topk)
+    assert np.array_equal(ids.cpu().numpy(), idx_ref)
+    np.testing.assert_allclose(w.cpu().numpy(), w_ref, rtol=1e-5, atol=1e-7)
+    order, offsets = ops.sort(ids, E)
+    order_ref, offsets_ref = O.sort_by_expert(idx_ref.reshape(-1), E)
+    assert np.array_equal(order.cpu().numpy(), order_ref) and np.array_equal(offsets.cpu().numpy(), offsets_ref)
+    xs = ops.gather(bf16_tensor(x, DEV), order, topk)
+    assert np.array_equal(bf16_numpy(xs), x[order_ref // topk])
+    ew = ExpertWeights(*stack_experts(experts, k_terms, DEV), hidden, inter, group, fmt)
+    y = MoELayer(ew, topk)(bf16_tensor(x, DEV), torch.from_numpy(logits).to(DEV))
+    want = O.moe_layer(x, w_ref, idx_ref, experts, hidden, inter, group, fmt)
+    assert O.rel_fro(bf16_numpy(y), want) < 2e-3 and O.cosine(bf16_numpy(y), want) > 0.99999
+
+
+def test_sort_large_and_bad_ids(kb):
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, 384, 98304).astype(np.int64)
+    order, offsets = kb.sort_by_expert(torch.from_numpy(ids).to(DEV), 384)
+    o_ref, f_ref = O.sort_by_expert(ids, 384)
+    assert np.array_equal(order.cpu().numpy(), o_ref) and np.array_equal(offsets.cpu().numpy(), f_ref)
+    order, offsets = kb.sort_by_expert(torch.from_numpy(ids.astype(np.int32)).to(DEV), 384)
+    assert np.array_equal(order.cpu().numpy(), o_ref)
+    order, offsets = kb.sort_by_expert(torch.zeros(0, dtype=torch.int64, device=DEV), 4)
+    assert order.numel() == 0 and offsets.cpu().tolist() == [0] * 5

@@ -1,0 +1,78 @@
+"""Host-side behaviour of the drop-in modules without a GPU: the error contract of the reference's
+kernel backend (boilerplate/kernels/ternary_cuda.py, tests/test_ternary_cuda.py:60-66 of the reference)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from deepseekternarized_b200.kernels import ternary_b200 as kb
+from deepseekternarized_b200.ternary import ops, pack
+
+NO_GPU = not torch.cuda.is_available()
+
+
+def test_format_helpers():
+    assert pack.packed_cols("tq2", 4096) == 1024 and pack.packed_cols("tq1", 4096) == 820
+    assert pack.packed_cols("tq1", 2048) == 410 and pack.packed_cols("tq2", 1) == 1
+    assert pack.bits_per_weight("tq1") == 1.6 and pack.bits_per_weight("tq2") == 2.0
+    assert pack.FORMATS == ("tq2", "tq1")
+
+
+def test_unknown_format_is_a_value_error():
+    with pytest.raises(ValueError, match="unknown ternary packing"):
+        kb.ternary_gemm(torch.zeros(1, 4, dtype=torch.int8), torch.ones(1), torch.zeros(2, 1, dtype=torch.uint8),
+                        torch.ones(2, 1), 4, 4, "tq3")
+
+
+def test_non_int8_activations_are_a_type_error():
+    with pytest.raises(TypeError, match="int8"):
+        kb.ternary_gemm(torch.zeros(1, 4), torch.ones(1), torch.zeros(2, 1, dtype=torch.uint8), torch.ones(2, 1), 4, 4, "tq2")
+    with pytest.raises(TypeError, match="bf16"):
+        kb.ternary_gemm_bf16(torch.zeros(1, 4), [torch.zeros(2, 1, dtype=torch.uint8)], [torch.ones(2, 1).half()], 4, 4, "tq2")
+
+
+def test_bad_offsets_are_a_value_error_before_anything_else():
+    x = torch.zeros(9, 8, dtype=torch.int8)
+    packed = torch.zeros(6, 4, 2, dtype=torch.uint8)
+    scales = torch.ones(6, 4, 1)
+    for offs in ([0, 9], [0, 1, 2, 3, 4, 5, 8], [1, 1, 2, 3, 4, 5, 9], [0, 3, 2, 3, 4, 5, 9]):
+        with pytest.raises(ValueError, match="offsets"):
+            kb.grouped_ternary_gemm(x, torch.ones(9), offs, packed, scales, 8, 8, "tq2")
+
+
+@pytest.mark.skipif(not NO_GPU, reason="checks the no-GPU behaviour")
+def test_backend_absence_is_clean_and_loud():
+    assert kb.ext() is None
+    x = torch.zeros(2, 64, dtype=torch.int8)
+    packed, scales = torch.zeros(4, 16, dtype=torch.uint8), torch.ones(4, 1)
+    for backend in ("auto", "cuda", "b200"):
+        with pytest.raises(RuntimeError, match="unavailable"):
+            kb.ternary_gemm(x, torch.ones(2), packed, scales, 64, 64, "tq2", backend=backend)
+    with pytest.raises(RuntimeError, match="unavailable"):
+        kb.grouped_ternary_gemm(x, torch.ones(2), [0, 2], packed[None], scales[None], 64, 64, "tq2")
+    with pytest.raises(RuntimeError, match="unavailable"):
+        kb.ternary_gemm_bf16(x.bfloat16(), [packed], [scales.half()], 64, 64, "tq2")
+    with pytest.raises(RuntimeError, match="unavailable"):
+        kb.sort_by_expert(torch.zeros(4, dtype=torch.int64), 2)
+    with pytest.raises(RuntimeError, match="unavailable"):
+        pack.pack(torch.zeros(2, 8, dtype=torch.int8), "tq1")
+    with pytest.raises(RuntimeError, match="unavailable"):
+        pack.unpack(torch.zeros(2, 2, dtype=torch.uint8), "tq2", 8)
+    with pytest.raises(RuntimeError, match="unavailable"):
+        ops.quant_act_int8(torch.zeros(2, 8))
+
+
+def test_ternary_linear_has_no_cpu_or_foreign_backend():
+    term = ops.PackedTerm(torch.zeros(4, 16, dtype=torch.uint8), torch.ones(4, 1).half())
+    for backend in ("cpp", "torch"):
+        with pytest.raises(RuntimeError, match="unavailable"):
+            ops.TernaryLinear([term], 64, "tq2", 64, act="bf16", backend=backend)
+    with pytest.raises(ValueError):
+        ops.TernaryLinear([term], 64, "tq9", 64)
+    with pytest.raises(ValueError):
+        ops.TernaryLinear([term], 64, "tq2", 64, act="fp8")
+    lin = ops.TernaryLinear([term], 64, "tq2", 64, act="bf16")
+    assert lin.out_features == 4
+    with pytest.raises(RuntimeError, match="unavailable"):
+        lin(torch.zeros(3, 64, dtype=torch.bfloat16))
