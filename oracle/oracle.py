@@ -303,6 +303,22 @@ def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_li
     return bf16_round(y)
 
 
+def moe_layer_f64(x, weights, indices, experts, hidden, inter, group, fmt):
+    """The same layer in fp64 with no intermediate rounding (dequantized weights, boilerplate/ternary/ops.py:51-58):
+    the yardstick for how much of a layer-level difference is bf16 rounding noise."""
+    x = np.asarray(x, np.float64)
+    y = np.zeros_like(x)
+    for e in range(len(experts)):
+        idx, top = np.nonzero(indices == e)
+        if idx.size == 0:
+            continue
+        w1, w2, w3 = (dequantized(t, K, group, fmt) for t, K in zip(experts[e], (hidden, inter, hidden)))
+        g, u = x[idx] @ w1.T, x[idx] @ w3.T
+        h = np.asarray(weights, np.float64)[idx, top, None] * (g / (1.0 + np.exp(-g))) * u
+        y[idx] += h @ w2.T
+    return y
+
+
 # ------------------------------------------------------------------------------------ metrics
 def rel_fro(a, ref) -> float:
     """boilerplate/reference/compare.py:61-62: ||a - ref||_F / ||ref||_F"""

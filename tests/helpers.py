@@ -40,6 +40,18 @@ def check_gemm(got: np.ndarray, x: np.ndarray, terms, K, group, fmt, tol=2e-3, c
     return rel, cos
 
 
+def check_layer(got: np.ndarray, want: np.ndarray, exact64: np.ndarray):
+    """Layer-level parity. The reference layer rounds to bf16 after each of its three linears and at
+    the end, so two correct implementations differ by rounding flips; measure both against the
+    unrounded fp64 layer: ours may be at most 25 % further from it than the reference-order oracle is,
+    and must stay within twice that distance of the oracle itself. Returns (ours, oracle's) distance."""
+    e_ref, e_got = O.rel_fro(want, exact64), O.rel_fro(got, exact64)
+    assert e_got <= max(1.25 * e_ref, 2e-3), (e_got, e_ref)
+    assert O.rel_fro(got, want) <= max(2.0 * e_ref, 2e-3), (O.rel_fro(got, want), e_ref)
+    assert O.cosine(got, want) >= 0.9999
+    return e_got, e_ref
+
+
 class OracleOps:
     """The MoE layer's compute steps on the CPU oracle, torch CPU tensors in and out."""
 

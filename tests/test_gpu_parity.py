@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.helpers import bf16_numpy, bf16_tensor, check_gemm, make_experts, make_terms, stack_experts
+from tests.helpers import bf16_numpy, bf16_tensor, check_gemm, check_layer, make_experts, make_terms, stack_experts
 
 pytestmark = pytest.mark.gpu
 FMT = {1: "tq1", 2: "tq2"}
@@ -277,7 +277,8 @@ def test_moe_layer_against_reference_golden(golden, fmt):
     ew = ExpertWeights(*stack_experts(experts, k_terms, DEV), hidden, inter, group, fmt)
     y = MoELayer(ew, topk)(bf16_tensor(x, DEV), logits)
     want = O.from_bf16_bits(g[f"{fmt}_y_bits"])
-    assert O.rel_fro(bf16_numpy(y), want) < 2e-3
+    y64 = O.moe_layer_f64(x, g[f"{fmt}_route_weights"], g[f"{fmt}_route_indices"], experts, hidden, inter, group, fmt)
+    check_layer(bf16_numpy(y), want, y64)
 
 
 @pytest.mark.parametrize("fmt,k_terms", [("tq1", 1), ("tq2", 2)])
@@ -304,7 +305,9 @@ def test_moe_layer_steps_against_oracle(fmt, k_terms):
     ew = ExpertWeights(*stack_experts(experts, k_terms, DEV), hidden, inter, group, fmt)
     y = MoELayer(ew, topk)(bf16_tensor(x, DEV), torch.from_numpy(logits).to(DEV))
     want = O.moe_layer(x, w_ref, idx_ref, experts, hidden, inter, group, fmt)
-    assert O.rel_fro(bf16_numpy(y), want) < 2e-3 and O.cosine(bf16_numpy(y), want) > 0.99999
+    check_layer(bf16_numpy(y), want, O.moe_layer_f64(x, w_ref, idx_ref, experts, hidden, inter, group, fmt))
+    y2 = MoELayer(ew.prepare(), topk)(bf16_tensor(x, DEV), torch.from_numpy(logits).to(DEV))  # weights tiled once
+    assert torch.equal(y, y2)
 
 
 def test_sort_large_and_bad_ids(kb):
