@@ -20,7 +20,8 @@ SOURCES = ["api.cu", "format_kernels.cu", "layout_kernels.cu", "gemm_generic.cu"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC"]
 
-OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_BAD_OFFSETS, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT = range(8)
+OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_BAD_OFFSETS, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(9)
+NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024 + 16384
 FMT_TQ1, FMT_TQ2 = 1, 2
 SCALE_F16, SCALE_F32, SCALE_BF16 = 0, 1, 2
 OUT_F32, OUT_BF16, OUT_F16 = 0, 1, 2
@@ -73,6 +74,10 @@ _SIGNATURES = {
                                                 ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
                                                 ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "dst_ternary_grouped_gemm_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                        ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]),
     "dst_gemm_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64]),
     "dst_tiled_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]),
     "dst_tile_weights": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,

@@ -33,6 +33,7 @@ extern "C" const char* dst_status_string(int status) {
     case DST_ERR_ALIGNMENT: return "pointer alignment not sufficient for the requested kernel";
     case DST_ERR_CUDA: return "CUDA runtime error";
     case DST_ERR_TIMEOUT: return "a bounded device-side wait expired";
+    case DST_ERR_TOO_LARGE: return "the call needs more scratch than the no-allocation entry point's fixed array holds";
     default: return "unknown status";
   }
 }

@@ -24,6 +24,8 @@
 // roles leave their loops, the CTA frees TMEM and the kernel records DST_ERR_TIMEOUT in the status word.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "dst_common.cuh"
 
 namespace dst {
@@ -573,4 +575,84 @@ extern "C" int dst_check_device_status(dst_stream_t stream) {
     return DST_ERR_TIMEOUT;
   }
   return DST_OK;
+}
+
+// ------------------------------------------------------------------------------------------ no-allocation entry
+// Scratch for dst_ternary_grouped_gemm_noalloc: the fp16 copy of the activations and the per-row factors
+// that the tcgen05 kernel otherwise keeps in a caller-provided workspace. It is part of the library
+// image, so every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DST_NOALLOC_SCRATCH_BYTES];
+
+namespace dst {
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};  // device address of g_noalloc_scratch, per device ordinal
+}  // namespace
+}  // namespace dst
+
+extern "C" int dst_ternary_grouped_gemm_noalloc(void* out, int out_dtype, int accumulate, const void* x, int act_dtype,
+                                                const float* row_scale, const int64_t* offsets, const int64_t* offsets_host,
+                                                const void* const* packed_tiled, const void* const* scales, int n_terms,
+                                                int64_t E, int64_t T, int64_t N, int64_t K, int fmt, dst_stream_t stream) {
+  using namespace dst;
+  if (K <= 0 || (fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2)) return DST_ERR_BAD_ARG;
+  if (out_dtype < DST_OUT_F32 || out_dtype > DST_OUT_F16 || (act_dtype != DST_ACT_BF16 && act_dtype != DST_ACT_F16))
+    return DST_ERR_BAD_ARG;
+  if (n_terms < 1 || n_terms > DST_MAX_TERMS || E < 0 || T < 0 || N < 0) return DST_ERR_BAD_ARG;
+  if (accumulate && out_dtype != DST_OUT_F32) return DST_ERR_BAD_ARG;
+  if (E > DST_MAX_EXPERTS || K > (int64_t(1) << 24) || N > (int64_t(1) << 22) || T >= (int64_t(1) << 30)) return DST_ERR_BAD_SHAPE;
+  if (K % 128 != 0) return DST_ERR_UNSUPPORTED;
+  if (E != 1 && E != 0 && offsets == nullptr) return DST_ERR_BAD_ARG;
+  if (offsets_host) {
+    if (offsets_host[0] != 0 || offsets_host[E] != T) return DST_ERR_BAD_OFFSETS;
+    for (int64_t e = 0; e < E; ++e)
+      if (offsets_host[e + 1] < offsets_host[e]) return DST_ERR_BAD_OFFSETS;
+  }
+  if (E == 0) return T == 0 ? DST_OK : DST_ERR_BAD_OFFSETS;
+  if (T == 0 || N == 0) return DST_OK;
+  if (!out || !x || !packed_tiled || !scales) return DST_ERR_BAD_ARG;
+  // The whole scratch need of this call must fit the static array: refuse anything larger.
+  if (prefill_workspace_bytes(act_dtype, T, K) > (size_t)DST_NOALLOC_SCRATCH_BYTES) return DST_ERR_TOO_LARGE;
+
+  // Set-up, once per device, with that device current: in host code the array's name is only a
+  // stand-in for the symbol, so ask the runtime for its device address and hand THAT to the kernels.
+  int dev = -1;
+  DST_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return DST_ERR_UNSUPPORTED;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    DST_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) return record_cuda_error(cudaErrorInvalidSymbol, "cudaGetSymbolAddress(g_noalloc_scratch)");
+    g_noalloc_ptr[dev] = ptr;
+  }
+
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.accumulate = accumulate;
+  a.x = x;
+  a.act_dtype = act_dtype;
+  a.row_scale = row_scale;
+  a.offsets = offsets;
+  a.terms.n = n_terms;
+  for (int i = 0; i < n_terms; ++i) {
+    if (!packed_tiled[i] || !scales[i]) return DST_ERR_BAD_ARG;
+    a.terms.packed[i] = static_cast<const uint8_t*>(packed_tiled[i]);
+    a.terms.scale[i] = scales[i];
+  }
+  a.scale_dtype = DST_SCALE_F16;
+  a.E = E;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.group = 128;
+  a.Kp = cdiv64(K, fmt == DST_FMT_TQ2 ? 4 : 5);
+  a.G = K / 128;
+  a.fmt = fmt;
+  a.max_rows = -1;
+  a.weight_layout = DST_LAYOUT_TILED;
+  a.workspace = g_noalloc_ptr[dev];
+  a.workspace_bytes = DST_NOALLOC_SCRATCH_BYTES;
+  return launch_prefill(a, static_cast<cudaStream_t>(stream));
 }

@@ -41,7 +41,8 @@ enum {
   DST_ERR_UNSUPPORTED = 4, /* the requested kernel does not cover this shape (see each entry) */
   DST_ERR_ALIGNMENT = 5,   /* a pointer misses the alignment the requested kernel needs */
   DST_ERR_CUDA = 6,        /* a CUDA runtime call failed; see dst_last_cuda_error() */
-  DST_ERR_TIMEOUT = 7      /* a bounded device-side wait expired (reported by dst_check_device_status) */
+  DST_ERR_TIMEOUT = 7,     /* a bounded device-side wait expired (reported by dst_check_device_status) */
+  DST_ERR_TOO_LARGE = 8    /* the call needs more scratch than the no-allocation entry point's fixed array holds */
 };
 
 enum { DST_FMT_TQ1 = 1, DST_FMT_TQ2 = 2 };           /* boilerplate/kernels/ternary_cuda.py:46-49 */
@@ -187,6 +188,40 @@ int dst_swiglu(const void* gu_bf16, const float* route_weights, const int64_t* o
  */
 int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
                 int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
+
+/*
+ * The grouped GEMM for callers that must not allocate device memory. (This entry has no counterpart
+ * in the reference project.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - a serving loop whose memory was
+ * carved up at start-up and handed to other owners, a host thread that may not take the allocator's
+ * lock or synchronise the device (cudaMalloc and cudaFree can do both), or a plug-in that is only
+ * given pointers and has no allocator of its own. dst_ternary_grouped_gemm needs a workspace from
+ * such a caller; this entry brings its own: DST_NOALLOC_SCRATCH_BYTES of device memory that are part
+ * of the library image (every GPU that loads the library holds them until the process exits).
+ *
+ * It is the tcgen05 kernel of dst_ternary_grouped_gemm (algo DST_ALGO_PREFILL) and returns the same
+ * results: tiled weights (dst_tile_weights), fp16 scales, group 128, K % 128 == 0, bf16 or fp16
+ * activations; inputs and outputs are still the caller's. The call itself performs no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *
+ * Limits and rules:
+ *   - T * K * 2 + T * 4 bytes (plus up to 512 bytes of alignment slack) must fit DST_NOALLOC_SCRATCH_BYTES,
+ *     8 MiB + 16 KiB: 1024 rows at K = 4096, 2048 rows at K = 2048. A larger call returns DST_ERR_TOO_LARGE
+ *     and launches nothing.
+ *   - The first call on a device looks up the scratch array's device address
+ *     (cudaGetSymbolAddress, with that device current) and keeps it. Make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the previous call left there.
+ *     Nothing in it has to start at zero (every byte a call reads, it has written first), but two calls
+ *     whose GPU work overlaps - different streams, or different host threads - race on it. Keep the
+ *     calls of one device on one stream, or order them with events.
+ */
+#define DST_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u + 16384u)
+int dst_ternary_grouped_gemm_noalloc(void* out, int out_dtype, int accumulate, const void* x, int act_dtype,
+                                     const float* row_scale, const int64_t* offsets, const int64_t* offsets_host,
+                                     const void* const* packed_tiled, const void* const* scales, int n_terms,
+                                     int64_t E, int64_t T, int64_t N, int64_t K, int fmt, dst_stream_t stream);
 
 /* Reads (and clears) the device-side status word that bounded waits in the tcgen05 kernel write when
  * they give up. Synchronises `stream`. Returns DST_OK or DST_ERR_TIMEOUT. */
