@@ -57,13 +57,14 @@ def measured_peaks():
 
 
 # --------------------------------------------------------------------------------------------- synthetic data
-def synth_expert_weights(n_local: int, expert0: int, device, fmt=FMT, hidden=HIDDEN, inter=INTER):
+def synth_expert_weights(n_local: int, expert0: int, device, fmt=None, hidden=HIDDEN, inter=INTER):
     """Seeded random-init experts generated on the device: trits i.i.d. P(0)=0.4, P(+-1)=0.3, scales
     lognormal(-4, 0.3) in fp16. Expert e's weights depend only on (SEED, e), so every sharding sees the
     same global model."""
     from deepseekternarized_b200.moe import ExpertWeights
     from deepseekternarized_b200.ternary.pack import pack, packed_cols
 
+    fmt = FMT if fmt is None else fmt
     w13p = torch.empty(n_local, 2 * inter, packed_cols(fmt, hidden), dtype=torch.uint8, device=device)
     w13s = torch.empty(n_local, 2 * inter, hidden // GROUP, dtype=torch.float16, device=device)
     w2p = torch.empty(n_local, hidden, packed_cols(fmt, inter), dtype=torch.uint8, device=device)
@@ -79,8 +80,9 @@ def synth_expert_weights(n_local: int, expert0: int, device, fmt=FMT, hidden=HID
     return ExpertWeights([w13p], [w13s], [w2p], [w2s], hidden, inter, GROUP, fmt).prepare()
 
 
-def synth_tokens(n_tokens: int, token0: int, n_experts=N_EXPERTS, hidden=HIDDEN):
+def synth_tokens(n_tokens: int, token0: int, n_experts=None, hidden=HIDDEN):
     """Host-side seeded tokens (bf16 ~N(0,1)) and router logits (f32 ~N(0,1)) in pinned memory."""
+    n_experts = N_EXPERTS if n_experts is None else n_experts
     g = torch.Generator().manual_seed(SEED + 7 + token0)
     x = torch.randn(n_tokens, hidden, generator=g).bfloat16()
     logits = torch.randn(n_tokens, n_experts, generator=g)
@@ -211,7 +213,9 @@ def run_reference_arm(args):
 
 
 def workload_config(n_gpus: int) -> dict:
-    return {"workload": "BASELINE config 4: expert-parallel MoE routed-expert layer", "tokens_per_step": TOKENS, "hidden": HIDDEN,
+    full = TOKENS == 16384 and N_EXPERTS == 384 and FMT == "tq1"
+    return {"workload": "BASELINE config 4: expert-parallel MoE routed-expert layer" if full else
+            "REDUCED case of BASELINE config 4 (fewer tokens/experts, same shapes): for profiler captures only", "tokens_per_step": TOKENS, "hidden": HIDDEN,
             "inter": INTER, "experts": N_EXPERTS, "top_k": TOP_K, "format": FMT, "group": GROUP, "scale_dtype": "fp16",
             "parallelism": f"ep{n_gpus}", "l2": "weights (2.09 GB) and activations exceed the 126 MB L2; no flush needed"}
 
@@ -249,11 +253,11 @@ def gemm_microbench(device, peaks) -> dict:
             u = torch.rand(N, K, generator=g, device=device)
             p[e] = pack(torch.where(u < 0.4, 0, torch.where(u < 0.7, 1, -1)).to(torch.int8), fmt)
         s = torch.exp(torch.randn(E, N, K // GROUP, generator=g, device=device) * 0.3 - 4.0).half()
-        return p, s
+        return kb.tile_weights(p, fmt, K), s  # tiled once, as a loaded model holds them
 
     for fmt, N, K, Ms in (("tq2", 4096, 4096, (1, 16)), ("tq1", 2048, 4096, (1, 8)), ("tq1", 4096, 4096, (1, 4, 8, 32)),
                           ("tq1", 11008, 4096, (1, 8))):
-        wbytes = N * packed_cols(fmt, K) + N * (K // GROUP) * 2
+        wbytes = N * packed_cols(fmt, K) + N * (K // GROUP) * 2  # canonical packed bytes + fp16 scales: the algorithmic bytes
         copies = max(2, int(np.ceil(400e6 / wbytes)))
         p, s = weights(copies, N, K, fmt)
         for M in Ms:
@@ -332,7 +336,12 @@ def main():
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel decode/prefill numbers")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per step over all ranks (default: BASELINE config 4)")
+    ap.add_argument("--experts", type=int, default=N_EXPERTS, help="routed experts (default: BASELINE config 4); smaller "
+                    "values give a reduced case for profiler captures and are named in the JSON line")
+    ap.add_argument("--fmt", default=FMT, choices=["tq1", "tq2"], help="packing of the expert weights (default: BASELINE config 4, tq1)")
     args = ap.parse_args()
+    globals()["TOKENS"], globals()["N_EXPERTS"], globals()["FMT"] = args.tokens, args.experts, args.fmt
     if args.impl == "reference":
         return run_reference_arm(args)
 

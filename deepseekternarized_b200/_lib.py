@@ -102,9 +102,10 @@ _SIGNATURES = {
 @lru_cache(1)
 def load() -> ctypes.CDLL:
     """dlopen the built library and declare every exported symbol. Raises if it was never built."""
-    if not LIB_PATH.exists():
-        raise RuntimeError(f"{LIB_PATH} is missing: run __graft_entry__.build() (there is no CPU fallback)")
-    lib = ctypes.CDLL(str(LIB_PATH))
+    path = Path(os.environ.get("DST_B200_LIB", str(LIB_PATH)))  # DST_B200_LIB: load a library built elsewhere
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: run __graft_entry__.build() (there is no CPU fallback)")
+    lib = ctypes.CDLL(str(path))
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args

@@ -7,8 +7,9 @@
 // Mapping ("swap AB"): the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), up to 256
 // token rows are the MMA N dimension (TMEM columns), so tiles stay full when an expert has few rows.
 // Both operands are fp16, K-major, 128-byte swizzled, 64 K-elements per pipeline stage:
-//   A (weights)      written by 8 dequant warps: packed trits (tiled layout, see layout_kernels.cu) ->
-//                    scale * trit, exact in fp16 -> st.shared in the canonical SWIZZLE_128B layout
+//   A (weights)      packed 8 KB slabs of the tiled layout (layout_kernels.cu) arrive by cp.async.bulk in a
+//                    two-slot ring; 8 dequant warps turn them into scale * trit, exact in fp16, and store
+//                    the tile in the canonical SWIZZLE_128B layout
 //   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA), 32-row boxes
 //   D (accumulator)  fp32 in TMEM, two buffers of 256 columns so the epilogue of one tile overlaps the
 //                    MMAs of the next
@@ -38,6 +39,8 @@ constexpr int PF_A_BYTES = 128 * 128; // one A stage: 128 weight rows x 64 fp16
 constexpr int PF_B_BYTES = PF_TN * 128;
 constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_B_BYTES;
 constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
+constexpr int PF_SLAB = 8192;                   // one (row tile, superblock) slab of packed weights
+constexpr int PF_SMEM_MAX = 232448;             // 227 KB of dynamic shared memory per CTA
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 __device__ int g_device_status = 0;
@@ -51,6 +54,7 @@ struct PrefillParams {
   void* out;
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S, kstages;
+  int nstage;  // depth of the A/B stage ring (2..4), chosen by the host from the shared-memory budget
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -127,7 +131,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 struct TileWalker {
   const int64_t* offsets;
   int E, T, NT;
-  int e = -1, mt_count = 0;
+  int e = -1, mt_count = 0, mt_rows = 0;
   long long before = 0;
   int64_t ra = 0, rb = 0;
   __device__ bool seek(long long t, int& e_out, int& nt, int& row0, int& rows) {
@@ -136,12 +140,16 @@ struct TileWalker {
       if (++e >= E) return false;
       row_range(offsets, e, T, ra, rb);
       mt_count = (int)((rb - ra + PF_TN - 1) / PF_TN);
+      // an expert with more rows than one tile holds is split evenly (multiples of 16 rows), so no
+      // tile repeats the dequantisation of the weights for a handful of left-over rows
+      mt_rows = mt_count > 0 ? (int)((((rb - ra + mt_count - 1) / mt_count) + 15) & ~15LL) : 0;
     }
     const long long local = t - before;
     const int mt = (int)(local / NT);
     nt = (int)(local - (long long)mt * NT);
-    row0 = (int)ra + mt * PF_TN;
-    rows = (int)(rb - row0 < PF_TN ? rb - row0 : PF_TN);
+    row0 = (int)ra + mt * mt_rows;
+    rows = (int)(rb - row0 < mt_rows ? rb - row0 : mt_rows);
+    if (rows < 0) rows = 0;
     e_out = e;
     return true;
   }
@@ -217,13 +225,33 @@ __device__ __forceinline__ void tq1_dispatch(int o, uint32_t lo, uint32_t hi, ui
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
-template <int FMT, int NSTAGE>
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Scale of group g (0..7 inside the 8 scales held in `sc`), as an fp16 pair.
+__device__ __forceinline__ __half2 pick_scale(const uint4& sc, int g) {
+  const uint32_t w = (g & 4) ? ((g & 2) ? sc.w : sc.z) : ((g & 2) ? sc.y : sc.x);
+  const uint32_t h = (g & 1) ? (w >> 16) : (w & 0xFFFFu);
+  return bits_h2(h | (h << 16));
+}
+
+// Shared memory map (dynamic, 1024-byte aligned):
+//   [0, nstage * 48 KB)            stage ring: A tile 16 KB (128 rows x 64 fp16) + B tile 32 KB (256 rows x 64 fp16)
+//   then 2 * n_terms * 8 KB        packed-weight slabs: slot-major, one 8 KB slab per stacked term
+//   then 64 KB (TQ1 only)          table of unscaled fp16 trits
+template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) {
+  constexpr int SPB = FMT == 2 ? 4 : 5;  // 64-trit stages per 64-byte superblock
+  constexpr int MAX_STAGE = 4;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* lut = smem + NSTAGE * PF_STAGE_BYTES;  // TQ1 only
-  __shared__ uint64_t bar_full[NSTAGE], bar_empty[NSTAGE], bar_tfull[2], bar_tempty[2];
+  const int NSTAGE = p.nstage;
+  uint8_t* slabs = smem + NSTAGE * PF_STAGE_BYTES;
+  uint8_t* lut = slabs + 2 * p.n_terms * PF_SLAB;  // TQ1 only
+  __shared__ uint64_t bar_full[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[2], bar_tempty[2], bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
@@ -231,13 +259,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     abort_s = 0;
-    for (int s = 0; s < NSTAGE; ++s) {
+    for (int s = 0; s < MAX_STAGE; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1 + 8);  // TMA producer's expect_tx arrive + one arrive per dequant warp
       mbar_init(smem_u32(&bar_empty[s]), 1);     // tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);   // tcgen05.commit after the tile's last MMA
       mbar_init(smem_u32(&bar_tempty[a]), 4);  // one arrive per epilogue warp
+      mbar_init(smem_u32(&bar_pfull[a]), 1);   // bulk-copy producer's expect_tx arrive
+      mbar_init(smem_u32(&bar_pempty[a]), 8);  // one arrive per dequant warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -275,15 +305,43 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
   walk.T = p.T;
   walk.NT = p.NT;
   int e, nt, row0, rows;
+  const int nsb = (p.kstages + SPB - 1) / SPB;  // superblocks a tile touches
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (activations)
+    // ------------------------------------------------------------------ producer: TMA for B, bulk copies for packed slabs
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, pit = 0;  // stage counter, packed-slab counter (both run across tiles)
       bool ok = true;
+      // One slab (all stacked terms of one superblock) is always requested one superblock ahead of the
+      // stage loads, so the dequant warps find it in shared memory when they get there.
+      TileWalker ahead = walk;
+      int ae, ant, arow0, arows, asb = 0;
+      long long at = blockIdx.x;
+      bool have = ahead.seek(at, ae, ant, arow0, arows);
+      auto issue_slab = [&]() -> bool {
+        while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
+        if (!have) return true;
+        const int slot = pit & 1;
+        if (!mbar_wait(smem_u32(&bar_pempty[slot]), ((pit >> 1) & 1u) ^ 1u, abort_flag)) return false;
+        const uint32_t full = smem_u32(&bar_pfull[slot]);
+        mbar_arrive_expect_tx(full, (uint32_t)p.n_terms * PF_SLAB);
+        const int64_t off = (((int64_t)ae * p.NT + ant) * p.S + asb) * PF_SLAB;
+        for (int i = 0; i < p.n_terms; ++i)
+          bulk_load(smem_u32(slabs + (slot * p.n_terms + i) * PF_SLAB), p.tiled[i] + off, PF_SLAB, full);
+        ++pit;
+        if (++asb >= nsb) {
+          asb = 0;
+          at += gridDim.x;
+          have = ahead.seek(at, ae, ant, arow0, arows);
+        }
+        return true;
+      };
+      ok = issue_slab();
       for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+        if (rows <= 0) continue;
         const int boxes = (rows + PF_BOX - 1) / PF_BOX;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
+          if (ks % SPB == 0 && !issue_slab()) { ok = false; break; }
           const int s = it % NSTAGE;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
@@ -298,7 +356,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
     if (lane == 0) {
       uint32_t it = 0, tile = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x, ++tile) {
+      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+        if (rows <= 0) continue;
         const uint32_t a = tile & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[a]), ((tile >> 1) & 1u) ^ 1u, abort_flag)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -317,13 +376,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
           umma_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs have read it
         }
         if (ok) umma_commit(smem_u32(&bar_tfull[a]));
+        ++tile;
       }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tile = 0;
-    for (long long t = blockIdx.x; walk.seek(t, e, nt, row0, rows); t += gridDim.x, ++tile) {
+    for (long long t = blockIdx.x; walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+      if (rows <= 0) continue;
       const uint32_t a = tile & 1u;
       if (!mbar_wait(smem_u32(&bar_tfull[a]), (tile >> 1) & 1u, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -341,12 +402,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
           for (int j = 16; j < 32; ++j) v[j] = 0u;
         }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const float rs_lane = (p.row_scale && c0 + lane < rows) ? p.row_scale[row0 + c0 + lane] : 1.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int m = c0 + j;
+          const float rs = __shfl_sync(0xffffffffu, rs_lane, j);
           if (m < rows && n_ok) {
-            float val = __uint_as_float(v[j]);
-            if (p.row_scale) val *= p.row_scale[row0 + m];
+            const float val = __uint_as_float(v[j]) * rs;
             const int64_t o = (int64_t)(row0 + m) * p.N + n;
             if (p.out_dtype == DST_OUT_BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(val);
             else if (p.out_dtype == DST_OUT_F16) static_cast<__half*>(p.out)[o] = __float2half_rn(val);
@@ -357,31 +419,72 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[a]));
+      ++tile;
     }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
     const int td = tid - 192;
     const int r = td & 127, hh = td >> 7;
+    const int swz = (r >> 1) & 3;  // 16-byte chunk swizzle of the tiled layout
     const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
-    uint32_t it = 0;
+    const bool vec_scales = (p.G & 7) == 0;  // rows of 8 k scales are 16-byte aligned
+    uint32_t it = 0, pit = 0;
     bool ok = true;
+    // scales of the row for 8 groups (16 stages) at a time, fetched one block ahead (also across tiles)
+    uint4 sc_next[DST_MAX_TERMS];
+    TileWalker ahead = walk;
+    int ae, ant, arow0, arows;
+    long long at = blockIdx.x;
+    bool have = ahead.seek(at, ae, ant, arow0, arows);
+    while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
+    auto load_scales = [&](int ee, int nn, int g0, uint4* dst) {
+      const bool n_ok = nn < p.N;
+#pragma unroll
+      for (int i = 0; i < DST_MAX_TERMS; ++i) {
+        if (i < p.n_terms) {
+          if (!n_ok || g0 >= p.G) {
+            dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          } else if (vec_scales) {
+            dst[i] = *reinterpret_cast<const uint4*>(p.scale[i] + ((int64_t)ee * p.N + nn) * p.G + g0);
+          } else {
+            uint32_t h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              h[j] = g0 + j < p.G ? (uint32_t)__half_as_ushort(p.scale[i][((int64_t)ee * p.N + nn) * p.G + g0 + j]) : 0u;
+            dst[i] = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+          }
+        }
+      }
+    };
+    if (have) load_scales(ae, ant * 128 + r, 0, sc_next);
     for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
-      const int n = nt * 128 + r;
-      const bool n_ok = n < p.N;
-      const int64_t srow = ((int64_t)e * p.N + (n_ok ? n : 0)) * p.G;
-      const int64_t tile_base = (((int64_t)e * p.NT + nt) * p.S) * 8192 + (int64_t)r * 64;
+      if (rows <= 0) continue;
+      // the tile after this one (for the scale prefetch at the end of this tile)
+      at = t + gridDim.x;
+      have = ahead.seek(at, ae, ant, arow0, arows);
+      while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
+      uint4 sc[DST_MAX_TERMS];
       for (int ks = 0; ks < p.kstages; ++ks, ++it) {
         const int s = it % NSTAGE;
+        if ((ks & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < DST_MAX_TERMS; ++i) sc[i] = sc_next[i];
+          if (ks + 16 < p.kstages) load_scales(e, nt * 128 + r, (ks + 16) >> 1, sc_next);
+          else if (have) load_scales(ae, ant * 128 + r, 0, sc_next);
+        }
+        const int sbk = ks % SPB;
+        const uint32_t slot = pit & 1u;
+        if (sbk == 0 && !mbar_wait(smem_u32(&bar_pfull[slot]), (pit >> 1) & 1u, abort_flag)) { ok = false; break; }
+        const uint8_t* slab = slabs + (size_t)slot * p.n_terms * PF_SLAB + r * 64;
         __half2 acc[16];
-        const int g = ks >> 1;  // 64-trit stage -> 128-trit scale group
+        const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
         if (FMT == 2) {
-          const int64_t off = tile_base + (int64_t)(ks >> 2) * 8192 + (ks & 3) * 16 + hh * 8;
+          const int boff = ((sbk ^ swz) << 4) + hh * 8;
 #pragma unroll
           for (int i = 0; i < DST_MAX_TERMS; ++i) {
             if (i < p.n_terms) {
-              const uint2 w = *reinterpret_cast<const uint2*>(p.tiled[i] + off);
-              const __half sc = n_ok ? p.scale[i][srow + g] : __float2half(0.f);
-              const __half2 s2 = __half2half2(sc);
+              const uint2 w = *reinterpret_cast<const uint2*>(slab + i * PF_SLAB + boff);
+              const __half2 s2 = pick_scale(sc[i], g);
               if (i == 0) {
                 tq2_word<true>(w.x, s2, acc);
                 tq2_word<true>(w.y, s2, acc + 8);
@@ -392,22 +495,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
             }
           }
         } else {
-          const int sb = ks / 5, qq = (ks - sb * 5) * 2 + hh;  // 32-trit slot 0..9 inside the 320-trit superblock
+          const int qq = sbk * 2 + hh;  // 32-trit slot 0..9 inside the 320-trit superblock
           const int tau = qq * 32, b0 = tau / 5, o = tau - b0 * 5;
           const int wi = b0 >> 2, sh = (b0 & 3) * 8;
-          const int64_t off = tile_base + (int64_t)sb * 8192;
 #pragma unroll
           for (int i = 0; i < DST_MAX_TERMS; ++i) {
             if (i < p.n_terms) {
-              const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.tiled[i] + off);
-              const uint32_t w0 = wp[wi], w1 = wi + 1 < 16 ? wp[wi + 1] : 0u, w2 = wi + 2 < 16 ? wp[wi + 2] : 0u;
+              const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
+              // logical word w of the row sits in chunk (w >> 2) ^ swz
+              const uint32_t w0 = wp[(((wi >> 2) ^ swz) << 2) | (wi & 3)];
+              const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) >> 2) ^ swz) << 2) | ((wi + 1) & 3)] : 0u;
+              const uint32_t w2 = wi + 2 < 16 ? wp[((((wi + 2) >> 2) ^ swz) << 2) | ((wi + 2) & 3)] : 0u;
               const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
-              const __half sc = n_ok ? p.scale[i][srow + g] : __float2half(0.f);
-              const __half2 s2 = __half2half2(sc);
+              const __half2 s2 = pick_scale(sc[i], g);
               if (i == 0) tq1_dispatch<true>(o, lo, hi, lut_addr, s2, acc);
               else tq1_dispatch<false>(o, lo, hi, lut_addr, s2, acc);
             }
           }
+        }
+        if (sbk == SPB - 1 || ks == p.kstages - 1) {  // last read of this slab: hand the slot back
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+          ++pit;
         }
         if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         uint8_t* arow = smem + s * PF_STAGE_BYTES + r * 128;
@@ -486,15 +595,21 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int FMT, int NSTAGE>
-int launch_fmt(const CUtensorMap& map, const PrefillParams& p, long long tiles_upper, cudaStream_t st) {
-  const size_t smem = 1024 + (size_t)NSTAGE * PF_STAGE_BYTES + (FMT == 1 ? PF_LUT_BYTES : 0);
-  DST_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<FMT, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+template <int FMT>
+int launch_fmt(const CUtensorMap& map, PrefillParams p, long long tiles_upper, cudaStream_t st) {
+  // deepest stage ring the shared-memory budget allows next to the packed slabs and the TQ1 table
+  const size_t fixed = 1024 + (size_t)2 * p.n_terms * PF_SLAB + (FMT == 1 ? PF_LUT_BYTES : 0);
+  int nstage = (int)((PF_SMEM_MAX - fixed) / PF_STAGE_BYTES);
+  nstage = nstage > 4 ? 4 : nstage;
+  if (nstage < 2) return DST_ERR_UNSUPPORTED;
+  p.nstage = nstage;
+  const size_t smem = fixed + (size_t)nstage * PF_STAGE_BYTES;
+  DST_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   DST_CUDA_TRY(cudaGetDevice(&dev));
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = (int)(tiles_upper < sms ? (tiles_upper < 1 ? 1 : tiles_upper) : sms);
-  prefill_kernel<FMT, NSTAGE><<<grid, PF_THREADS, smem, st>>>(map, p);
+  prefill_kernel<FMT><<<grid, PF_THREADS, smem, st>>>(map, p);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }
@@ -518,7 +633,7 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   if (!prefill_supports(a)) return DST_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return DST_ERR_ALIGNMENT;
   for (int i = 0; i < a.terms.n; ++i)
-    if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 1) != 0)
+    if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 15) != 0)
       return DST_ERR_ALIGNMENT;
 
   // 1. activations -> fp16 rows + per-row power-of-two factor, in the workspace
@@ -560,7 +675,7 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.kstages = (int)(a.K / 64);
   const long long tiles_upper = ((long long)cdiv64(a.T, PF_TN) + a.E) * p.NT;
-  return a.fmt == DST_FMT_TQ2 ? launch_fmt<2, 4>(map, p, tiles_upper, stream) : launch_fmt<1, 3>(map, p, tiles_upper, stream);
+  return a.fmt == DST_FMT_TQ2 ? launch_fmt<2>(map, p, tiles_upper, stream) : launch_fmt<1>(map, p, tiles_upper, stream);
 }
 
 }  // namespace dst

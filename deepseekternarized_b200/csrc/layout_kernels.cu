@@ -17,6 +17,10 @@
 //        (low half, high half) pair is two consecutive trits: trit 2j sits in bits [2j, 2j+1], trit 2j+1
 //        in bits [16+2j, 17+2j]. One AND then yields an fp16x2 of adjacent weights.
 //
+// Inside a row-superblock the four 16-byte chunks are stored at chunk index c ^ ((r >> 1) & 3): when a slab
+// sits in shared memory and 32 threads read the same word of 32 consecutive rows (64-byte stride), the
+// accesses spread over 8 bank groups instead of 2.
+//
 // dst_untile_weights inverts the permutation bit for bit.
 #include "dst_common.cuh"
 
@@ -67,7 +71,7 @@ __global__ void tile_kernel(const uint8_t* __restrict__ canon, int64_t E, int64_
         }
       }
     }
-    tiled[i] = w;
+    tiled[(i & ~15LL) | (((q >> 2) ^ ((r >> 1) & 3)) << 2) | (q & 3)] = w;
   }
 }
 
@@ -84,7 +88,8 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int64_t E, int6
     uint8_t v;
     if (FMT == 1) {
       const int64_t sb = b >> 6;
-      v = tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + (b & 63)];
+      const int bi = (int)(b & 63);
+      v = tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + ((((bi >> 4) ^ ((int)(r >> 1) & 3)) << 4) | (bi & 15))];
     } else {
       uint32_t acc = 0;
 #pragma unroll
@@ -92,7 +97,8 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int64_t E, int6
         const int64_t k = b * 4 + j;
         const int64_t sb = k >> 8;
         const int kk = (int)(k & 255), q = kk >> 4, t = kk & 15;
-        const uint32_t w = reinterpret_cast<const uint32_t*>(tiled)[(((e * NT + nt) * S + sb) * 128 + r) * 16 + q];
+        const uint32_t w = reinterpret_cast<const uint32_t*>(tiled)[(((e * NT + nt) * S + sb) * 128 + r) * 16 +
+                                                                    ((((q >> 2) ^ ((int)(r >> 1) & 3)) << 2) | (q & 3))];
         const int bit = (t & 1) ? 16 + (t >> 1) * 2 : (t >> 1) * 2;
         acc |= ((w >> bit) & 3u) << (2 * j);
       }
