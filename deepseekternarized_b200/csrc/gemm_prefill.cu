@@ -17,9 +17,20 @@
 // element within 2^-22 of the row's absolute maximum); the factor comes back through row_scale.
 // tcgen05 kind::f16 refuses an fp16 A with a bf16 B (illegal instruction), hence the conversion.
 //
-// Warp roles (448 threads, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer for B           warp 1      MMA issuer, owns the TMEM allocation
-//   warps 2-5   epilogue (TMEM -> registers -> global)    warps 6-13  dequant producers for A
+// CTA pairs (template parameter CG = 2, used when N is a multiple of 256): two CTAs of a cluster share
+// one tile of 256 weight rows x up to 256 token rows. Each CTA dequantises its own 128 weight rows and
+// loads HALF of the token rows; the pair's leader issues tcgen05.mma.cta_group::2 (M = 256), which reads
+// the A tile of both CTAs and both halves of B. Per SM this halves the activation bytes fetched from L2
+// and held in shared memory per FLOP, which is what bounds the single-CTA form (its 32 KB B stages are
+// too few to cover the TMA latency). The stage-full barrier lives in the leader and collects the TMA
+// bytes and the dequant arrivals of both CTAs; tcgen05.commit multicasts the stage-free and
+// accumulator-full signals to both. Every TMA load writes into the shared memory of the CTA that issues it.
+//
+// Warp roles (704 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer for B and bulk copies of packed slabs
+//   warp 1      MMA issuer, owns the TMEM allocation (in the non-leader CTA of a pair: relays "my A tile is ready")
+//   warps 2-5   epilogue (TMEM -> registers -> global)
+//   warps 6-21  dequant producers for A: thread (row, quarter) turns 16 trits per stage into two 16-byte chunks
 //
 // Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all
 // roles leave their loops, the CTA frees TMEM and the kernel records DST_ERR_TIMEOUT in the status word.
@@ -32,18 +43,33 @@
 namespace dst {
 namespace {
 
-constexpr int PF_THREADS = 448;
+constexpr int PF_THREADS = 704;            // 6 control/epilogue warps + 16 dequant warps
+constexpr int PF_DQ_WARPS = 16;
 constexpr int PF_TN = 256;            // token rows per tile (TMEM columns per accumulator buffer)
 constexpr int PF_BOX = 32;            // token rows per TMA box
 constexpr int PF_A_BYTES = 128 * 128; // one A stage: 128 weight rows x 64 fp16
 constexpr int PF_B_BYTES = PF_TN * 128;
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_B_BYTES;
 constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
 constexpr int PF_SLAB = 8192;                   // one (row tile, superblock) slab of packed weights
 constexpr int PF_SMEM_MAX = 232448;             // 227 KB of dynamic shared memory per CTA
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 __device__ int g_device_status = 0;
+
+// Optional per-role cycle accounting (build with -DDST_ROLE_TIMERS): where each warp role of the tcgen05
+// kernel spends its time, summed over CTAs. Read with dst_role_timers(). Off in the shipped library.
+#ifdef DST_ROLE_TIMERS
+__device__ unsigned long long g_role_timers[64];
+#define RT_DECL(...) long long __VA_ARGS__
+#define RT_NOW() clock64()
+#define RT_ADD(slot, v) atomicAdd(&g_role_timers[slot], (unsigned long long)(v))
+#define RT_WAIT(acc, call) [&]() { const long long t0__ = clock64(); const bool r__ = (call); acc += clock64() - t0__; return r__; }()
+#else
+#define RT_DECL(...)
+#define RT_NOW() 0
+#define RT_ADD(slot, v)
+#define RT_WAIT(acc, call) (call)
+#endif
 
 struct PrefillParams {
   const uint8_t* tiled[DST_MAX_TERMS];
@@ -75,11 +101,15 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
                : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
-// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed.
+// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed. BACKOFF sleeps between
+// polls: for roles that wait long (epilogue, producer), so their polling does not take issue slots from the
+// dequant warps.
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
+    if (BACKOFF) __nanosleep(40);
     if (mbar_test(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
@@ -109,6 +139,38 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void umma_f16_2cta(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_2cta(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_2cta(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
+}
+
 #define TMEM_LD_32(v, taddr)                                                                                              \
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                  \
                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"   \
@@ -130,7 +192,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 // same sequence with its own copy of this state.
 struct TileWalker {
   const int64_t* offsets;
-  int E, T, NT;
+  int E, T, NT;      // NT: tiles along the weight rows (pairs of 128-row tiles when CTA pairs are used)
+  int row_round;     // token rows per tile are a multiple of this (16, or 32 for CTA pairs)
   int e = -1, mt_count = 0, mt_rows = 0;
   long long before = 0;
   int64_t ra = 0, rb = 0;
@@ -140,9 +203,9 @@ struct TileWalker {
       if (++e >= E) return false;
       row_range(offsets, e, T, ra, rb);
       mt_count = (int)((rb - ra + PF_TN - 1) / PF_TN);
-      // an expert with more rows than one tile holds is split evenly (multiples of 16 rows), so no
+      // an expert with more rows than one tile holds is split evenly (whole multiples of row_round), so no
       // tile repeats the dequantisation of the weights for a handful of left-over rows
-      mt_rows = mt_count > 0 ? (int)((((rb - ra + mt_count - 1) / mt_count) + 15) & ~15LL) : 0;
+      mt_rows = mt_count > 0 ? (int)((((rb - ra + mt_count - 1) / mt_count) + row_round - 1) / row_round * row_round) : 0;
     }
     const long long local = t - before;
     const int mt = (int)(local / NT);
@@ -183,44 +246,41 @@ __device__ __forceinline__ void tq2_word(uint32_t w, __half2 s2, __half2* acc /*
   for (int j = 0; j < 8; ++j) acc[j] = FIRST ? __hmul2(t[j], s2) : __hfma2(t[j], s2, acc[j]);
 }
 
-// TQ1: the thread needs the 32 trits [tau, tau + 32) of its row-superblock, tau = 32 q. They start at
-// trit `o` of byte b0 = tau / 5. Bytes go through a shared-memory table of unscaled fp16 trits in two
-// alignments (first trit in the low or the high half of a pair), so pairs never need re-alignment:
-// entry even = (v0,v1)(v2,v3)(v4,0), entry odd = (0,v0)(v1,v2)(v3,v4). Byte i lands at pair index
-// floor((5 i - o) / 2); neighbouring bytes share one pair, merged with OR.
+// TQ1: the thread needs the 16 trits [tau, tau + 16) of its row-superblock, tau = 16 q. They start at
+// trit `o` of byte b0 = tau / 5 and always lie inside 4 consecutive bytes. Bytes go through a shared-memory
+// table of unscaled fp16 trits in two alignments (first trit in the low or the high half of a pair), so
+// pairs never need re-alignment: entry even = (v0,v1)(v2,v3)(v4,0), entry odd = (0,v0)(v1,v2)(v3,v4).
+// Byte i lands at pair index floor((5 i - o) / 2); neighbouring bytes share one pair, merged with OR.
 template <int O, bool FIRST>
-__device__ __forceinline__ void tq1_decode(uint32_t lo, uint32_t hi, uint32_t lut_addr, __half2 s2, __half2* acc /* 16 */) {
-  uint32_t out[16];
+__device__ __forceinline__ void tq1_decode(uint32_t win, uint32_t lut_addr, __half2 s2, __half2* acc /* 8 */) {
+  uint32_t out[8];
 #pragma unroll
-  for (int h = 0; h < 16; ++h) out[h] = 0u;
-  constexpr int NB = (O + 32 + 4) / 5;  // bytes touched: 7, or 8 when O == 4
+  for (int h = 0; h < 8; ++h) out[h] = 0u;
 #pragma unroll
-  for (int i = 0; i < NB; ++i) {
-    const uint32_t src = i < 4 ? lo : hi;
-    const int sh = 8 * (i & 3) - 7;
-    const uint32_t idx = (sh >= 0 ? (src >> (sh >= 0 ? sh : 0)) : (src << 7)) & 0x7F80u;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t idx = (i == 0 ? (win << 7) : (win >> (8 * i - 7))) & 0x7F80u;
     const int p = 5 * i - O;                       // position of the byte's first trit
     const int odd = ((p % 2) + 2) % 2;             // first trit lands in the high half
     const int h0 = (p - odd) / 2;                  // floor(p / 2), exact for negative p too
     uint32_t t0, t1, t2, t3;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t0), "=r"(t1), "=r"(t2), "=r"(t3) : "r"(lut_addr + idx + odd * 32768u));
     (void)t3;
-    if (h0 >= 0 && h0 < 16) out[h0] |= t0;
-    if (h0 + 1 >= 0 && h0 + 1 < 16) out[h0 + 1] |= t1;
-    if (h0 + 2 >= 0 && h0 + 2 < 16) out[h0 + 2] |= t2;
+    if (h0 >= 0 && h0 < 8) out[h0] |= t0;
+    if (h0 + 1 >= 0 && h0 + 1 < 8) out[h0 + 1] |= t1;
+    if (h0 + 2 >= 0 && h0 + 2 < 8) out[h0 + 2] |= t2;
   }
 #pragma unroll
-  for (int h = 0; h < 16; ++h) acc[h] = FIRST ? __hmul2(bits_h2(out[h]), s2) : __hfma2(bits_h2(out[h]), s2, acc[h]);
+  for (int h = 0; h < 8; ++h) acc[h] = FIRST ? __hmul2(bits_h2(out[h]), s2) : __hfma2(bits_h2(out[h]), s2, acc[h]);
 }
 
 template <bool FIRST>
-__device__ __forceinline__ void tq1_dispatch(int o, uint32_t lo, uint32_t hi, uint32_t lut_addr, __half2 s2, __half2* acc) {
+__device__ __forceinline__ void tq1_dispatch(int o, uint32_t win, uint32_t lut_addr, __half2 s2, __half2* acc) {
   switch (o) {
-    case 0: tq1_decode<0, FIRST>(lo, hi, lut_addr, s2, acc); break;
-    case 1: tq1_decode<1, FIRST>(lo, hi, lut_addr, s2, acc); break;
-    case 2: tq1_decode<2, FIRST>(lo, hi, lut_addr, s2, acc); break;
-    case 3: tq1_decode<3, FIRST>(lo, hi, lut_addr, s2, acc); break;
-    default: tq1_decode<4, FIRST>(lo, hi, lut_addr, s2, acc); break;
+    case 0: tq1_decode<0, FIRST>(win, lut_addr, s2, acc); break;
+    case 1: tq1_decode<1, FIRST>(win, lut_addr, s2, acc); break;
+    case 2: tq1_decode<2, FIRST>(win, lut_addr, s2, acc); break;
+    case 3: tq1_decode<3, FIRST>(win, lut_addr, s2, acc); break;
+    default: tq1_decode<4, FIRST>(win, lut_addr, s2, acc); break;
   }
 }
 
@@ -237,37 +297,46 @@ __device__ __forceinline__ __half2 pick_scale(const uint4& sc, int g) {
   return bits_h2(h | (h << 16));
 }
 
-// Shared memory map (dynamic, 1024-byte aligned):
-//   [0, nstage * 48 KB)            stage ring: A tile 16 KB (128 rows x 64 fp16) + B tile 32 KB (256 rows x 64 fp16)
+// Shared memory map (dynamic, 1024-byte aligned), per CTA:
+//   [0, nstage * stage_bytes)      stage ring: A tile 16 KB (128 rows x 64 fp16) + B tile (256 token rows x 64 fp16 =
+//                                  32 KB for one CTA, 128 rows = 16 KB for each CTA of a pair)
 //   then 2 * n_terms * 8 KB        packed-weight slabs: slot-major, one 8 KB slab per stacked term
 //   then 64 KB (TQ1 only)          table of unscaled fp16 trits
-template <int FMT>
+template <int FMT, int CG, int TERMS>
 __global__ void __launch_bounds__(PF_THREADS, 1)
-prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) {
+prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant__ CUtensorMap xmap128, const PrefillParams p) {
   constexpr int SPB = FMT == 2 ? 4 : 5;  // 64-trit stages per 64-byte superblock
-  constexpr int MAX_STAGE = 4;
+  constexpr int MAX_STAGE = 6;
+  constexpr int B_BYTES = PF_B_BYTES / CG;
+  constexpr int STAGE_BYTES = PF_A_BYTES + B_BYTES;
+  constexpr int ROUND = CG == 2 ? 32 : 16;  // token rows per tile are padded to this for the MMA N
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int NSTAGE = p.nstage;
-  uint8_t* slabs = smem + NSTAGE * PF_STAGE_BYTES;
+  uint8_t* slabs = smem + NSTAGE * STAGE_BYTES;
   uint8_t* lut = slabs + 2 * p.n_terms * PF_SLAB;  // TQ1 only
-  __shared__ uint64_t bar_full[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[2], bar_tempty[2], bar_pfull[2], bar_pempty[2];
+  __shared__ uint64_t bar_full[MAX_STAGE], bar_afull[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[2], bar_tempty[2], bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;  // 0 = the pair's leader
+  const bool leader = rank == 0;
   if (tid == 0) {
     abort_s = 0;
     for (int s = 0; s < MAX_STAGE; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1 + 8);  // TMA producer's expect_tx arrive + one arrive per dequant warp
-      mbar_init(smem_u32(&bar_empty[s]), 1);     // tcgen05.commit
+      // stage full (leader): the TMA producer's expect_tx arrive + one arrive per local dequant warp
+      // + one relayed arrive for the peer's A tile
+      mbar_init(smem_u32(&bar_full[s]), 1 + PF_DQ_WARPS + (CG - 1));
+      mbar_init(smem_u32(&bar_afull[s]), PF_DQ_WARPS);  // non-leader CTA of a pair: its own A tile is written
+      mbar_init(smem_u32(&bar_empty[s]), 1);  // tcgen05.commit (multicast to both CTAs of a pair)
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bar_tfull[a]), 1);   // tcgen05.commit after the tile's last MMA
-      mbar_init(smem_u32(&bar_tempty[a]), 4);  // one arrive per epilogue warp
-      mbar_init(smem_u32(&bar_pfull[a]), 1);   // bulk-copy producer's expect_tx arrive
-      mbar_init(smem_u32(&bar_pempty[a]), 8);  // one arrive per dequant warp
+      mbar_init(smem_u32(&bar_tfull[a]), 1);        // tcgen05.commit after the tile's last MMA
+      mbar_init(smem_u32(&bar_tempty[a]), 4 * CG);  // leader: one arrive per epilogue warp of every CTA of the pair
+      mbar_init(smem_u32(&bar_pfull[a]), 1);        // bulk-copy producer's expect_tx arrive
+      mbar_init(smem_u32(&bar_pempty[a]), PF_DQ_WARPS);  // one arrive per dequant warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -291,11 +360,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
   }
   __syncwarp();
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    if (CG == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // the peer's barriers are initialised before anyone arrives on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_s;
 
@@ -303,92 +378,132 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
   walk.offsets = p.offsets;
   walk.E = p.E;
   walk.T = p.T;
-  walk.NT = p.NT;
-  int e, nt, row0, rows;
+  walk.NT = p.NT / CG;
+  walk.row_round = ROUND;
+  int e, ntp, row0, rows;
   const int nsb = (p.kstages + SPB - 1) / SPB;  // superblocks a tile touches
+  const long long t_first = blockIdx.x / CG, t_step = gridDim.x / CG;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer: TMA for B, bulk copies for packed slabs
     if (lane == 0) {
       uint32_t it = 0, pit = 0;  // stage counter, packed-slab counter (both run across tiles)
       bool ok = true;
+      RT_DECL(w_pempty = 0, w_empty = 0, t_begin = RT_NOW());
       // One slab (all stacked terms of one superblock) is always requested one superblock ahead of the
       // stage loads, so the dequant warps find it in shared memory when they get there.
       TileWalker ahead = walk;
-      int ae, ant, arow0, arows, asb = 0;
-      long long at = blockIdx.x;
-      bool have = ahead.seek(at, ae, ant, arow0, arows);
+      int ae, antp, arow0, arows, asb = 0;
+      long long at = t_first;
+      bool have = ahead.seek(at, ae, antp, arow0, arows);
       auto issue_slab = [&]() -> bool {
-        while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
+        while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
         if (!have) return true;
         const int slot = pit & 1;
-        if (!mbar_wait(smem_u32(&bar_pempty[slot]), ((pit >> 1) & 1u) ^ 1u, abort_flag)) return false;
+        if (!RT_WAIT(w_pempty, mbar_wait<true>(smem_u32(&bar_pempty[slot]), ((pit >> 1) & 1u) ^ 1u, abort_flag))) return false;
         const uint32_t full = smem_u32(&bar_pfull[slot]);
         mbar_arrive_expect_tx(full, (uint32_t)p.n_terms * PF_SLAB);
-        const int64_t off = (((int64_t)ae * p.NT + ant) * p.S + asb) * PF_SLAB;
+        const int64_t off = (((int64_t)ae * p.NT + antp * CG + rank) * p.S + asb) * PF_SLAB;
         for (int i = 0; i < p.n_terms; ++i)
           bulk_load(smem_u32(slabs + (slot * p.n_terms + i) * PF_SLAB), p.tiled[i] + off, PF_SLAB, full);
         ++pit;
         if (++asb >= nsb) {
           asb = 0;
-          at += gridDim.x;
-          have = ahead.seek(at, ae, ant, arow0, arows);
+          at += t_step;
+          have = ahead.seek(at, ae, antp, arow0, arows);
         }
         return true;
       };
       ok = issue_slab();
-      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
         if (rows <= 0) continue;
-        const int boxes = (rows + PF_BOX - 1) / PF_BOX;
+        const int n_eff = (rows + ROUND - 1) / ROUND * ROUND;
+        const int my_rows = n_eff / CG;                    // token rows this CTA stages
+        const int my_row0 = row0 + (int)rank * my_rows;
+        const bool big = my_rows == 128;                   // one 128-row box instead of 32-row boxes
+        const int boxes = big ? 1 : (my_rows + PF_BOX - 1) / PF_BOX;
+        const uint32_t bytes = big ? 128u * 128u : (uint32_t)boxes * PF_BOX * 128u;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
           if (ks % SPB == 0 && !issue_slab()) { ok = false; break; }
           const int s = it % NSTAGE;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!RT_WAIT(w_empty, mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_arrive_expect_tx(full, (uint32_t)boxes * PF_BOX * 128u);
-          const uint32_t dst = smem_u32(smem + s * PF_STAGE_BYTES + PF_A_BYTES);
-          for (int b = 0; b < boxes; ++b) tma_load_2d(dst + b * PF_BOX * 128, &xmap, ks * 64, row0 + b * PF_BOX, full);
+          const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + PF_A_BYTES);
+          if (CG == 2) {
+            const uint32_t lfull = mapa(full, 0);
+            if (leader) mbar_arrive_expect_tx(full, bytes * 2u);  // both CTAs stage the same number of bytes
+            if (big) tma_load_2d_2cta(dst, &xmap128, ks * 64, my_row0, lfull);
+            else for (int b = 0; b < boxes; ++b) tma_load_2d_2cta(dst + b * PF_BOX * 128, &xmap32, ks * 64, my_row0 + b * PF_BOX, lfull);
+          } else {
+            mbar_arrive_expect_tx(full, bytes);
+            if (big) tma_load_2d(dst, &xmap128, ks * 64, my_row0, full);
+            else for (int b = 0; b < boxes; ++b) tma_load_2d(dst + b * PF_BOX * 128, &xmap32, ks * 64, my_row0 + b * PF_BOX, full);
+          }
         }
       }
+      RT_ADD(0, RT_NOW() - t_begin); RT_ADD(1, w_pempty); RT_ADD(2, w_empty); RT_ADD(3, it); RT_ADD(4, 1);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (the leader CTA of a pair only)
+    if (lane == 0 && leader) {
       uint32_t it = 0, tile = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+      RT_DECL(w_tempty = 0, w_full = 0, t_begin = RT_NOW());
+      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
         if (rows <= 0) continue;
         const uint32_t a = tile & 1u;
-        if (!mbar_wait(smem_u32(&bar_tempty[a]), ((tile >> 1) & 1u) ^ 1u, abort_flag)) break;
+        if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[a]), ((tile >> 1) & 1u) ^ 1u, abort_flag))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t n_eff = (uint32_t)((rows + 15) & ~15);
+        const uint32_t n_eff = (uint32_t)((rows + ROUND - 1) / ROUND * ROUND);
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-        const uint32_t idesc = (1u << 4) | ((n_eff >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | ((n_eff >> 3) << 17) | (((128u * CG) >> 4) << 24);
         const uint32_t d_tmem = tmem + a * PF_TN;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
           const int s = it % NSTAGE;
-          if (!mbar_wait(smem_u32(&bar_full[s]), (it / NSTAGE) & 1u, abort_flag)) { ok = false; break; }
+          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), (it / NSTAGE) & 1u, abort_flag))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = smem_u32(smem + s * PF_STAGE_BYTES), sb = sa + PF_A_BYTES;
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + PF_A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs have read it
+          for (int kk = 0; kk < 4; ++kk) {
+            if (CG == 2) umma_f16_2cta(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          }
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if (CG == 2) umma_commit_2cta(smem_u32(&bar_empty[s]));
+          else umma_commit(smem_u32(&bar_empty[s]));
         }
-        if (ok) umma_commit(smem_u32(&bar_tfull[a]));
+        if (ok) {
+          if (CG == 2) umma_commit_2cta(smem_u32(&bar_tfull[a]));
+          else umma_commit(smem_u32(&bar_tfull[a]));
+        }
         ++tile;
+      }
+      RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, it); RT_ADD(12, 1); RT_ADD(13, tile);
+    } else if (CG == 2 && lane == 0) {
+      // non-leader CTA of a pair: when this CTA's dequant warps have written their A tile of a stage, tell the
+      // leader's stage-full barrier (one cluster-scope arrive per stage instead of one per dequant warp)
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
+        if (rows <= 0) continue;
+        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait(smem_u32(&bar_afull[s]), (it / NSTAGE) & 1u, abort_flag)) { ok = false; break; }
+          mbar_arrive_cluster(mapa(smem_u32(&bar_full[s]), 0));
+        }
       }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tile = 0;
-    for (long long t = blockIdx.x; walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+    RT_DECL(w_tfull = 0, t_begin = RT_NOW());
+    for (long long t = t_first; walk.seek(t, e, ntp, row0, rows); t += t_step) {
       if (rows <= 0) continue;
       const uint32_t a = tile & 1u;
-      if (!mbar_wait(smem_u32(&bar_tfull[a]), (tile >> 1) & 1u, abort_flag)) break;
+      if (!RT_WAIT(w_tfull, mbar_wait<true>(smem_u32(&bar_tfull[a]), (tile >> 1) & 1u, abort_flag))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int n = nt * 128 + q * 32 + lane;
+      const int n = (ntp * CG + (int)rank) * 128 + q * 32 + lane;
       const bool n_ok = n < p.N;
       const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + a * PF_TN;
       const int n_eff = (rows + 15) & ~15;
@@ -418,29 +533,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[a]));
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[a]), 0));
+        else mbar_arrive(smem_u32(&bar_tempty[a]));
+      }
       ++tile;
     }
+    if (warp == 2 && lane == 0) { RT_ADD(16, RT_NOW() - t_begin); RT_ADD(17, w_tfull); RT_ADD(18, 1); }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
     const int td = tid - 192;
-    const int r = td & 127, hh = td >> 7;
+    const int r = td & 127, q4 = td >> 7;  // row of the tile, quarter (16 trits) of the 64-trit stage
     const int swz = (r >> 1) & 3;  // 16-byte chunk swizzle of the tiled layout
     const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
     const bool vec_scales = (p.G & 7) == 0;  // rows of 8 k scales are 16-byte aligned
     uint32_t it = 0, pit = 0;
     bool ok = true;
+    RT_DECL(w_pfull = 0, w_dempty = 0, w_tail = 0, t_begin = RT_NOW());
     // scales of the row for 8 groups (16 stages) at a time, fetched one block ahead (also across tiles)
-    uint4 sc_next[DST_MAX_TERMS];
+    uint4 sc_next[TERMS];
     TileWalker ahead = walk;
-    int ae, ant, arow0, arows;
-    long long at = blockIdx.x;
-    bool have = ahead.seek(at, ae, ant, arow0, arows);
-    while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
+    int ae, antp, arow0, arows;
+    long long at = t_first;
+    bool have = ahead.seek(at, ae, antp, arow0, arows);
+    while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
     auto load_scales = [&](int ee, int nn, int g0, uint4* dst) {
       const bool n_ok = nn < p.N;
 #pragma unroll
-      for (int i = 0; i < DST_MAX_TERMS; ++i) {
+      for (int i = 0; i < TERMS; ++i) {
         if (i < p.n_terms) {
           if (!n_ok || g0 >= p.G) {
             dst[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -456,60 +576,55 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
         }
       }
     };
-    if (have) load_scales(ae, ant * 128 + r, 0, sc_next);
-    for (long long t = blockIdx.x; ok && walk.seek(t, e, nt, row0, rows); t += gridDim.x) {
+    if (have) load_scales(ae, (antp * CG + (int)rank) * 128 + r, 0, sc_next);
+    for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
       if (rows <= 0) continue;
+      const int nt = ntp * CG + (int)rank;
       // the tile after this one (for the scale prefetch at the end of this tile)
-      at = t + gridDim.x;
-      have = ahead.seek(at, ae, ant, arow0, arows);
-      while (have && arows <= 0) { at += gridDim.x; have = ahead.seek(at, ae, ant, arow0, arows); }
-      uint4 sc[DST_MAX_TERMS];
+      at = t + t_step;
+      have = ahead.seek(at, ae, antp, arow0, arows);
+      while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
+      uint4 sc[TERMS];
       for (int ks = 0; ks < p.kstages; ++ks, ++it) {
         const int s = it % NSTAGE;
         if ((ks & 15) == 0) {
 #pragma unroll
-          for (int i = 0; i < DST_MAX_TERMS; ++i) sc[i] = sc_next[i];
+          for (int i = 0; i < TERMS; ++i) sc[i] = sc_next[i];
           if (ks + 16 < p.kstages) load_scales(e, nt * 128 + r, (ks + 16) >> 1, sc_next);
-          else if (have) load_scales(ae, ant * 128 + r, 0, sc_next);
+          else if (have) load_scales(ae, (antp * CG + (int)rank) * 128 + r, 0, sc_next);
         }
         const int sbk = ks % SPB;
         const uint32_t slot = pit & 1u;
-        if (sbk == 0 && !mbar_wait(smem_u32(&bar_pfull[slot]), (pit >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (sbk == 0 && !RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), (pit >> 1) & 1u, abort_flag))) { ok = false; break; }
         const uint8_t* slab = slabs + (size_t)slot * p.n_terms * PF_SLAB + r * 64;
-        __half2 acc[16];
+        __half2 acc[8];
         const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
         if (FMT == 2) {
-          const int boff = ((sbk ^ swz) << 4) + hh * 8;
+          const int boff = ((sbk ^ swz) << 4) + q4 * 4;
 #pragma unroll
-          for (int i = 0; i < DST_MAX_TERMS; ++i) {
+          for (int i = 0; i < TERMS; ++i) {
             if (i < p.n_terms) {
-              const uint2 w = *reinterpret_cast<const uint2*>(slab + i * PF_SLAB + boff);
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB + boff);
               const __half2 s2 = pick_scale(sc[i], g);
-              if (i == 0) {
-                tq2_word<true>(w.x, s2, acc);
-                tq2_word<true>(w.y, s2, acc + 8);
-              } else {
-                tq2_word<false>(w.x, s2, acc);
-                tq2_word<false>(w.y, s2, acc + 8);
-              }
+              if (i == 0) tq2_word<true>(w, s2, acc);
+              else tq2_word<false>(w, s2, acc);
             }
           }
         } else {
-          const int qq = sbk * 2 + hh;  // 32-trit slot 0..9 inside the 320-trit superblock
-          const int tau = qq * 32, b0 = tau / 5, o = tau - b0 * 5;
+          const int qq = sbk * 4 + q4;  // 16-trit slot 0..19 inside the 320-trit superblock
+          const int tau = qq * 16, b0 = tau / 5, o = tau - b0 * 5;
           const int wi = b0 >> 2, sh = (b0 & 3) * 8;
 #pragma unroll
-          for (int i = 0; i < DST_MAX_TERMS; ++i) {
+          for (int i = 0; i < TERMS; ++i) {
             if (i < p.n_terms) {
               const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
               // logical word w of the row sits in chunk (w >> 2) ^ swz
               const uint32_t w0 = wp[(((wi >> 2) ^ swz) << 2) | (wi & 3)];
               const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) >> 2) ^ swz) << 2) | ((wi + 1) & 3)] : 0u;
-              const uint32_t w2 = wi + 2 < 16 ? wp[((((wi + 2) >> 2) ^ swz) << 2) | ((wi + 2) & 3)] : 0u;
-              const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
+              const uint32_t win = __funnelshift_r(w0, w1, sh);  // bytes b0 .. b0 + 3 of the row-superblock
               const __half2 s2 = pick_scale(sc[i], g);
-              if (i == 0) tq1_dispatch<true>(o, lo, hi, lut_addr, s2, acc);
-              else tq1_dispatch<false>(o, lo, hi, lut_addr, s2, acc);
+              if (i == 0) tq1_dispatch<true>(o, win, lut_addr, s2, acc);
+              else tq1_dispatch<false>(o, win, lut_addr, s2, acc);
             }
           }
         }
@@ -518,19 +633,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
           if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
           ++pit;
         }
-        if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        uint8_t* arow = smem + s * PF_STAGE_BYTES + r * 128;
+        if (!RT_WAIT(w_dempty, mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
+        RT_DECL(t_tail = RT_NOW());
+        uint8_t* arow = smem + s * STAGE_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int chunk = hh * 4 + c;
+        for (int c = 0; c < 2; ++c) {
+          const int chunk = q4 * 2 + c;
           *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) =
               make_uint4(h2_bits(acc[4 * c]), h2_bits(acc[4 * c + 1]), h2_bits(acc[4 * c + 2]), h2_bits(acc[4 * c + 3]));
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+        if (lane == 0) mbar_arrive(smem_u32(CG == 2 && !leader ? &bar_afull[s] : &bar_full[s]));
+#ifdef DST_ROLE_TIMERS
+        w_tail += RT_NOW() - t_tail;
+#endif
       }
     }
+    if (warp == 6 && lane == 0) { RT_ADD(24, RT_NOW() - t_begin); RT_ADD(25, w_pfull); RT_ADD(26, w_dempty); RT_ADD(27, it); RT_ADD(28, 1); RT_ADD(29, w_tail); }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -541,9 +661,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const PrefillParams p) 
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // neither CTA leaves while its peer may still read its shared memory or signal it
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
   }
   if (tid == 0 && abort_s) atomicExch(&g_device_status, DST_ERR_TIMEOUT);
 }
@@ -595,22 +717,49 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int FMT>
-int launch_fmt(const CUtensorMap& map, PrefillParams p, long long tiles_upper, cudaStream_t st) {
+template <int FMT, int CG, int TERMS>
+int launch_fmt(const CUtensorMap& map32, const CUtensorMap& map128, PrefillParams p, long long tiles_upper, cudaStream_t st) {
   // deepest stage ring the shared-memory budget allows next to the packed slabs and the TQ1 table
+  const size_t stage_bytes = PF_A_BYTES + PF_B_BYTES / CG;
   const size_t fixed = 1024 + (size_t)2 * p.n_terms * PF_SLAB + (FMT == 1 ? PF_LUT_BYTES : 0);
-  int nstage = (int)((PF_SMEM_MAX - fixed) / PF_STAGE_BYTES);
-  nstage = nstage > 4 ? 4 : nstage;
+  int nstage = (int)((PF_SMEM_MAX - fixed) / stage_bytes);
+  nstage = nstage > 6 ? 6 : nstage;
   if (nstage < 2) return DST_ERR_UNSUPPORTED;
   p.nstage = nstage;
-  const size_t smem = fixed + (size_t)nstage * PF_STAGE_BYTES;
-  DST_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const size_t smem = fixed + (size_t)nstage * stage_bytes;
+  auto kernel = prefill_kernel<FMT, CG, TERMS>;
+  DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   DST_CUDA_TRY(cudaGetDevice(&dev));
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int grid = (int)(tiles_upper < sms ? (tiles_upper < 1 ? 1 : tiles_upper) : sms);
-  prefill_kernel<FMT><<<grid, PF_THREADS, smem, st>>>(map, p);
-  DST_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(PF_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  int n_attr = 0;
+  long long units = tiles_upper / CG;  // tiles (CG = 1) or pair tiles (CG = 2) at most
+  if (units < 1) units = 1;
+  int groups = sms / CG;
+  if (CG == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    n_attr = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3((unsigned)sms / 2 * 2, 1, 1);
+    int max_clusters = 0;
+    DST_CUDA_TRY(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg));
+    if (max_clusters < 1) return DST_ERR_UNSUPPORTED;
+    groups = max_clusters < groups ? max_clusters : groups;
+  }
+  if (units < groups) groups = (int)units;
+  cfg.gridDim = dim3((unsigned)(groups * CG), 1, 1);
+  cfg.attrs = n_attr ? attr : nullptr;
+  cfg.numAttrs = n_attr;
+  DST_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map32, map128, p));
   return DST_OK;
 }
 
@@ -645,15 +794,18 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
     convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale, xh, rs);
   DST_CUDA_TRY(cudaGetLastError());
 
-  // 2. tensor map over the fp16 rows: [T, K], box 64 x 32, 128-byte swizzle, zero fill outside
-  CUtensorMap map;
+  // 2. tensor maps over the fp16 rows: [T, K], boxes of 64 x 32 and 64 x 128, 128-byte swizzle, zero fill outside
+  CUtensorMap map32, map128;
   const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.T};
   const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
-  const cuuint32_t box[2] = {64, PF_BOX};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult cr = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (cr != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  for (int which = 0; which < 2; ++which) {
+    const cuuint32_t box[2] = {64, which ? 128u : (cuuint32_t)PF_BOX};
+    const CUresult cr = encode_fn()(which ? &map128 : &map32, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  }
 
   PrefillParams p;
   for (int i = 0; i < DST_MAX_TERMS; ++i) {
@@ -675,10 +827,34 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.kstages = (int)(a.K / 64);
   const long long tiles_upper = ((long long)cdiv64(a.T, PF_TN) + a.E) * p.NT;
-  return a.fmt == DST_FMT_TQ2 ? launch_fmt<2>(map, p, tiles_upper, stream) : launch_fmt<1>(map, p, tiles_upper, stream);
+  // CTA pairs need an even number of 128-row weight tiles
+  const bool pairs = a.N % 256 == 0;
+#define DST_PF_LAUNCH(FMT_, CG_)                                                                          \
+  (a.terms.n == 1 ? launch_fmt<FMT_, CG_, 1>(map32, map128, p, tiles_upper, stream)                       \
+                  : a.terms.n == 2 ? launch_fmt<FMT_, CG_, 2>(map32, map128, p, tiles_upper, stream)      \
+                                   : launch_fmt<FMT_, CG_, 4>(map32, map128, p, tiles_upper, stream))
+  if (a.fmt == DST_FMT_TQ2) return pairs ? DST_PF_LAUNCH(2, 2) : DST_PF_LAUNCH(2, 1);
+  return pairs ? DST_PF_LAUNCH(1, 2) : DST_PF_LAUNCH(1, 1);
+#undef DST_PF_LAUNCH
 }
 
 }  // namespace dst
+
+#ifdef DST_ROLE_TIMERS
+// Profiling builds only: copies (and optionally clears) the 64 role-timer slots. Slots: 0-4 producer (total
+// cycles, wait packed-slot free, wait stage free, stages, threads), 8-13 MMA issuer (total, wait accumulator
+// free, wait stage full, stages, threads, tiles), 16-18 epilogue warp (total, wait accumulator full, threads),
+// 24-29 one dequant warp (total, wait packed slab, wait stage free, stages, threads, store+fence+arrive).
+extern "C" int dst_role_timers(unsigned long long* out, int reset) {
+  DST_CUDA_TRY(cudaDeviceSynchronize());
+  DST_CUDA_TRY(cudaMemcpyFromSymbol(out, dst::g_role_timers, sizeof(unsigned long long) * 64));
+  if (reset) {
+    unsigned long long z[64] = {0};
+    DST_CUDA_TRY(cudaMemcpyToSymbol(dst::g_role_timers, z, sizeof(z)));
+  }
+  return DST_OK;
+}
+#endif
 
 extern "C" int dst_check_device_status(dst_stream_t stream) {
   DST_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
