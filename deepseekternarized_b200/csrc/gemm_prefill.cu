@@ -6,13 +6,17 @@
 //
 // Mapping ("swap AB"): the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), up to 256
 // token rows are the MMA N dimension (TMEM columns), so tiles stay full when an expert has few rows.
-// Both operands are fp16, K-major, 128-byte swizzled, 64 K-elements per pipeline stage:
+// Both operands are fp16, 64 K-elements per pipeline stage:
 //   A (weights)      packed 8 KB slabs of the tiled layout (layout_kernels.cu) arrive by cp.async.bulk in a
-//                    two-slot ring; 8 dequant warps turn them into scale * trit, exact in fp16, and store
-//                    the tile in the canonical SWIZZLE_128B layout
-//   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA), 32-row boxes
-//   D (accumulator)  fp32 in TMEM, two buffers of 256 columns so the epilogue of one tile overlaps the
-//                    MMAs of the next
+//                    two-slot ring; 16 dequant warps turn them into scale * trit, exact in fp16, and write
+//                    them with tcgen05.st straight into TENSOR MEMORY (lane = weight row, one 32-bit column
+//                    = two consecutive K elements; 32 columns per stage, ring of 8 stages): the MMA takes A
+//                    from TMEM, so the dequantised tile never passes through shared memory
+//   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA) into K-major,
+//                    128-byte-swizzled shared-memory stages
+//   D (accumulator)  fp32 in TMEM columns 0..255; columns 256..511 are the A ring
+// Shared-memory bandwidth is what bounds this kernel when A goes through shared memory (measured: the MMA
+// issuer stalled ~1100 cycles per 512-cycle stage); with A in TMEM only B is written and read there.
 // bf16 activations are converted once to fp16 with a power-of-two factor per row (exact for every
 // element within 2^-22 of the row's absolute maximum); the factor comes back through row_scale.
 // tcgen05 kind::f16 refuses an fp16 A with a bf16 B (illegal instruction), hence the conversion.
@@ -30,7 +34,10 @@
 //   warp 0      TMA producer for B and bulk copies of packed slabs
 //   warp 1      MMA issuer, owns the TMEM allocation (in the non-leader CTA of a pair: relays "my A tile is ready")
 //   warps 2-5   epilogue (TMEM -> registers -> global)
-//   warps 6-21  dequant producers for A: thread (row, quarter) turns 16 trits per stage into two 16-byte chunks
+//   warps 6-21  dequant producers for A, in four groups of four warps: group g owns the stages with index = g
+//               (mod 4), so four stages are dequantised at once (each warp's instruction stream is a long
+//               dependent chain; one group per stage could not keep up with the MMAs); inside a group warp w
+//               owns the 32 weight rows of TMEM lane quarter w % 4, one thread per row per 64-trit stage
 //
 // Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all
 // roles leave their loops, the CTA frees TMEM and the kernel records DST_ERR_TIMEOUT in the status word.
@@ -46,8 +53,8 @@ namespace {
 constexpr int PF_THREADS = 704;            // 6 control/epilogue warps + 16 dequant warps
 constexpr int PF_DQ_WARPS = 16;
 constexpr int PF_TN = 256;            // token rows per tile (TMEM columns per accumulator buffer)
-constexpr int PF_BOX = 32;            // token rows per TMA box
-constexpr int PF_A_BYTES = 128 * 128; // one A stage: 128 weight rows x 64 fp16
+constexpr int PF_A_COLS = 32;         // TMEM columns of one A stage: 64 fp16 per weight row
+constexpr int PF_A_RING = 8;          // A stages in TMEM (columns 256..511)
 constexpr int PF_B_BYTES = PF_TN * 128;
 constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
 constexpr int PF_SLAB = 8192;                   // one (row tile, superblock) slab of packed weights
@@ -71,6 +78,11 @@ __device__ unsigned long long g_role_timers[64];
 #define RT_WAIT(acc, call) (call)
 #endif
 
+// One tensor map per TMA box height (16, 32, ... 256 token rows), so a stage is always one TMA instruction.
+struct TmaMaps {
+  CUtensorMap m[16];
+};
+
 struct PrefillParams {
   const uint8_t* tiled[DST_MAX_TERMS];
   const __half* scale[DST_MAX_TERMS];
@@ -80,7 +92,7 @@ struct PrefillParams {
   void* out;
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S, kstages;
-  int nstage;  // depth of the A/B stage ring (2..4), chosen by the host from the shared-memory budget
+  int nstage_log2;  // log2 of the stage ring depth (2, 4 or 8 stages), chosen by the host from the shared-memory budget
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -127,9 +139,19 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
          ((uint64_t)2 << 61);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+// A operand from tensor memory (lane = row, 32-bit column = 2 K elements), B from shared memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_2cta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 8 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -155,10 +177,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void umma_f16_2cta(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
 __device__ __forceinline__ void umma_commit_2cta(uint32_t bar) {
@@ -298,24 +316,25 @@ __device__ __forceinline__ __half2 pick_scale(const uint4& sc, int g) {
 }
 
 // Shared memory map (dynamic, 1024-byte aligned), per CTA:
-//   [0, nstage * stage_bytes)      stage ring: A tile 16 KB (128 rows x 64 fp16) + B tile (256 token rows x 64 fp16 =
-//                                  32 KB for one CTA, 128 rows = 16 KB for each CTA of a pair)
+//   [0, nstage * stage_bytes)      B stage ring: 256 token rows x 64 fp16 = 32 KB for one CTA, 128 rows = 16 KB for
+//                                  each CTA of a pair; nstage <= 8 and stage s pairs with A ring slot s in TMEM
 //   then 2 * n_terms * 8 KB        packed-weight slabs: slot-major, one 8 KB slab per stacked term
 //   then 64 KB (TQ1 only)          table of unscaled fp16 trits
 template <int FMT, int CG, int TERMS>
 __global__ void __launch_bounds__(PF_THREADS, 1)
-prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant__ CUtensorMap xmap128, const PrefillParams p) {
+prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
   constexpr int SPB = FMT == 2 ? 4 : 5;  // 64-trit stages per 64-byte superblock
-  constexpr int MAX_STAGE = 6;
+  constexpr int MAX_STAGE = PF_A_RING;
   constexpr int B_BYTES = PF_B_BYTES / CG;
-  constexpr int STAGE_BYTES = PF_A_BYTES + B_BYTES;
+  constexpr int STAGE_BYTES = B_BYTES;
   constexpr int ROUND = CG == 2 ? 32 : 16;  // token rows per tile are padded to this for the MMA N
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int NSTAGE = p.nstage;
+  const int NSTAGE = 1 << p.nstage_log2;
+  const uint32_t smask = (uint32_t)NSTAGE - 1u, sshift = (uint32_t)p.nstage_log2;
   uint8_t* slabs = smem + NSTAGE * STAGE_BYTES;
   uint8_t* lut = slabs + 2 * p.n_terms * PF_SLAB;  // TQ1 only
-  __shared__ uint64_t bar_full[MAX_STAGE], bar_afull[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[2], bar_tempty[2], bar_pfull[2], bar_pempty[2];
+  __shared__ uint64_t bar_full[MAX_STAGE], bar_afull[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[1], bar_tempty[1], bar_pfull[2], bar_pempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
@@ -326,15 +345,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
   if (tid == 0) {
     abort_s = 0;
     for (int s = 0; s < MAX_STAGE; ++s) {
-      // stage full (leader): the TMA producer's expect_tx arrive + one arrive per local dequant warp
+      // stage full (leader): the TMA producer's expect_tx arrive + one arrive per warp of the dequant group that owns the stage
       // + one relayed arrive for the peer's A tile
-      mbar_init(smem_u32(&bar_full[s]), 1 + PF_DQ_WARPS + (CG - 1));
-      mbar_init(smem_u32(&bar_afull[s]), PF_DQ_WARPS);  // non-leader CTA of a pair: its own A tile is written
+      mbar_init(smem_u32(&bar_full[s]), 1 + 4 + (CG - 1));
+      mbar_init(smem_u32(&bar_afull[s]), 4);  // non-leader CTA of a pair: its own A tile is written (4 warps per stage)
       mbar_init(smem_u32(&bar_empty[s]), 1);  // tcgen05.commit (multicast to both CTAs of a pair)
     }
+    mbar_init(smem_u32(&bar_tfull[0]), 1);        // tcgen05.commit after the tile's last MMA
+    mbar_init(smem_u32(&bar_tempty[0]), 4 * CG);  // leader: one arrive per epilogue warp of every CTA of the pair
     for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bar_tfull[a]), 1);        // tcgen05.commit after the tile's last MMA
-      mbar_init(smem_u32(&bar_tempty[a]), 4 * CG);  // leader: one arrive per epilogue warp of every CTA of the pair
       mbar_init(smem_u32(&bar_pfull[a]), 1);        // bulk-copy producer's expect_tx arrive
       mbar_init(smem_u32(&bar_pempty[a]), PF_DQ_WARPS);  // one arrive per dequant warp
     }
@@ -415,29 +434,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
         return true;
       };
       ok = issue_slab();
+      const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]), dst0 = smem_u32(smem);
+      const uint32_t lfull0 = CG == 2 ? mapa(full0, 0) : full0;  // the stage-full barriers of the pair's leader
       for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
         if (rows <= 0) continue;
         const int n_eff = (rows + ROUND - 1) / ROUND * ROUND;
-        const int my_rows = n_eff / CG;                    // token rows this CTA stages
+        const int my_rows = n_eff / CG;                    // token rows this CTA stages (a multiple of 16)
         const int my_row0 = row0 + (int)rank * my_rows;
-        const bool big = my_rows == 128;                   // one 128-row box instead of 32-row boxes
-        const int boxes = big ? 1 : (my_rows + PF_BOX - 1) / PF_BOX;
-        const uint32_t bytes = big ? 128u * 128u : (uint32_t)boxes * PF_BOX * 128u;
+        const CUtensorMap* map = &xmaps.m[my_rows / 16 - 1];
+        const uint32_t bytes = (uint32_t)my_rows * 128u;
+        int sbk = 0;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          if (ks % SPB == 0 && !issue_slab()) { ok = false; break; }
-          const int s = it % NSTAGE;
-          if (!RT_WAIT(w_empty, mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
-          const uint32_t full = smem_u32(&bar_full[s]);
-          const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + PF_A_BYTES);
+          if (sbk == 0 && !issue_slab()) { ok = false; break; }
+          if (++sbk == SPB) sbk = 0;
+          const uint32_t s = it & smask;
+          if (!RT_WAIT(w_empty, mbar_wait(empty0 + s * 8, ((it >> sshift) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
           if (CG == 2) {
-            const uint32_t lfull = mapa(full, 0);
-            if (leader) mbar_arrive_expect_tx(full, bytes * 2u);  // both CTAs stage the same number of bytes
-            if (big) tma_load_2d_2cta(dst, &xmap128, ks * 64, my_row0, lfull);
-            else for (int b = 0; b < boxes; ++b) tma_load_2d_2cta(dst + b * PF_BOX * 128, &xmap32, ks * 64, my_row0 + b * PF_BOX, lfull);
+            if (leader) mbar_arrive_expect_tx(full0 + s * 8, bytes * 2u);  // both CTAs stage the same number of bytes
+            tma_load_2d_2cta(dst0 + s * STAGE_BYTES, map, ks * 64, my_row0, lfull0 + s * 8);
           } else {
-            mbar_arrive_expect_tx(full, bytes);
-            if (big) tma_load_2d(dst, &xmap128, ks * 64, my_row0, full);
-            else for (int b = 0; b < boxes; ++b) tma_load_2d(dst + b * PF_BOX * 128, &xmap32, ks * 64, my_row0 + b * PF_BOX, full);
+            mbar_arrive_expect_tx(full0 + s * 8, bytes);
+            tma_load_2d(dst0 + s * STAGE_BYTES, map, ks * 64, my_row0, full0 + s * 8);
           }
         }
       }
@@ -448,33 +465,39 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
     if (lane == 0 && leader) {
       uint32_t it = 0, tile = 0;
       bool ok = true;
+      const uint64_t b_desc0 = umma_desc(smem_u32(smem));
+      const uint32_t b_desc_lo = (uint32_t)b_desc0, b_desc_hi = (uint32_t)(b_desc0 >> 32);
       RT_DECL(w_tempty = 0, w_full = 0, t_begin = RT_NOW());
       for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
         if (rows <= 0) continue;
-        const uint32_t a = tile & 1u;
-        if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[a]), ((tile >> 1) & 1u) ^ 1u, abort_flag))) break;
+        // one accumulator: the epilogue of the previous tile must have drained it
+        if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t n_eff = (uint32_t)((rows + ROUND - 1) / ROUND * ROUND);
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
         const uint32_t idesc = (1u << 4) | ((n_eff >> 3) << 17) | (((128u * CG) >> 4) << 24);
-        const uint32_t d_tmem = tmem + a * PF_TN;
+        const uint32_t d_tmem = tmem;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          const int s = it % NSTAGE;
-          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), (it / NSTAGE) & 1u, abort_flag))) { ok = false; break; }
+          const int s = (int)(it & smask);
+          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), (it >> sshift) & 1u, abort_flag))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + PF_A_BYTES;
+          const uint32_t a_tmem = tmem + PF_TN + s * PF_A_COLS;  // this stage's slot of the A ring
+          // only the start-address field of the B descriptor changes with the stage and the K step
+          const uint32_t b_lo = b_desc_lo + (uint32_t)s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            if (CG == 2) umma_f16_2cta(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-            else umma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            uint64_t db;
+            asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2), "r"(b_desc_hi));
+            if (CG == 2) umma_f16_ts_2cta(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            else umma_f16_ts(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
           }
           // frees the stage (in both CTAs of a pair) when these MMAs have read it
           if (CG == 2) umma_commit_2cta(smem_u32(&bar_empty[s]));
           else umma_commit(smem_u32(&bar_empty[s]));
         }
         if (ok) {
-          if (CG == 2) umma_commit_2cta(smem_u32(&bar_tfull[a]));
-          else umma_commit(smem_u32(&bar_tfull[a]));
+          if (CG == 2) umma_commit_2cta(smem_u32(&bar_tfull[0]));
+          else umma_commit(smem_u32(&bar_tfull[0]));
         }
         ++tile;
       }
@@ -487,8 +510,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
       for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
         if (rows <= 0) continue;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          const int s = it % NSTAGE;
-          if (!mbar_wait(smem_u32(&bar_afull[s]), (it / NSTAGE) & 1u, abort_flag)) { ok = false; break; }
+          const int s = (int)(it & smask);
+          if (!mbar_wait(smem_u32(&bar_afull[s]), (it >> sshift) & 1u, abort_flag)) { ok = false; break; }
           mbar_arrive_cluster(mapa(smem_u32(&bar_full[s]), 0));
         }
       }
@@ -500,13 +523,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
     RT_DECL(w_tfull = 0, t_begin = RT_NOW());
     for (long long t = t_first; walk.seek(t, e, ntp, row0, rows); t += t_step) {
       if (rows <= 0) continue;
-      const uint32_t a = tile & 1u;
-      if (!RT_WAIT(w_tfull, mbar_wait<true>(smem_u32(&bar_tfull[a]), (tile >> 1) & 1u, abort_flag))) break;
+      if (!RT_WAIT(w_tfull, mbar_wait<true>(smem_u32(&bar_tfull[0]), tile & 1u, abort_flag))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int n = (ntp * CG + (int)rank) * 128 + q * 32 + lane;
       const bool n_ok = n < p.N;
-      const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + a * PF_TN;
+      const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16);
       const int n_eff = (rows + 15) & ~15;
+      // this thread owns output column n; consecutive token rows are p.N elements apart
+      const size_t esz = p.out_dtype == DST_OUT_F32 ? 4 : 2;
+      uint8_t* optr = static_cast<uint8_t*>(p.out) + ((size_t)row0 * p.N + (n_ok ? n : 0)) * esz;
+      const size_t ostep = (size_t)p.N * esz;
       for (int c0 = 0; c0 < n_eff; c0 += 32) {
         uint32_t v[32];
         if (c0 + 32 <= n_eff) {
@@ -516,34 +542,47 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
 #pragma unroll
           for (int j = 16; j < 32; ++j) v[j] = 0u;
         }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const float rs_lane = (p.row_scale && c0 + lane < rows) ? p.row_scale[row0 + c0 + lane] : 1.f;
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int lim = n_ok ? rows - c0 : 0;  // token rows of this chunk that exist (and a column that exists)
+        if (p.out_dtype == DST_OUT_BF16) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int m = c0 + j;
-          const float rs = __shfl_sync(0xffffffffu, rs_lane, j);
-          if (m < rows && n_ok) {
-            const float val = __uint_as_float(v[j]) * rs;
-            const int64_t o = (int64_t)(row0 + m) * p.N + n;
-            if (p.out_dtype == DST_OUT_BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(val);
-            else if (p.out_dtype == DST_OUT_F16) static_cast<__half*>(p.out)[o] = __float2half_rn(val);
-            else static_cast<float*>(p.out)[o] = p.accumulate ? static_cast<float*>(p.out)[o] + val : val;
+          for (int j = 0; j < 32; ++j) {
+            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+            if (j < lim) *reinterpret_cast<__nv_bfloat16*>(optr + j * ostep) = __float2bfloat16_rn(val);
+          }
+        } else if (p.out_dtype == DST_OUT_F16) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+            if (j < lim) *reinterpret_cast<__half*>(optr + j * ostep) = __float2half_rn(val);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+            if (j < lim) {
+              float* o = reinterpret_cast<float*>(optr + j * ostep);
+              *o = p.accumulate ? *o + val : val;
+            }
           }
         }
+        optr += 32 * ostep;
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        if (CG == 2) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[a]), 0));
-        else mbar_arrive(smem_u32(&bar_tempty[a]));
+        if (CG == 2) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[0]), 0));
+        else mbar_arrive(smem_u32(&bar_tempty[0]));
       }
       ++tile;
     }
     if (warp == 2 && lane == 0) { RT_ADD(16, RT_NOW() - t_begin); RT_ADD(17, w_tfull); RT_ADD(18, 1); }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
-    const int td = tid - 192;
-    const int r = td & 127, q4 = td >> 7;  // row of the tile, quarter (16 trits) of the 64-trit stage
+    // A warp may only write the TMEM lanes of its own quarter (warp id % 4): it owns those 32 weight rows.
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t grp = (uint32_t)(warp - 6) >> 2;  // this warp dequantises the stages with (stage index & 3) == grp
     const int swz = (r >> 1) & 3;  // 16-byte chunk swizzle of the tiled layout
     const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
     const bool vec_scales = (p.G & 7) == 0;  // rows of 8 k scales are 16-byte aligned
@@ -585,64 +624,79 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap32, const __grid_constant
       have = ahead.seek(at, ae, antp, arow0, arows);
       while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
       uint4 sc[TERMS];
+      int sbk = -1;
       for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-        const int s = it % NSTAGE;
+        if (++sbk == SPB) sbk = 0;
+        const int s = (int)(it & smask);
         if ((ks & 15) == 0) {
 #pragma unroll
           for (int i = 0; i < TERMS; ++i) sc[i] = sc_next[i];
           if (ks + 16 < p.kstages) load_scales(e, nt * 128 + r, (ks + 16) >> 1, sc_next);
           else if (have) load_scales(ae, (antp * CG + (int)rank) * 128 + r, 0, sc_next);
         }
-        const int sbk = ks % SPB;
         const uint32_t slot = pit & 1u;
         if (sbk == 0 && !RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), (pit >> 1) & 1u, abort_flag))) { ok = false; break; }
         const uint8_t* slab = slabs + (size_t)slot * p.n_terms * PF_SLAB + r * 64;
-        __half2 acc[8];
-        const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
-        if (FMT == 2) {
-          const int boff = ((sbk ^ swz) << 4) + q4 * 4;
-#pragma unroll
-          for (int i = 0; i < TERMS; ++i) {
-            if (i < p.n_terms) {
-              const uint32_t w = *reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB + boff);
-              const __half2 s2 = pick_scale(sc[i], g);
-              if (i == 0) tq2_word<true>(w, s2, acc);
-              else tq2_word<false>(w, s2, acc);
-            }
+        const bool last_of_slab = sbk == SPB - 1 || ks == p.kstages - 1;
+        if ((it & 3u) != grp) {  // another group's stage: only keep the slab ring's bookkeeping in step
+          if (last_of_slab) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
+            ++pit;
           }
-        } else {
-          const int qq = sbk * 4 + q4;  // 16-trit slot 0..19 inside the 320-trit superblock
-          const int tau = qq * 16, b0 = tau / 5, o = tau - b0 * 5;
-          const int wi = b0 >> 2, sh = (b0 & 3) * 8;
-#pragma unroll
-          for (int i = 0; i < TERMS; ++i) {
-            if (i < p.n_terms) {
-              const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
-              // logical word w of the row sits in chunk (w >> 2) ^ swz
-              const uint32_t w0 = wp[(((wi >> 2) ^ swz) << 2) | (wi & 3)];
-              const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) >> 2) ^ swz) << 2) | ((wi + 1) & 3)] : 0u;
-              const uint32_t win = __funnelshift_r(w0, w1, sh);  // bytes b0 .. b0 + 3 of the row-superblock
-              const __half2 s2 = pick_scale(sc[i], g);
-              if (i == 0) tq1_dispatch<true>(o, win, lut_addr, s2, acc);
-              else tq1_dispatch<false>(o, win, lut_addr, s2, acc);
-            }
-          }
+          continue;
         }
-        if (sbk == SPB - 1 || ks == p.kstages - 1) {  // last read of this slab: hand the slot back
+        const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
+        uint32_t v[32];               // the row's 64 weights of this stage: 32 fp16 pairs = 32 TMEM columns
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          __half2 acc[8];
+          if (FMT == 2) {
+            const int boff = ((sbk ^ swz) << 4) + q4 * 4;
+#pragma unroll
+            for (int i = 0; i < TERMS; ++i) {
+              if (i < p.n_terms) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB + boff);
+                const __half2 s2 = pick_scale(sc[i], g);
+                if (i == 0) tq2_word<true>(w, s2, acc);
+                else tq2_word<false>(w, s2, acc);
+              }
+            }
+          } else {
+            const int qq = sbk * 4 + q4;  // 16-trit slot 0..19 inside the 320-trit superblock
+            const int tau = qq * 16, b0 = tau / 5, o = tau - b0 * 5;
+            const int wi = b0 >> 2, sh = (b0 & 3) * 8;
+#pragma unroll
+            for (int i = 0; i < TERMS; ++i) {
+              if (i < p.n_terms) {
+                const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
+                // logical word w of the row sits in chunk (w >> 2) ^ swz
+                const uint32_t w0 = wp[(((wi >> 2) ^ swz) << 2) | (wi & 3)];
+                const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) >> 2) ^ swz) << 2) | ((wi + 1) & 3)] : 0u;
+                const uint32_t win = __funnelshift_r(w0, w1, sh);  // bytes b0 .. b0 + 3 of the row-superblock
+                const __half2 s2 = pick_scale(sc[i], g);
+                if (i == 0) tq1_dispatch<true>(o, win, lut_addr, s2, acc);
+                else tq1_dispatch<false>(o, win, lut_addr, s2, acc);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[q4 * 8 + j] = h2_bits(acc[j]);
+        }
+        if (last_of_slab) {  // last read of this slab: hand the slot back
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
           ++pit;
         }
-        if (!RT_WAIT(w_dempty, mbar_wait(smem_u32(&bar_empty[s]), ((it / NSTAGE) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
+        if (!RT_WAIT(w_dempty, mbar_wait<true>(smem_u32(&bar_empty[s]), ((it >> sshift) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
         RT_DECL(t_tail = RT_NOW());
-        uint8_t* arow = smem + s * STAGE_BYTES + r * 128;
+        {
+          const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + PF_TN + s * PF_A_COLS;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int chunk = q4 * 2 + c;
-          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(h2_bits(acc[4 * c]), h2_bits(acc[4 * c + 1]), h2_bits(acc[4 * c + 2]), h2_bits(acc[4 * c + 3]));
+          for (int q4 = 0; q4 < 4; ++q4) tmem_st_8(taddr + q4 * 8, v + q4 * 8);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(CG == 2 && !leader ? &bar_afull[s] : &bar_full[s]));
 #ifdef DST_ROLE_TIMERS
@@ -718,14 +772,14 @@ EncodeFn encode_fn() {
 }
 
 template <int FMT, int CG, int TERMS>
-int launch_fmt(const CUtensorMap& map32, const CUtensorMap& map128, PrefillParams p, long long tiles_upper, cudaStream_t st) {
+int launch_fmt(const TmaMaps& maps, PrefillParams p, long long tiles_upper, cudaStream_t st) {
   // deepest stage ring the shared-memory budget allows next to the packed slabs and the TQ1 table
-  const size_t stage_bytes = PF_A_BYTES + PF_B_BYTES / CG;
+  const size_t stage_bytes = PF_B_BYTES / CG;
   const size_t fixed = 1024 + (size_t)2 * p.n_terms * PF_SLAB + (FMT == 1 ? PF_LUT_BYTES : 0);
-  int nstage = (int)((PF_SMEM_MAX - fixed) / stage_bytes);
-  nstage = nstage > 6 ? 6 : nstage;
-  if (nstage < 2) return DST_ERR_UNSUPPORTED;
-  p.nstage = nstage;
+  const int fit = (int)((PF_SMEM_MAX - fixed) / stage_bytes);
+  if (fit < 2) return DST_ERR_UNSUPPORTED;
+  p.nstage_log2 = fit >= 8 ? 3 : (fit >= 4 ? 2 : 1);  // a power of two, so ring indices are a mask and a shift
+  const int nstage = 1 << p.nstage_log2;
   const size_t smem = fixed + (size_t)nstage * stage_bytes;
   auto kernel = prefill_kernel<FMT, CG, TERMS>;
   DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -759,7 +813,7 @@ int launch_fmt(const CUtensorMap& map32, const CUtensorMap& map128, PrefillParam
   cfg.gridDim = dim3((unsigned)(groups * CG), 1, 1);
   cfg.attrs = n_attr ? attr : nullptr;
   cfg.numAttrs = n_attr;
-  DST_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map32, map128, p));
+  DST_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, p));
   return DST_OK;
 }
 
@@ -794,14 +848,14 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
     convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale, xh, rs);
   DST_CUDA_TRY(cudaGetLastError());
 
-  // 2. tensor maps over the fp16 rows: [T, K], boxes of 64 x 32 and 64 x 128, 128-byte swizzle, zero fill outside
-  CUtensorMap map32, map128;
+  // 2. tensor maps over the fp16 rows: [T, K], boxes of 64 K-elements x 16 i token rows, 128-byte swizzle, zero fill outside
+  TmaMaps maps;
   const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.T};
   const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
   const cuuint32_t estr[2] = {1, 1};
-  for (int which = 0; which < 2; ++which) {
-    const cuuint32_t box[2] = {64, which ? 128u : (cuuint32_t)PF_BOX};
-    const CUresult cr = encode_fn()(which ? &map128 : &map32, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr,
+  for (int i = 0; i < 16; ++i) {
+    const cuuint32_t box[2] = {64, (cuuint32_t)(16 * (i + 1))};
+    const CUresult cr = encode_fn()(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -830,9 +884,9 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   // CTA pairs need an even number of 128-row weight tiles
   const bool pairs = a.N % 256 == 0;
 #define DST_PF_LAUNCH(FMT_, CG_)                                                                          \
-  (a.terms.n == 1 ? launch_fmt<FMT_, CG_, 1>(map32, map128, p, tiles_upper, stream)                       \
-                  : a.terms.n == 2 ? launch_fmt<FMT_, CG_, 2>(map32, map128, p, tiles_upper, stream)      \
-                                   : launch_fmt<FMT_, CG_, 4>(map32, map128, p, tiles_upper, stream))
+  (a.terms.n == 1 ? launch_fmt<FMT_, CG_, 1>(maps, p, tiles_upper, stream)                       \
+                  : a.terms.n == 2 ? launch_fmt<FMT_, CG_, 2>(maps, p, tiles_upper, stream)      \
+                                   : launch_fmt<FMT_, CG_, 4>(maps, p, tiles_upper, stream))
   if (a.fmt == DST_FMT_TQ2) return pairs ? DST_PF_LAUNCH(2, 2) : DST_PF_LAUNCH(2, 1);
   return pairs ? DST_PF_LAUNCH(1, 2) : DST_PF_LAUNCH(1, 1);
 #undef DST_PF_LAUNCH
