@@ -58,6 +58,7 @@ constexpr int PF_A_RING = 8;          // A stages in TMEM (columns 256..511)
 constexpr int PF_B_BYTES = PF_TN * 128;
 constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
 constexpr int PF_SLAB = 8192;                   // one (row tile, superblock) slab of packed weights
+constexpr bool kUseCtaPairs = false;
 constexpr int PF_SMEM_MAX = 232448;             // 227 KB of dynamic shared memory per CTA
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
@@ -881,8 +882,11 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.kstages = (int)(a.K / 64);
   const long long tiles_upper = ((long long)cdiv64(a.T, PF_TN) + a.E) * p.NT;
-  // CTA pairs need an even number of 128-row weight tiles
-  const bool pairs = a.N % 256 == 0;
+  // CTA pairs (cta_group::2) need an even number of 128-row weight tiles. They are correct but measured SLOWER
+  // than single CTAs here (2.51 M vs 1.58 M cycles per launch on the same case): the cross-CTA barrier traffic
+  // (remote arrives, multicast commits) costs more than the halved activation traffic saves while the kernel is
+  // bound by its per-stage handshakes. Kept compiled and tested behind this switch for when that changes.
+  const bool pairs = kUseCtaPairs && a.N % 256 == 0;
 #define DST_PF_LAUNCH(FMT_, CG_)                                                                          \
   (a.terms.n == 1 ? launch_fmt<FMT_, CG_, 1>(maps, p, tiles_upper, stream)                       \
                   : a.terms.n == 2 ? launch_fmt<FMT_, CG_, 2>(maps, p, tiles_upper, stream)      \
