@@ -110,7 +110,7 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
   }
   // AUTO: few rows per expert -> decode GEMV; many -> tcgen05 grouped GEMM; otherwise generic.
   const int64_t avg_rows = a.max_rows >= 0 ? a.max_rows : cdiv64(T, E);
-  if (avg_rows <= 32 && decode_supports(a)) return launch_decode(a, st);
+  if (avg_rows <= 16 && decode_supports(a)) return launch_decode(a, st);
   if (prefill_supports(a)) return launch_prefill(a, st);
   if (decode_supports(a)) return launch_decode(a, st);
   if (weight_layout == DST_LAYOUT_TILED) return DST_ERR_UNSUPPORTED;

@@ -584,7 +584,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     // A warp may only write the TMEM lanes of its own quarter (warp id % 4): it owns those 32 weight rows.
     const int r = (warp & 3) * 32 + lane;
     const uint32_t grp = (uint32_t)(warp - 6) >> 2;  // this warp dequantises the stages with (stage index & 3) == grp
-    const int swz = (r >> 1) & 3;  // 16-byte chunk swizzle of the tiled layout
+    const int swz = (r >> 1) & 3;  // swizzle of the tiled layout: logical word w sits at physical word (((w & 3) ^ swz) << 2) | (w >> 2)
     const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
     const bool vec_scales = (p.G & 7) == 0;  // rows of 8 k scales are 16-byte aligned
     uint32_t it = 0, pit = 0;
@@ -653,7 +653,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         for (int q4 = 0; q4 < 4; ++q4) {
           __half2 acc[8];
           if (FMT == 2) {
-            const int boff = ((sbk ^ swz) << 4) + q4 * 4;
+            const int boff = ((q4 ^ swz) << 4) + sbk * 4;  // logical word 4 sbk + q4
 #pragma unroll
             for (int i = 0; i < TERMS; ++i) {
               if (i < p.n_terms) {
@@ -671,9 +671,8 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
             for (int i = 0; i < TERMS; ++i) {
               if (i < p.n_terms) {
                 const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
-                // logical word w of the row sits in chunk (w >> 2) ^ swz
-                const uint32_t w0 = wp[(((wi >> 2) ^ swz) << 2) | (wi & 3)];
-                const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) >> 2) ^ swz) << 2) | ((wi + 1) & 3)] : 0u;
+                const uint32_t w0 = wp[(((wi & 3) ^ swz) << 2) | (wi >> 2)];
+                const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) & 3) ^ swz) << 2) | ((wi + 1) >> 2)] : 0u;
                 const uint32_t win = __funnelshift_r(w0, w1, sh);  // bytes b0 .. b0 + 3 of the row-superblock
                 const __half2 s2 = pick_scale(sc[i], g);
                 if (i == 0) tq1_dispatch<true>(o, win, lut_addr, s2, acc);

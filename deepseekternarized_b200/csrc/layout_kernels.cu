@@ -17,9 +17,12 @@
 //        (low half, high half) pair is two consecutive trits: trit 2j sits in bits [2j, 2j+1], trit 2j+1
 //        in bits [16+2j, 17+2j]. One AND then yields an fp16x2 of adjacent weights.
 //
-// Inside a row-superblock the four 16-byte chunks are stored at chunk index c ^ ((r >> 1) & 3): when a slab
-// sits in shared memory and 32 threads read the same word of 32 consecutive rows (64-byte stride), the
-// accesses spread over 8 bank groups instead of 2.
+// Inside a row-superblock the sixteen 32-bit words are transposed 4 x 4 and swizzled: logical word w (trits
+// 16 w .. 16 w + 15 in TQ2, bytes 4 w .. 4 w + 3 in TQ1) is stored at physical word (((w & 3) ^ s) << 2) | (w >> 2)
+// with s = (r >> 1) & 3. One 128-bit load of physical unit (c ^ s) therefore returns words c, 4 + c, 8 + c,
+// 12 + c: the decode kernel's lane c of a quad gets its k-slots of all four 64-trit chunks in one load, and a
+// quad reads the row's 64 bytes contiguously. The swizzle spreads the accesses of 32 threads that read the
+// same word of 32 consecutive rows of a slab in shared memory (64-byte stride) over 8 bank groups instead of 2.
 //
 // dst_untile_weights inverts the permutation bit for bit.
 #include "dst_common.cuh"
@@ -71,7 +74,7 @@ __global__ void tile_kernel(const uint8_t* __restrict__ canon, int64_t E, int64_
         }
       }
     }
-    tiled[(i & ~15LL) | (((q >> 2) ^ ((r >> 1) & 3)) << 2) | (q & 3)] = w;
+    tiled[(i & ~15LL) | (((q & 3) ^ ((r >> 1) & 3)) << 2) | (q >> 2)] = w;
   }
 }
 
@@ -88,8 +91,8 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int64_t E, int6
     uint8_t v;
     if (FMT == 1) {
       const int64_t sb = b >> 6;
-      const int bi = (int)(b & 63);
-      v = tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + ((((bi >> 4) ^ ((int)(r >> 1) & 3)) << 4) | (bi & 15))];
+      const int bi = (int)(b & 63), w = bi >> 2;
+      v = tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + ((((w & 3) ^ ((int)(r >> 1) & 3)) << 4) | ((w >> 2) << 2) | (bi & 3))];
     } else {
       uint32_t acc = 0;
 #pragma unroll
@@ -98,7 +101,7 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int64_t E, int6
         const int64_t sb = k >> 8;
         const int kk = (int)(k & 255), q = kk >> 4, t = kk & 15;
         const uint32_t w = reinterpret_cast<const uint32_t*>(tiled)[(((e * NT + nt) * S + sb) * 128 + r) * 16 +
-                                                                    ((((q >> 2) ^ ((int)(r >> 1) & 3)) << 2) | (q & 3))];
+                                                                    ((((q & 3) ^ ((int)(r >> 1) & 3)) << 2) | (q >> 2))];
         const int bit = (t & 1) ? 16 + (t >> 1) * 2 : (t >> 1) * 2;
         acc |= ((w >> bit) & 3u) << (2 * j);
       }

@@ -82,7 +82,8 @@ int dst_unpack(const uint8_t* packed, int64_t N, int64_t K, int fmt, int8_t* tri
  * Tiled device layout: tiled[e][n / 128][sb][n % 128][64 bytes], a superblock sb being 64 bytes of one
  * row (256 trits in TQ2, 320 in TQ1). Rows are padded to a multiple of 128 and K to whole superblocks
  * with zero trits. TQ1 bytes keep their base-3 value; TQ2 32-bit words are bit-permuted so that the
- * low and the high half hold the even and the odd trits of 16 consecutive ones. dst_tiled_bytes gives
+ * low and the high half hold the even and the odd trits of 16 consecutive ones; the sixteen words of a
+ * row-superblock are stored transposed 4 x 4 and swizzled by the row (see csrc/layout_kernels.cu). dst_tiled_bytes gives
  * the buffer size (-1 on bad arguments); dst_untile_weights restores the canonical bytes bit for bit.
  * `tiled` must be 16-byte aligned. The conversion is the one-time copy the reference makes when a
  * linear first meets a device (boilerplate/ternary/ops.py:41-45, TernaryLinear._on).

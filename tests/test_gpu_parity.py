@@ -18,10 +18,11 @@ FMT = {1: "tq1", 2: "tq2"}
 DEV = "cuda"
 
 
-def fast_algos(K, group, scale_dtype=np.float16):
-    """Kernels that must accept a shape: the fast ones cover group 128, K % 128 == 0, fp16 scales."""
+def fast_algos(K, group, scale_dtype=np.float16, fmt="tq1"):
+    """Kernels that must accept a shape: the tcgen05 kernel covers group 128, K % 128 == 0, fp16 scales; the
+    decode GEMV additionally needs TQ2 and K % 256 == 0."""
     ok = group == 128 and K % 128 == 0 and scale_dtype == np.float16
-    return ["generic", "auto"] + (["prefill"] if ok else [])
+    return ["generic", "auto"] + (["prefill"] if ok else []) + (["decode"] if ok and fmt == "tq2" and K % 256 == 0 else [])
 
 
 @pytest.fixture(scope="module")
@@ -93,7 +94,7 @@ def test_bf16_linear_against_reference_golden(golden, kb):
         fmt = FMT[code]
         x = O.from_bf16_bits(g[f"c{c}_x_bits"])
         terms = [(g[f"c{c}_packed{i}"], g[f"c{c}_scale{i}"]) for i in range(k_terms)]
-        for algo in fast_algos(K, group):
+        for algo in fast_algos(K, group, fmt=fmt):
             lin = TernaryLinear([PackedTerm(torch.from_numpy(p), torch.from_numpy(s)) for p, s in terms], K, fmt, group,
                                 act="bf16", backend="b200", algo=algo)
             xt = bf16_tensor(x, DEV).view(-1, K)
@@ -121,7 +122,7 @@ def test_baseline_shapes_against_oracle_and_golden(golden, kb, case):
     s = O.synth_scales(rng, (N, K // 128))
     x = O.synth_acts(rng, (M, K))
     p = O.pack(t, fmt)
-    for algo in fast_algos(K, 128):
+    for algo in fast_algos(K, 128, fmt=fmt):
         y = kb.ternary_gemm_bf16(bf16_tensor(x, DEV), [torch.from_numpy(p).to(DEV)], [torch.from_numpy(s).to(DEV)], K, 128,
                                  fmt, algo=algo).cpu().numpy()
         np.testing.assert_allclose(y.reshape(-1)[::61], g[f"c{case}_sample"], rtol=1e-4, atol=1e-3)
@@ -153,7 +154,7 @@ def test_config3_stacked_k2_decode(kb, fmt, M):
         rng = np.random.default_rng(M + N)
         terms = make_terms(rng, N, K, 128, fmt, k_terms=2)
         x = O.synth_acts(rng, (M, K))
-        for algo in fast_algos(K, 128):
+        for algo in fast_algos(K, 128, fmt=fmt):
             y = kb.ternary_gemm_bf16(bf16_tensor(x, DEV), [torch.from_numpy(p).to(DEV) for p, _ in terms],
                                      [torch.from_numpy(s).to(DEV) for _, s in terms], K, 128, fmt, algo=algo).cpu().numpy()
             check_gemm(y, x, terms, K, 128, fmt)
@@ -161,15 +162,16 @@ def test_config3_stacked_k2_decode(kb, fmt, M):
             np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-3)
 
 
-def test_accumulate_row_scale_and_output_types(kb):
+@pytest.mark.parametrize("fmt,K", [("tq1", 384), ("tq2", 512)])
+def test_accumulate_row_scale_and_output_types(kb, fmt, K):
     rng = np.random.default_rng(5)
-    N, K, M, fmt = 96, 384, 5, "tq1"
+    N, M = 96, 5
     terms = make_terms(rng, N, K, 128, fmt, 1)
     x = O.synth_acts(rng, (M, K))
     rs = rng.random(M).astype(np.float32) + 0.5
     p, s = [torch.from_numpy(terms[0][0]).to(DEV)], [torch.from_numpy(terms[0][1]).to(DEV)]
     base = O.gemm_f32(x, terms[0][0], terms[0][1].astype(np.float32), K, 128, fmt)
-    for algo in fast_algos(K, 128):
+    for algo in fast_algos(K, 128, fmt=fmt):
         out = torch.full((M, N), 2.0, device=DEV)
         kb.ternary_gemm_bf16(bf16_tensor(x, DEV), p, s, K, 128, fmt, row_scale=torch.from_numpy(rs).to(DEV), out=out,
                              accumulate=True, algo=algo)
@@ -237,6 +239,26 @@ def test_reference_cuda_parity_shapes(kb, fmt, T):
     got = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, [torch.from_numpy(packed).to(DEV)],
                                        [torch.from_numpy(s16).to(DEV)], K, group, fmt)
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=2e-3)
+
+
+@pytest.mark.parametrize("algo", ["decode", "prefill", "auto"])
+def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo):
+    """Grouped GEMV as a MoE decode step sees it: few rows per expert, some experts empty, one above 16 rows."""
+    E, N, K, fmt = 7, 200, 1024, "tq2"
+    rng = np.random.default_rng(21)
+    terms = make_terms(rng, N, K, 128, fmt, 2, lead=(E,))
+    counts = np.array([1, 0, 8, 3, 19, 0, 2])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = O.synth_acts(rng, (int(offsets[-1]), K))
+    tiled = [kb.tile_weights(torch.from_numpy(p).to(DEV), fmt, K) for p, _ in terms]
+    y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, tiled, [torch.from_numpy(s).to(DEV) for _, s in terms], K, 128, fmt,
+                                     algo=algo).cpu().numpy()
+    for e in range(E):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            check_gemm(y[a:b], x[a:b], [(p[e], s[e]) for p, s in terms], K, 128, fmt)
+            want = O.ternary_linear(x[a:b], [(p[e], s[e]) for p, s in terms], K, 128, fmt, out_bf16=False)
+            np.testing.assert_allclose(y[a:b], want, rtol=1e-4, atol=1e-3)
 
 
 def test_native_entry_rejects_malformed_tensors(kb):
