@@ -99,11 +99,18 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines = index, None, []  # lines: (host time when read, text)
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -112,7 +119,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -124,7 +131,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        inside = [ln for ts, ln in self.lines if self.t0 is None or (self.t0 <= ts <= (self.t1 or ts) + 0.05)]
+        for ln in inside:
             f = [v.strip() for v in ln.split(",")]
             if len(f) < 8:
                 continue
@@ -210,6 +218,17 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def traffic_per_launch(n_gpus: int):
+    """DRAM bytes per grouped-GEMM launch (mean of the gate+up and the down launch): dram__bytes_read.sum +
+    dram__bytes_write.sum of one ncu capture on the reduced case (96 experts x 4096 tokens: 737 MB and 462 MB,
+    profiles/prefill_kernel_tq1_moe_reduced_case.md), scaled by the experts and rows one launch processes (traffic is
+    proportional to both). None for workloads the capture does not describe."""
+    if FMT != "tq1" or TOKENS * 96 != 4096 * N_EXPERTS:
+        return None
+    scale = (N_EXPERTS / 96.0) / n_gpus
+    return 0.5 * (737.4e6 + 462.0e6) * scale
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -330,7 +349,7 @@ class TimedOps:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--algo", default="auto")
@@ -399,11 +418,15 @@ def main():
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
-    ops.launches, ops.timing = 0, True
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()  # started ahead of the timed region (nvidia-smi takes a moment to deliver its first sample)
+    for _ in range(20):
+        step_resident()
+    ops.launches, ops.timing = 0, True
+    sampler.mark_begin()
     total_ms = timed(step_resident, args.steps)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     launches = ops.launches
     ops.timing = False
@@ -427,7 +450,7 @@ def main():
                     "h2d_bytes_per_step": int(x_host.numel() * 2 + logits_host.numel() * 4) * world,
                     "d2h_bytes_per_step": int(y_host.numel() * 2) * world},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / peak) if achieved else None, "traffic": traffic_per_launch(world),
                          "kernel": "grouped expert GEMM (2 launches per step: gate+up, down)", "peak_source": peaks["source"] + " (sustained)",
                          "ms_per_launch": float(np.mean(gemm_ms)) if gemm_ms else None},
         }

@@ -261,6 +261,29 @@ def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo):
             np.testing.assert_allclose(y[a:b], want, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_prefill_many_tiles_per_cta(kb, fmt):
+    """More tiles than SMs, so every persistent CTA of the tcgen05 kernel walks several tiles (ring phases, the
+    packed-slab ring and the accumulator hand-over all wrap across tile borders); ragged rows per expert around the
+    256-row tile size, one empty expert. Checked on sampled experts against the oracle, all rows for finiteness."""
+    E, N, K = 12, 2048, 1024
+    rng = np.random.default_rng(77)
+    terms = make_terms(rng, N, K, 128, fmt, 1, lead=(E,))
+    counts = np.array([257, 300, 0, 129, 256, 512, 31, 270, 255, 1, 513, 240])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = O.synth_acts(rng, (int(offsets[-1]), K))
+    tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), fmt, K)]
+    y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), torch.from_numpy(offsets).to(DEV), tiled, [torch.from_numpy(terms[0][1]).to(DEV)],
+                                     K, 128, fmt, algo="prefill", validate_offsets=False)
+    torch.cuda.synchronize()
+    assert kb.ext().dst_check_device_status(None) == 0
+    y = y.cpu().numpy()
+    assert np.isfinite(y).all()
+    for e in (0, 5, 9, 10):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        check_gemm(y[a:b], x[a:b], [(terms[0][0][e], terms[0][1][e])], K, 128, fmt)
+
+
 def test_native_entry_rejects_malformed_tensors(kb):
     """tests/test_kernel_security.py:19-38 of the reference, against this backend: every malformed
     argument raises RuntimeError before any launch."""
