@@ -321,13 +321,15 @@ class TimedOps:
         self.launches += 3
         return self.base.sort(*a)
 
-    def gather(self, *a):
-        self.launches += 1
-        return self.base.gather(*a)
+    fused_norm = True
 
-    def swiglu(self, *a):
+    def gather(self, *a, **k):
         self.launches += 1
-        return self.base.swiglu(*a)
+        return self.base.gather(*a, **k)
+
+    def swiglu(self, *a, **k):
+        self.launches += 1
+        return self.base.swiglu(*a, **k)
 
     def combine(self, *a):
         self.launches += 2
@@ -342,7 +344,7 @@ class TimedOps:
         y = self.base.gemm(x, offsets, packed, scales, K, group, fmt)
         b.record()
         self.events.append((a, b))
-        self.flops += 2.0 * x.size(0) * packed[0].size(1) * K * len(packed)
+        self.flops += 2.0 * x.size(0) * packed[0].size(1) * K
         return y
 
 

@@ -25,7 +25,7 @@ NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024 + 16384
 FMT_TQ1, FMT_TQ2 = 1, 2
 SCALE_F16, SCALE_F32, SCALE_BF16 = 0, 1, 2
 OUT_F32, OUT_BF16, OUT_F16 = 0, 1, 2
-ACT_BF16, ACT_F16, ACT_I8 = 0, 1, 2
+ACT_BF16, ACT_F16, ACT_I8, ACT_F16_NORM = 0, 1, 2, 3
 ALGO_AUTO, ALGO_GENERIC, ALGO_DECODE, ALGO_PREFILL = 0, 1, 2, 3
 MAX_TERMS = 4
 LAYOUT_CANONICAL, LAYOUT_TILED = 0, 1
@@ -91,6 +91,10 @@ _SIGNATURES = {
                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_gather_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                        ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_gather_rows_norm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_swiglu_norm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                       ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_swiglu": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                   ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,

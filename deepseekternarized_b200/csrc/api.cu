@@ -46,12 +46,14 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
                                         dst_stream_t stream) {
   using namespace dst;
   if (K <= 0 || group <= 0 || (fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2)) return DST_ERR_BAD_ARG;
-  if (out_dtype < DST_OUT_F32 || out_dtype > DST_OUT_F16 || act_dtype < DST_ACT_BF16 || act_dtype > DST_ACT_I8 ||
+  if (out_dtype < DST_OUT_F32 || out_dtype > DST_OUT_F16 || act_dtype < DST_ACT_BF16 || act_dtype > DST_ACT_F16_NORM ||
       scale_dtype < DST_SCALE_F16 || scale_dtype > DST_SCALE_BF16 || algo < DST_ALGO_AUTO || algo > DST_ALGO_PREFILL)
     return DST_ERR_BAD_ARG;
   if (n_terms < 1 || n_terms > DST_MAX_TERMS || E < 0 || T < 0 || N < 0) return DST_ERR_BAD_ARG;
   if (weight_layout != DST_LAYOUT_CANONICAL && weight_layout != DST_LAYOUT_TILED) return DST_ERR_BAD_ARG;
   if (accumulate && out_dtype != DST_OUT_F32) return DST_ERR_BAD_ARG;
+  if (act_dtype == DST_ACT_F16_NORM && (row_scale == nullptr || algo == DST_ALGO_GENERIC || algo == DST_ALGO_DECODE))
+    return act_dtype == DST_ACT_F16_NORM && row_scale == nullptr ? DST_ERR_BAD_ARG : DST_ERR_UNSUPPORTED;
   if (E > DST_MAX_EXPERTS || K > (int64_t(1) << 24) || N > (int64_t(1) << 24) || T > 0x7fffffff ||
       group > (int64_t(1) << 24))
     return DST_ERR_BAD_SHAPE;
@@ -108,6 +110,7 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
     case DST_ALGO_PREFILL: return launch_prefill(a, st);
     default: break;
   }
+  if (act_dtype == DST_ACT_F16_NORM) return launch_prefill(a, st);  // only the tcgen05 kernel reads this format
   // AUTO: few rows per expert -> decode GEMV; many -> tcgen05 grouped GEMM; otherwise generic.
   const int64_t avg_rows = a.max_rows >= 0 ? a.max_rows : cdiv64(T, E);
   if (avg_rows <= 16 && decode_supports(a)) return launch_decode(a, st);

@@ -826,26 +826,36 @@ size_t prefill_workspace_bytes(int act_dtype, int64_t T, int64_t K) {
 
 bool prefill_supports(const GemmArgs& a) {
   return a.weight_layout == DST_LAYOUT_TILED && a.group == 128 && a.K % 128 == 0 && a.scale_dtype == DST_SCALE_F16 &&
-         (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) && a.workspace != nullptr &&
-         a.workspace_bytes >= prefill_workspace_bytes(a.act_dtype, a.T, a.K) && a.T < (int64_t(1) << 30) &&
+         ((a.act_dtype == DST_ACT_F16_NORM && a.row_scale != nullptr) ||
+          ((a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) && a.workspace != nullptr &&
+           a.workspace_bytes >= prefill_workspace_bytes(a.act_dtype, a.T, a.K))) &&
+         a.T < (int64_t(1) << 30) &&
          a.N <= (int64_t(1) << 22) && encode_fn() != nullptr;
 }
 
 int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   if (a.T == 0 || a.N == 0 || a.E == 0) return DST_OK;
   if (!prefill_supports(a)) return DST_ERR_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return DST_ERR_ALIGNMENT;
+  const bool prenorm = a.act_dtype == DST_ACT_F16_NORM;
+  if (!prenorm && (reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return DST_ERR_ALIGNMENT;
+  if (prenorm && (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return DST_ERR_ALIGNMENT;
   for (int i = 0; i < a.terms.n; ++i)
     if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 15) != 0)
       return DST_ERR_ALIGNMENT;
 
   // 1. activations -> fp16 rows + per-row power-of-two factor, in the workspace
-  __half* xh = static_cast<__half*>(a.workspace);
-  float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + (((size_t)a.T * a.K * 2 + 255) & ~(size_t)255));
-  if (a.act_dtype == DST_ACT_BF16)
-    convert_rows_kernel<__nv_bfloat16><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.x), a.K, a.row_scale, xh, rs);
+  //    (skipped when the caller hands in rows that are in that format already)
+  const __half* xh = prenorm ? static_cast<const __half*>(a.x) : static_cast<const __half*>(a.workspace);
+  const float* rs = prenorm ? a.row_scale
+                            : reinterpret_cast<const float*>(static_cast<const uint8_t*>(a.workspace) + (((size_t)a.T * a.K * 2 + 255) & ~(size_t)255));
+  if (prenorm) {
+    // nothing to convert
+  } else if (a.act_dtype == DST_ACT_BF16)
+    convert_rows_kernel<__nv_bfloat16><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.x), a.K, a.row_scale,
+                                                                          static_cast<__half*>(a.workspace), const_cast<float*>(rs));
   else
-    convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale, xh, rs);
+    convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale,
+                                                                   static_cast<__half*>(a.workspace), const_cast<float*>(rs));
   DST_CUDA_TRY(cudaGetLastError());
 
   // 2. tensor maps over the fp16 rows: [T, K], boxes of 64 K-elements x 16 i token rows, 128-byte swizzle, zero fill outside
@@ -855,7 +865,7 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   const cuuint32_t estr[2] = {1, 1};
   for (int i = 0; i < 16; ++i) {
     const cuuint32_t box[2] = {64, (cuuint32_t)(16 * (i + 1))};
-    const CUresult cr = encode_fn()(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr,
+    const CUresult cr = encode_fn()(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xh), dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");

@@ -202,6 +202,82 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, const float*
   }
 }
 
+// ------------------------------------------------------------------------------ fp16-normalised rows
+// The tcgen05 kernel takes fp16 token rows scaled by a power of two per row (row maximum in [128, 256), exact
+// for every element within 2^-22 of the maximum) plus that factor. Producing them directly here saves the
+// separate conversion pass over the activations.
+__device__ __forceinline__ float block_max(float v, float* red) {
+  for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float w = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int off = 16; off > 0; off >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, off));
+    if (threadIdx.x == 0) red[0] = w;
+  }
+  __syncthreads();
+  const float r = red[0];
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ int norm_exponent(float amax) {
+  int ex = 0;
+  if (amax > 0.f && isfinite(amax)) {
+    (void)frexpf(amax, &ex);
+    ex -= 8;  // amax * 2^-ex in [128, 256)
+  }
+  return ex;
+}
+
+// dst[p, :] = fp16(src[order[p] / top_k, :] * 2^-e_p), factor[p] = 2^e_p; one block per row, K <= 8 * 1024 per thread loop
+__global__ void gather_rows_norm_kernel(const __nv_bfloat16* __restrict__ src, const int64_t* __restrict__ order, int64_t K,
+                                        int top_k, __half* __restrict__ dst, float* __restrict__ factor) {
+  __shared__ float red[32];
+  const int64_t p = blockIdx.x;
+  const int64_t t = order ? order[p] / top_k : p;
+  const __nv_bfloat16* s = src + t * K;
+  float amax = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(s[k])));
+  const int ex = norm_exponent(block_max(amax, red));
+  const float down = ldexpf(1.f, -ex);
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) dst[p * K + k] = __float2half_rn(__bfloat162float(s[k]) * down);
+  if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
+}
+
+// h = bf16(w * silu(gate) * up) (the reference's rounding point), then the row normalised to fp16 as above
+__global__ void swiglu_norm_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route_weights,
+                                   const int64_t* __restrict__ order, int64_t inter, float limit, __half* __restrict__ h,
+                                   float* __restrict__ factor) {
+  __shared__ float red[32];
+  const int64_t p = blockIdx.x;
+  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const __nv_bfloat16* g = gu + p * 2 * inter;
+  const __nv_bfloat16* u = g + inter;
+  float amax = 0.f;
+  for (int pass = 0; pass < 2; ++pass) {
+    int ex = 0;
+    float down = 1.f;
+    if (pass == 1) {
+      ex = norm_exponent(block_max(amax, red));
+      down = ldexpf(1.f, -ex);
+      if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
+    }
+    for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) {
+      float gate = __bfloat162float(g[i]), up = __bfloat162float(u[i]);
+      if (limit > 0.f) {
+        up = fminf(fmaxf(up, -limit), limit);
+        gate = fminf(gate, limit);
+      }
+      float v = (gate / (1.f + expf(-gate))) * up;
+      if (route_weights) v = w * v;
+      v = __bfloat162float(__float2bfloat16_rn(v));
+      if (pass == 0) amax = fmaxf(amax, fabsf(v));
+      else h[p * inter + i] = __float2half_rn(v * down);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------- combine
 __global__ void invert_order_kernel(const int64_t* __restrict__ order, int64_t n, int64_t* __restrict__ inv) {
   const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -327,6 +403,30 @@ extern "C" int dst_swiglu(const void* gu_bf16, const float* route_weights, const
   swiglu_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gu_bf16), route_weights, order, n_rows, inter, limit,
       static_cast<__nv_bfloat16*>(h_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_gather_rows_norm(const void* src_bf16, const int64_t* order, int64_t n_rows, int64_t K, int top_k,
+                                    void* dst_f16, float* row_factor, dst_stream_t stream) {
+  if (n_rows < 0 || K <= 0 || top_k <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!src_bf16 || !dst_f16 || !row_factor) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  gather_rows_norm_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src_bf16), order, K, top_k, static_cast<__half*>(dst_f16), row_factor);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
+                               int64_t inter, float limit, void* h_f16, float* row_factor, dst_stream_t stream) {
+  if (n_rows < 0 || inter <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!gu_bf16 || !h_f16 || !row_factor) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  swiglu_norm_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu_bf16), route_weights, order, inter, limit, static_cast<__half*>(h_f16), row_factor);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

@@ -89,6 +89,22 @@ class TiledWeights:
         return out
 
 
+class NormRows:
+    """Token rows in the tcgen05 kernel's input format: fp16 ``data`` [rows, K], each row scaled by a power of
+    two so its largest magnitude lies in [128, 256), and ``factor`` [rows] float32 holding that power of two
+    (``dst_gather_rows_norm`` / ``dst_swiglu_norm`` produce them; see ``include/dst_b200.h``)."""
+
+    def __init__(self, data: torch.Tensor, factor: torch.Tensor):
+        self.data, self.factor = data, factor
+
+    def size(self, dim: int) -> int:
+        return self.data.size(dim)
+
+    @property
+    def device(self):
+        return self.data.device
+
+
 def tile_weights(packed: torch.Tensor, fmt: str, K: int) -> TiledWeights:
     """Canonical packed weights ``[E, N, packed_cols]`` (or ``[N, packed_cols]``) -> ``TiledWeights``: the one-time
     device re-layout the fast kernels read (the reference copies weights to the device at the same
@@ -142,7 +158,7 @@ def _offsets(offsets, E: int, T: int, device, validate: bool):
 
 
 def _grouped(lib, x, row_scale, offsets, packed_terms, scale_terms, K, group, fmt, out, accumulate, algo,
-             validate_offsets=True):
+             validate_offsets=True, act_code=None):
     """Shared launcher. packed_terms[i] [E, N, Kp] uint8, scale_terms[i] [E, N, G]."""
     code = _fmt_code(fmt)
     n_terms = len(packed_terms)
@@ -191,11 +207,12 @@ def _grouped(lib, x, row_scale, offsets, packed_terms, scale_terms, K, group, fm
         offs_dev, offs_host = _offsets(offsets, E, T, x.device, validate_offsets)
     pk = (ctypes.c_void_p * n_terms)(*[p.data_ptr() for p in raw])
     sc = (ctypes.c_void_p * n_terms)(*[s.data_ptr() for s in scale_terms])
-    ws_bytes = int(lib.dst_gemm_workspace_bytes(_ALGO[algo], _ACT[x.dtype], T, K)) if tiled else 0
+    act = _ACT[x.dtype] if act_code is None else act_code
+    ws_bytes = int(lib.dst_gemm_workspace_bytes(_ALGO[algo], act, T, K)) if tiled and act != _lib.ACT_F16_NORM else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
     with torch.cuda.device(x.device):
         rc = lib.dst_ternary_grouped_gemm(
-            out.data_ptr(), _OUT[out.dtype], int(bool(accumulate)), x.data_ptr(), _ACT[x.dtype],
+            out.data_ptr(), _OUT[out.dtype], int(bool(accumulate)), x.data_ptr(), act,
             row_scale.data_ptr() if row_scale is not None else None,
             offs_dev.data_ptr() if offs_dev is not None else None, offs_host,
             pk, _lib.LAYOUT_TILED if tiled else _lib.LAYOUT_CANONICAL, sc, n_terms, _SCALE[sdt], E, T, N, K, group, code,
@@ -284,6 +301,11 @@ def grouped_ternary_gemm_bf16(x: torch.Tensor, offsets, packed_terms, scale_term
     (the kernels then clamp row ranges to the row count instead).
     """
     _fmt_code(fmt)
+    norm = isinstance(x, NormRows)
+    if norm:
+        if row_scale is not None:
+            raise RuntimeError("normalised rows carry their own row factors")
+        x, row_scale = x.data, x.factor
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("the bf16 path takes bf16 or fp16 activations")
     lib = _require(backend)
@@ -292,6 +314,11 @@ def grouped_ternary_gemm_bf16(x: torch.Tensor, offsets, packed_terms, scale_term
     if out is None:
         out = torch.empty(x.size(0), packed_terms[0].size(1), dtype=out_dtype, device=x.device)
         accumulate = False
+    if norm:
+        if x.dtype != torch.float16 or not all(isinstance(p, TiledWeights) for p in packed_terms):
+            raise RuntimeError("normalised rows are fp16 and go with tiled weights")
+        return _grouped(lib, x.contiguous(), row_scale, offsets, list(packed_terms), [s.contiguous() for s in scale_terms], K, group,
+                        fmt, out, accumulate, "prefill", validate_offsets, act_code=_lib.ACT_F16_NORM)
     return _grouped(lib, x.contiguous(), row_scale, offsets,
                     [p if isinstance(p, TiledWeights) else p.contiguous() for p in packed_terms],
                     [s.contiguous() for s in scale_terms], K, group, fmt, out, accumulate, algo, validate_offsets)

@@ -78,8 +78,9 @@ class ExpertWeights:
 class B200Ops:
     """The CUDA implementation of the layer's steps (``libdst_b200.so`` through ctypes)."""
 
-    def __init__(self, algo: str = "auto"):
-        self.algo = algo
+    def __init__(self, algo: str = "auto", fused_norm: bool = True):
+        # fused_norm: gather and SwiGLU write the tcgen05 kernel's fp16 row format directly (no conversion pass)
+        self.algo, self.fused_norm = algo, fused_norm
 
     @staticmethod
     def _lib():
@@ -99,9 +100,20 @@ class B200Ops:
     def sort(self, ids: torch.Tensor, n_experts: int):
         return kb.sort_by_expert(ids.reshape(-1), n_experts)
 
-    def gather(self, x: torch.Tensor, order: torch.Tensor, top_k: int) -> torch.Tensor:
+    def _norm_ok(self, weights, rows: int) -> bool:
+        return (self.fused_norm and self.algo in ("auto", "prefill") and isinstance(weights[0], kb.TiledWeights)
+                and rows > 16 * weights[0].E)
+
+    def gather(self, x: torch.Tensor, order: torch.Tensor, top_k: int, for_weights=None):
         lib = self._lib()
         x = x.contiguous()
+        if for_weights is not None and x.dtype == torch.bfloat16 and self._norm_ok(for_weights, order.numel()):
+            out = torch.empty(order.numel(), x.size(1), dtype=torch.float16, device=x.device)
+            fac = torch.empty(order.numel(), dtype=torch.float32, device=x.device)
+            with torch.cuda.device(x.device):
+                _lib.check(lib.dst_gather_rows_norm(x.data_ptr(), order.data_ptr(), order.numel(), x.size(1), top_k, out.data_ptr(),
+                                                    fac.data_ptr(), kb._stream(x)))
+            return kb.NormRows(out, fac)
         out = torch.empty(order.numel(), x.size(1), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):
             _lib.check(lib.dst_gather_rows(x.data_ptr(), order.data_ptr(), order.numel(), x.size(1), top_k, out.data_ptr(),
@@ -113,8 +125,16 @@ class B200Ops:
                                             algo=self.algo, validate_offsets=False)
 
     def swiglu(self, gu: torch.Tensor, row_weights: torch.Tensor | None, order: torch.Tensor | None, inter: int,
-               limit: float) -> torch.Tensor:
+               limit: float, for_weights=None):
         lib = self._lib()
+        if for_weights is not None and self._norm_ok(for_weights, gu.size(0)):
+            h = torch.empty(gu.size(0), inter, dtype=torch.float16, device=gu.device)
+            fac = torch.empty(gu.size(0), dtype=torch.float32, device=gu.device)
+            with torch.cuda.device(gu.device):
+                _lib.check(lib.dst_swiglu_norm(gu.data_ptr(), row_weights.data_ptr() if row_weights is not None else None,
+                                               order.data_ptr() if order is not None else None, gu.size(0), inter,
+                                               ctypes.c_float(limit), h.data_ptr(), fac.data_ptr(), kb._stream(gu)))
+            return kb.NormRows(h, fac)
         h = torch.empty(gu.size(0), inter, dtype=torch.bfloat16, device=gu.device)
         with torch.cuda.device(gu.device):
             _lib.check(lib.dst_swiglu(gu.data_ptr(), row_weights.data_ptr() if row_weights is not None else None,
@@ -145,15 +165,24 @@ class MoELayer:
         """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows."""
         w = self.w
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
-        h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit)
+        if getattr(self.ops, "fused_norm", False):
+            h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit, for_weights=w.w2_packed)
+        else:
+            h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit)
         return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
+
+    def gather_for_experts(self, x: torch.Tensor, order: torch.Tensor, top_k: int):
+        """Rows in expert-sorted order, in the format the first expert GEMM reads fastest."""
+        if getattr(self.ops, "fused_norm", False):
+            return self.ops.gather(x, order, top_k, for_weights=self.w.w13_packed)
+        return self.ops.gather(x, order, top_k)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """x [T, hidden] bf16, router logits [T, E] f32 -> y [T, hidden] bf16."""
         T = x.size(0)
         weights, ids = self.ops.route(logits, self.top_k, self.route_scale)
         order, offsets = self.ops.sort(ids, self.w.n_experts)
-        xs = self.ops.gather(x, order, self.top_k)
+        xs = self.gather_for_experts(x, order, self.top_k)
         down = self.experts_forward(xs, offsets, weights.reshape(-1), order)
         return self.ops.combine(down, order, ids, T, self.top_k)
 
@@ -217,7 +246,7 @@ class ExpertParallelMoE:
         # received rows are ordered (source rank, local expert): sort them by local expert
         local_ids = torch.arange(El, device=x.device, dtype=torch.int64).repeat(W).repeat_interleave(recv_counts.view(-1), output_size=R)
         order2, offsets2 = self.ops.sort(local_ids, El)
-        xs2 = self.ops.gather(xr, order2, 1)
+        xs2 = self.local.gather_for_experts(xr, order2, 1)
         down2 = self.local.experts_forward(xs2, offsets2, wr, order2)
         back = torch.empty_like(down2)
         back[order2] = down2  # undo the local sort: row p of down2 is received row order2[p]

@@ -48,7 +48,10 @@ enum {
 enum { DST_FMT_TQ1 = 1, DST_FMT_TQ2 = 2 };           /* boilerplate/kernels/ternary_cuda.py:46-49 */
 enum { DST_SCALE_F16 = 0, DST_SCALE_F32 = 1, DST_SCALE_BF16 = 2 };
 enum { DST_OUT_F32 = 0, DST_OUT_BF16 = 1, DST_OUT_F16 = 2 };
-enum { DST_ACT_BF16 = 0, DST_ACT_F16 = 1, DST_ACT_I8 = 2 };
+/* F16_NORM: fp16 rows the caller has already scaled by a power of two per row (row maximum in [128, 256)), with
+ * the factors in row_scale; dst_gather_rows_norm / dst_swiglu_norm produce them. The tcgen05 kernel then needs
+ * no conversion pass and no workspace. */
+enum { DST_ACT_BF16 = 0, DST_ACT_F16 = 1, DST_ACT_I8 = 2, DST_ACT_F16_NORM = 3 };
 /* Kernel choice. AUTO picks DECODE for few rows per expert, PREFILL for many, and GENERIC for
  * shapes the two fast kernels do not cover. */
 enum { DST_ALGO_AUTO = 0, DST_ALGO_GENERIC = 1, DST_ALGO_DECODE = 2, DST_ALGO_PREFILL = 3 };
@@ -180,6 +183,17 @@ int dst_gather_rows(const void* src, const int64_t* order, int64_t n_rows, int64
  */
 int dst_swiglu(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
                int64_t inter, float limit, void* h_bf16, dst_stream_t stream);
+
+/*
+ * The same two steps producing the tcgen05 kernel's input format directly (DST_ACT_F16_NORM): fp16 rows scaled
+ * by 2^-e per row so the row maximum lies in [128, 256), and row_factor[p] = 2^e. Values are the reference's
+ * (bf16 activations; bf16-rounded SwiGLU output) times an exact power of two. `order` may be NULL in
+ * dst_gather_rows_norm (identity: convert rows in place order).
+ */
+int dst_gather_rows_norm(const void* src_bf16, const int64_t* order, int64_t n_rows, int64_t K, int top_k,
+                         void* dst_f16, float* row_factor, dst_stream_t stream);
+int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
+                    int64_t inter, float limit, void* h_f16, float* row_factor, dst_stream_t stream);
 
 /*
  * Combine: y[t, :] = bf16( sum over the token's top_k slots, in increasing expert id, of
