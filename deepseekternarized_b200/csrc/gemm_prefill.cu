@@ -1,43 +1,43 @@
 // Prefill grouped ternary GEMM for sm_100a: tcgen05 MMA with TMEM accumulators, TMA-fed activations,
-// warp-specialised dequantisation of packed trits into fp16 shared-memory tiles.
+// warp-specialised dequantisation of packed trits straight into tensor memory.
 //
 // Problem (per expert e, rows ra..rb of the expert-sorted activations):
 //     out[m, n] = row_scale[m] * sum_k x[m, k] * W_e[n, k],   W_e[n, k] = sum_i scale_i[e, n, k/128] * trit_i[e, n, k]
 //
-// Mapping ("swap AB"): the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), up to 256
-// token rows are the MMA N dimension (TMEM columns), so tiles stay full when an expert has few rows.
+// Mapping ("swap AB"): the 128 weight rows of a tile are the MMA M dimension (TMEM lanes), the token rows of
+// one expert (up to 320 per tile) are the MMA N dimension (TMEM columns), so tiles stay full when an expert
+// has few rows and an expert with up to 320 rows has its weights dequantised ONCE per 128-row weight tile.
 // Both operands are fp16, 64 K-elements per pipeline stage:
 //   A (weights)      packed 8 KB slabs of the tiled layout (layout_kernels.cu) arrive by cp.async.bulk in a
-//                    two-slot ring; 16 dequant warps turn them into scale * trit, exact in fp16, and write
-//                    them with tcgen05.st straight into TENSOR MEMORY (lane = weight row, one 32-bit column
-//                    = two consecutive K elements; 32 columns per stage, ring of 8 stages): the MMA takes A
-//                    from TMEM, so the dequantised tile never passes through shared memory
+//                    small ring; 16 dequant warps turn them into scale * trit, exact in fp16, and write them
+//                    with tcgen05.st straight into TENSOR MEMORY (lane = weight row, one 32-bit column = two
+//                    consecutive K elements; 32 columns per stage): the MMA takes A from TMEM, so the
+//                    dequantised tile never passes through shared memory
 //   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA) into K-major,
-//                    128-byte-swizzled shared-memory stages
-//   D (accumulator)  fp32 in TMEM columns 0..255; columns 256..511 are the A ring
+//                    128-byte-swizzled shared-memory stages (one box for up to 256 rows, two for more)
+//   D (accumulator)  fp32 in TMEM columns 0..319 (tiles of more than 256 token rows are two MMAs per K step,
+//                    each over half of the rows); columns 320..511 hold the A ring (stage s = slot s)
 // Shared-memory bandwidth is what bounds this kernel when A goes through shared memory (measured: the MMA
 // issuer stalled ~1100 cycles per 512-cycle stage); with A in TMEM only B is written and read there.
 // bf16 activations are converted once to fp16 with a power-of-two factor per row (exact for every
 // element within 2^-22 of the row's absolute maximum); the factor comes back through row_scale.
 // tcgen05 kind::f16 refuses an fp16 A with a bf16 B (illegal instruction), hence the conversion.
 //
-// CTA pairs (template parameter CG = 2, used when N is a multiple of 256): two CTAs of a cluster share
-// one tile of 256 weight rows x up to 256 token rows. Each CTA dequantises its own 128 weight rows and
-// loads HALF of the token rows; the pair's leader issues tcgen05.mma.cta_group::2 (M = 256), which reads
-// the A tile of both CTAs and both halves of B. Per SM this halves the activation bytes fetched from L2
-// and held in shared memory per FLOP, which is what bounds the single-CTA form (its 32 KB B stages are
-// too few to cover the TMA latency). The stage-full barrier lives in the leader and collects the TMA
-// bytes and the dequant arrivals of both CTAs; tcgen05.commit multicasts the stage-free and
-// accumulator-full signals to both. Every TMA load writes into the shared memory of the CTA that issues it.
-//
-// Warp roles (704 threads, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer for B and bulk copies of packed slabs
-//   warp 1      MMA issuer, owns the TMEM allocation (in the non-leader CTA of a pair: relays "my A tile is ready")
-//   warps 2-5   epilogue (TMEM -> registers -> global)
-//   warps 6-21  dequant producers for A, in four groups of four warps: group g owns the stages with index = g
-//               (mod 4), so four stages are dequantised at once (each warp's instruction stream is a long
-//               dependent chain; one group per stage could not keep up with the MMAs); inside a group warp w
-//               owns the 32 weight rows of TMEM lane quarter w % 4, one thread per row per 64-trit stage
+// Warp roles (736 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer for B (one thread)
+//   warp 1      MMA issuer (one thread), owns the TMEM allocation
+//   warp 2      bulk-copy producer of the packed slabs (one thread)
+//   warps 3-6   epilogue: TMEM -> registers -> global, one warp per TMEM lane quarter (warp id % 4)
+//   warps 7-22  dequant producers for A, in four groups of four warps: group g owns the stages with global
+//               index = g (mod 4), so four stages are dequantised at once (each warp's instruction stream is a
+//               long dependent chain; one group per stage could not keep up with the MMAs); inside a group
+//               the warp with id % 4 == q owns the 32 weight rows of TMEM lane quarter q, one thread per row
+//               per 64-trit stage
+// The accumulator is drained by warps that do nothing else. A variant in which the 20 dequant warps also drained
+// it (tcgen05.ld in the same, register-starved instruction stream as the dequantisation) raised "unspecified
+// launch failure" on the GPU although the same code with extra progress stores passed; tcgen05.ld writes its
+// destination registers asynchronously, so that role keeps few live registers and nothing between the load and
+// tcgen05.wait::ld.
 //
 // Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all
 // roles leave their loops, the CTA frees TMEM and the kernel records DST_ERR_TIMEOUT in the status word.
@@ -50,16 +50,21 @@
 namespace dst {
 namespace {
 
-constexpr int PF_THREADS = 704;            // 6 control/epilogue warps + 16 dequant warps
-constexpr int PF_DQ_WARPS = 16;
-constexpr int PF_TN = 256;            // token rows per tile (TMEM columns per accumulator buffer)
-constexpr int PF_A_COLS = 32;         // TMEM columns of one A stage: 64 fp16 per weight row
-constexpr int PF_A_RING = 8;          // A stages in TMEM (columns 256..511)
-constexpr int PF_B_BYTES = PF_TN * 128;
-constexpr int PF_LUT_BYTES = 2 * 256 * 8 * 16;  // TQ1: two alignments x 256 byte values x 8 bank replicas x 16 B
-constexpr int PF_SLAB = 8192;                   // one (row tile, superblock) slab of packed weights
-constexpr bool kUseCtaPairs = false;
-constexpr int PF_SMEM_MAX = 232448;             // 227 KB of dynamic shared memory per CTA
+constexpr int PF_CTRL_WARPS = 3;
+constexpr int PF_EPI_WARPS = 4;              // accumulator drain, one warp per TMEM lane quarter
+constexpr int PF_GROUPS = 4;                 // dequant warp groups (4 warps each, one per TMEM lane quarter)
+constexpr int PF_DQ_WARPS = 4 * PF_GROUPS;
+constexpr int PF_DQ_WARP0 = PF_CTRL_WARPS + PF_EPI_WARPS;
+constexpr int PF_THREADS = 32 * (PF_DQ_WARP0 + PF_DQ_WARPS);
+constexpr int PF_TN_MAX = 320;               // token rows per tile at most = accumulator columns in TMEM
+constexpr int PF_A_COLS = 32;                // TMEM columns of one A stage: 64 fp16 per weight row
+constexpr int PF_MAX_STAGES = 6;             // 320 + 6 * 32 = 512 TMEM columns
+constexpr int PF_MAX_SLABS = 3;
+constexpr int PF_LUT_BYTES = 256 * 16 * 4;   // TQ1: 256 byte values x 16 bank replicas x 4 B
+constexpr int PF_SLAB = 8192;                // one (row tile, superblock) slab of packed weights
+constexpr int PF_MAX_E = 1023;               // experts per launch: two int arrays of E + 1 entries live in shared memory
+constexpr int PF_SMEM_MAX = 232448;          // 227 KB of shared memory per CTA
+constexpr int PF_SMEM_STATIC = 512;          // allowance for the statically declared barriers and flags
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 __device__ int g_device_status = 0;
@@ -72,14 +77,16 @@ __device__ unsigned long long g_role_timers[64];
 #define RT_NOW() clock64()
 #define RT_ADD(slot, v) atomicAdd(&g_role_timers[slot], (unsigned long long)(v))
 #define RT_WAIT(acc, call) [&]() { const long long t0__ = clock64(); const bool r__ = (call); acc += clock64() - t0__; return r__; }()
+#define RT_SPAN(acc, t0) acc += clock64() - (t0)
 #else
 #define RT_DECL(...)
 #define RT_NOW() 0
 #define RT_ADD(slot, v)
 #define RT_WAIT(acc, call) (call)
+#define RT_SPAN(acc, t0)
 #endif
 
-// One tensor map per TMA box height (16, 32, ... 256 token rows), so a stage is always one TMA instruction.
+// One tensor map per TMA box height (16, 32, ... 256 token rows), so half a stage or a whole one is one TMA instruction.
 struct TmaMaps {
   CUtensorMap m[16];
 };
@@ -93,7 +100,10 @@ struct PrefillParams {
   void* out;
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S, kstages;
-  int nstage_log2;  // log2 of the stage ring depth (2, 4 or 8 stages), chosen by the host from the shared-memory budget
+  // chosen by the host from the shared-memory budget
+  int tn_max;       // token rows per tile at most (a multiple of 32, <= PF_TN_MAX)
+  int nb;           // depth of the stage ring (B stage in shared memory + A slot in TMEM), 2..6
+  int nslab;        // slots of the packed-slab ring, 2 or 3
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -115,8 +125,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 // Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed. BACKOFF sleeps between
-// polls: for roles that wait long (epilogue, producer), so their polling does not take issue slots from the
-// dequant warps.
+// polls: for roles that wait long, so their polling does not take issue slots from the dequant warps.
 template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;
@@ -145,10 +154,6 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_f16_ts_2cta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
 // 8 consecutive 32-bit columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint32_t* v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
@@ -161,33 +166,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
-__device__ __forceinline__ void umma_commit_2cta(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"((uint16_t)3) : "memory");
-}
-// TMA load into this CTA's shared memory whose completion bytes are counted on a barrier of the pair's leader
-__device__ __forceinline__ void tma_load_2d_2cta(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
-  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 #define TMEM_LD_32(v, taddr)                                                                                              \
@@ -206,107 +187,108 @@ __device__ __forceinline__ void tma_load_2d_2cta(uint32_t dst, const CUtensorMap
                : "r"(taddr))
 
 // ------------------------------------------------------------------------------------------ tile walk
+// Token rows a tile of `rows` rows occupies in the MMA N dimension: a multiple of 16 up to 256 (one MMA per K
+// step), a multiple of 32 above (two MMAs, each over half of the rows, and N must be a multiple of 16).
+__device__ __forceinline__ int tile_neff(int rows) { return rows <= 256 ? (rows + 15) & ~15 : (rows + 31) & ~31; }
+
 // Tiles are numbered expert-major, then token tile, then weight-row tile (fastest), so the CTAs that run
-// at the same time share an expert's activation rows and packed weights in L2. Every role walks the
-// same sequence with its own copy of this state.
-struct TileWalker {
-  const int64_t* offsets;
-  int E, T, NT;      // NT: tiles along the weight rows (pairs of 128-row tiles when CTA pairs are used)
-  int row_round;     // token rows per tile are a multiple of this (16, or 32 for CTA pairs)
-  int e = -1, mt_count = 0, mt_rows = 0;
-  long long before = 0;
-  int64_t ra = 0, rb = 0;
-  __device__ bool seek(long long t, int& e_out, int& nt, int& row0, int& rows) {
-    while (e < 0 || t >= before + (long long)mt_count * NT) {
-      if (e >= 0) before += (long long)mt_count * NT;
-      if (++e >= E) return false;
-      row_range(offsets, e, T, ra, rb);
-      mt_count = (int)((rb - ra + PF_TN - 1) / PF_TN);
-      // an expert with more rows than one tile holds is split evenly (whole multiples of row_round), so no
-      // tile repeats the dequantisation of the weights for a handful of left-over rows
-      mt_rows = mt_count > 0 ? (int)((((rb - ra + mt_count - 1) / mt_count) + row_round - 1) / row_round * row_round) : 0;
-    }
-    const long long local = t - before;
-    const int mt = (int)(local / NT);
-    nt = (int)(local - (long long)mt * NT);
-    row0 = (int)ra + mt * mt_rows;
-    rows = (int)(rb - row0 < mt_rows ? rb - row0 : mt_rows);
-    if (rows < 0) rows = 0;
-    e_out = e;
-    return true;
-  }
-};
+// at the same time share an expert's activation rows in L2. The kernel keeps two int arrays in shared memory:
+// offs[e] = first token row of expert e (clamped to [0, T]) and tpre[e] = number of tiles of the experts
+// before e. A tile index is resolved with a short forward scan from the expert of the previous tile.
+__device__ __forceinline__ int expert_tiles(const int* offs, int e, int tn_max, int NT) {
+  const int n = offs[e + 1] - offs[e];
+  return n > 0 ? (n + tn_max - 1) / tn_max * NT : 0;
+}
+// e: in = an expert at or before the tile's expert, out = the tile's expert. t must be < tpre[E].
+__device__ __forceinline__ void tile_seek(const PrefillParams& p, const int* offs, const int* tpre, int t, int& e, int& nt, int& row0,
+                                          int& rows) {
+  while (tpre[e + 1] <= t) ++e;
+  const int ra = offs[e], rb = offs[e + 1];  // rb > ra: the expert has tiles
+  const int n = rb - ra;
+  const int mt_count = (n + p.tn_max - 1) / p.tn_max;
+  // an expert with more rows than one tile holds is split evenly, so no tile repeats the dequantisation
+  // of the weights for a handful of left-over rows
+  const int mt_rows = tile_neff((n + mt_count - 1) / mt_count);
+  const unsigned local = (unsigned)(t - tpre[e]);
+  const unsigned mt = local / (unsigned)p.NT;
+  nt = (int)(local - mt * (unsigned)p.NT);
+  row0 = ra + (int)mt * mt_rows;
+  rows = rb - row0 < mt_rows ? rb - row0 : mt_rows;
+}
 
 // ------------------------------------------------------------------------------------------ dequant
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
-// TQ2, tiled word format: trit 2j in bits [2j, 2j+1], trit 2j+1 in bits [16+2j, 17+2j] (digit u = t + 1).
-// (w & (0x00030003 << 2j')) | 0x64006400 is the fp16 pair 1024 + u * 4^j'; one fused multiply-add maps it
-// to u - 1 exactly; one multiply applies the group scale exactly.
+// Field f (0..4) of a word that holds trit digits u = t + 1 as 2-bit fields, an even trit in bits [2f, 2f+1]
+// and the odd trit after it in bits [16+2f, 17+2f]: (w & (0x00030003 << 2f)) | 0x64006400 is the fp16 pair
+// 1024 + u * 4^f; one fused multiply-add maps it to u - 1 exactly.
+template <int F>
+__device__ __forceinline__ __half2 trit_pair(uint32_t w) {
+  constexpr float m = F == 0 ? 1.f : F == 1 ? 0.25f : F == 2 ? 0.0625f : F == 3 ? 0.015625f : 0.00390625f;
+  constexpr float a = F == 0 ? -1025.f : F == 1 ? -257.f : F == 2 ? -65.f : F == 3 ? -17.f : -5.f;
+  return __hfma2(bits_h2((w & (0x00030003u << (2 * F))) | 0x64006400u), __floats2half2_rn(m, m), __floats2half2_rn(a, a));
+}
+template <bool FIRST>
+__device__ __forceinline__ void put(__half2& acc, __half2 t, __half2 s2) {
+  acc = FIRST ? __hmul2(t, s2) : __hfma2(t, s2, acc);  // the group scale is applied exactly (trit in {-1, 0, 1})
+}
+
+// TQ2, tiled word format: 16 trits, trit 2j in field j of the low half, trit 2j+1 in field j of the high half.
 template <bool FIRST>
 __device__ __forceinline__ void tq2_word(uint32_t w, __half2 s2, __half2* acc /* 8 */) {
-  const uint32_t magic = 0x64006400u;
   const uint32_t w2 = w >> 10;
-  const __half2 m0 = __floats2half2_rn(1.f, 1.f), m1 = __floats2half2_rn(0.25f, 0.25f), m2 = __floats2half2_rn(0.0625f, 0.0625f),
-                m3 = __floats2half2_rn(0.015625f, 0.015625f), m4 = __floats2half2_rn(0.00390625f, 0.00390625f);
-  const __half2 a0 = __floats2half2_rn(-1025.f, -1025.f), a1 = __floats2half2_rn(-257.f, -257.f), a2 = __floats2half2_rn(-65.f, -65.f),
-                a3 = __floats2half2_rn(-17.f, -17.f), a4 = __floats2half2_rn(-5.f, -5.f);
-  __half2 t[8];
-  t[0] = __hfma2(bits_h2((w & 0x00030003u) | magic), m0, a0);
-  t[1] = __hfma2(bits_h2((w & 0x000C000Cu) | magic), m1, a1);
-  t[2] = __hfma2(bits_h2((w & 0x00300030u) | magic), m2, a2);
-  t[3] = __hfma2(bits_h2((w & 0x00C000C0u) | magic), m3, a3);
-  t[4] = __hfma2(bits_h2((w & 0x03000300u) | magic), m4, a4);
-  t[5] = __hfma2(bits_h2((w2 & 0x00030003u) | magic), m0, a0);
-  t[6] = __hfma2(bits_h2((w2 & 0x000C000Cu) | magic), m1, a1);
-  t[7] = __hfma2(bits_h2((w2 & 0x00300030u) | magic), m2, a2);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = FIRST ? __hmul2(t[j], s2) : __hfma2(t[j], s2, acc[j]);
+  put<FIRST>(acc[0], trit_pair<0>(w), s2);
+  put<FIRST>(acc[1], trit_pair<1>(w), s2);
+  put<FIRST>(acc[2], trit_pair<2>(w), s2);
+  put<FIRST>(acc[3], trit_pair<3>(w), s2);
+  put<FIRST>(acc[4], trit_pair<4>(w), s2);
+  put<FIRST>(acc[5], trit_pair<0>(w2), s2);
+  put<FIRST>(acc[6], trit_pair<1>(w2), s2);
+  put<FIRST>(acc[7], trit_pair<2>(w2), s2);
 }
 
-// TQ1: the thread needs the 16 trits [tau, tau + 16) of its row-superblock, tau = 16 q. They start at
-// trit `o` of byte b0 = tau / 5 and always lie inside 4 consecutive bytes. Bytes go through a shared-memory
-// table of unscaled fp16 trits in two alignments (first trit in the low or the high half of a pair), so
-// pairs never need re-alignment: entry even = (v0,v1)(v2,v3)(v4,0), entry odd = (0,v0)(v1,v2)(v3,v4).
-// Byte i lands at pair index floor((5 i - o) / 2); neighbouring bytes share one pair, merged with OR.
-template <int O, bool FIRST>
-__device__ __forceinline__ void tq1_decode(uint32_t win, uint32_t lut_addr, __half2 s2, __half2* acc /* 8 */) {
-  uint32_t out[8];
-#pragma unroll
-  for (int h = 0; h < 8; ++h) out[h] = 0u;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t idx = (i == 0 ? (win << 7) : (win >> (8 * i - 7))) & 0x7F80u;
-    const int p = 5 * i - O;                       // position of the byte's first trit
-    const int odd = ((p % 2) + 2) % 2;             // first trit lands in the high half
-    const int h0 = (p - odd) / 2;                  // floor(p / 2), exact for negative p too
-    uint32_t t0, t1, t2, t3;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t0), "=r"(t1), "=r"(t2), "=r"(t3) : "r"(lut_addr + idx + odd * 32768u));
-    (void)t3;
-    if (h0 >= 0 && h0 < 8) out[h0] |= t0;
-    if (h0 + 1 >= 0 && h0 + 1 < 8) out[h0 + 1] |= t1;
-    if (h0 + 2 >= 0 && h0 + 2 < 8) out[h0 + 2] |= t2;
-  }
-#pragma unroll
-  for (int h = 0; h < 8; ++h) acc[h] = FIRST ? __hmul2(bits_h2(out[h]), s2) : __hfma2(bits_h2(out[h]), s2, acc[h]);
+// TQ1, tiled grouping (layout_kernels.cu): the 64 trits of stage s of a row-superblock are the 12 bytes
+// 12 s .. 12 s + 11 (5 trits each) plus digit s of the 4 bytes 60..63. A shared-memory table maps a byte to its
+// five digits as 2-bit fields placed for BOTH positions a byte can have in a pair of bytes (10 trits = 5 fp16
+// pairs): as the first byte its digits 0,2,4 are the even trits of pairs 0,1,2 and digits 1,3 the odd trits of
+// pairs 0,1; as the second byte digit 0 is the odd trit of pair 2, digits 1,3 the even and digits 2,4 the odd
+// trits of pairs 3,4. The two placements use disjoint bits, so one AND-OR merges two table entries into a
+// word of the TQ2 pair format above.
+constexpr uint32_t TQ1_FIRST_MASK = 0x000F003Fu, TQ1_SECOND_MASK = 0x03F003C0u;
+__host__ __device__ inline uint32_t tq1_table_entry(uint32_t byte) {
+  const uint32_t f = tq1_fields(byte);
+  const uint32_t d0 = f & 3u, d1 = (f >> 2) & 3u, d2 = (f >> 4) & 3u, d3 = (f >> 6) & 3u, d4 = (f >> 8) & 3u;
+  const uint32_t first = d0 | (d2 << 2) | (d4 << 4) | (d1 << 16) | (d3 << 18);
+  const uint32_t second = (d0 << 20) | (d1 << 6) | (d2 << 22) | (d3 << 8) | (d4 << 24);
+  return first | second;
 }
-
+__device__ __forceinline__ uint32_t tq1_lookup(uint32_t lut_addr, uint32_t word, int byte) {
+  const uint32_t idx = byte == 0 ? (word << 6) & 0x3FC0u : (word >> (8 * byte - 6)) & 0x3FC0u;  // byte value * 64
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lut_addr + idx));
+  return v;
+}
+// w[0..2]: the stage's 12 own bytes, w[3]: bytes 60..63 of the row-superblock; sbk: stage inside the superblock
 template <bool FIRST>
-__device__ __forceinline__ void tq1_dispatch(int o, uint32_t win, uint32_t lut_addr, __half2 s2, __half2* acc) {
-  switch (o) {
-    case 0: tq1_decode<0, FIRST>(win, lut_addr, s2, acc); break;
-    case 1: tq1_decode<1, FIRST>(win, lut_addr, s2, acc); break;
-    case 2: tq1_decode<2, FIRST>(win, lut_addr, s2, acc); break;
-    case 3: tq1_decode<3, FIRST>(win, lut_addr, s2, acc); break;
-    default: tq1_decode<4, FIRST>(win, lut_addr, s2, acc); break;
+__device__ __forceinline__ void tq1_stage(const uint32_t* w, int sbk, uint32_t lut_addr, __half2 s2, __half2* acc /* 32 */) {
+#pragma unroll
+  for (int q = 0; q < 6; ++q) {
+    const uint32_t c0 = tq1_lookup(lut_addr, w[(2 * q) >> 2], (2 * q) & 3);
+    const uint32_t c1 = tq1_lookup(lut_addr, w[(2 * q + 1) >> 2], (2 * q + 1) & 3);
+    const uint32_t m = (c0 & TQ1_FIRST_MASK) | (c1 & TQ1_SECOND_MASK);
+    put<FIRST>(acc[5 * q + 0], trit_pair<0>(m), s2);
+    put<FIRST>(acc[5 * q + 1], trit_pair<1>(m), s2);
+    put<FIRST>(acc[5 * q + 2], trit_pair<2>(m), s2);
+    put<FIRST>(acc[5 * q + 3], trit_pair<3>(m), s2);
+    put<FIRST>(acc[5 * q + 4], trit_pair<4>(m), s2);
   }
-}
-
-// ------------------------------------------------------------------------------------------ the kernel
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+  // trits 60..63: digit sbk of bytes 60..63; as a "first byte" entry digit d sits at bit (d >> 1) * 2 + (d & 1) * 16
+  const int sh = (sbk >> 1) * 2 + (sbk & 1) * 16;
+  const uint32_t e0 = (tq1_lookup(lut_addr, w[3], 0) >> sh) & 3u, e1 = (tq1_lookup(lut_addr, w[3], 1) >> sh) & 3u;
+  const uint32_t e2 = (tq1_lookup(lut_addr, w[3], 2) >> sh) & 3u, e3 = (tq1_lookup(lut_addr, w[3], 3) >> sh) & 3u;
+  put<FIRST>(acc[30], trit_pair<0>(e0 | (e1 << 16)), s2);
+  put<FIRST>(acc[31], trit_pair<0>(e2 | (e3 << 16)), s2);
 }
 
 // Scale of group g (0..7 inside the 8 scales held in `sc`), as an fp16 pair.
@@ -316,287 +298,270 @@ __device__ __forceinline__ __half2 pick_scale(const uint4& sc, int g) {
   return bits_h2(h | (h << 16));
 }
 
+// Drains a finished tile's accumulator: 32-column chunks col_first, col_first + col_step, ... of the warp's
+// TMEM lane quarter -> registers -> global (thread = output column n, chunk column j = token row j).
+__device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem, int col_first, int col_step, int r, uint32_t tfull_bar,
+                                        uint32_t tempty_bar, volatile int* abort_flag, int d_nt, int d_row0, int d_rows,
+                                        uint32_t d_tile) {
+  const int lane = r & 31;
+  const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
+  if (!mbar_wait<true>(tfull_bar, d_tile & 1u, abort_flag)) return false;
+  // Lanes leave the polling loop (and its per-thread sleeps) one by one; the .sync.aligned tcgen05 instructions
+  // below must be executed by the whole warp together.
+  __syncwarp();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const int dn = d_nt * 128 + r;
+  const bool n_ok = dn < p.N;
+  const int n_eff = tile_neff(d_rows);
+  // this thread owns output column dn; consecutive token rows are p.N elements apart
+  const size_t esz = p.out_dtype == DST_OUT_F32 ? 4 : 2;
+  const size_t ostep = (size_t)p.N * esz;
+  uint8_t* obase = static_cast<uint8_t*>(p.out) + ((size_t)d_row0 * p.N + (n_ok ? dn : 0)) * esz;
+  for (int c0 = col_first; c0 < n_eff; c0 += col_step) {
+    const float rs_lane = (p.row_scale && c0 + lane < d_rows) ? p.row_scale[d_row0 + c0 + lane] : 1.f;
+    uint32_t v[32];
+    if (c0 + 32 <= n_eff) {
+      TMEM_LD_32(v, tmem + lane_base + c0);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+      TMEM_LD_16(v, tmem + lane_base + c0);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int j = 16; j < 32; ++j) v[j] = 0u;
+    }
+    const int lim = n_ok ? d_rows - c0 : 0;  // token rows of this chunk that exist (and a column that exists)
+    uint8_t* optr = obase + (size_t)c0 * ostep;
+    if (p.out_dtype == DST_OUT_BF16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+        if (j < lim) *reinterpret_cast<__nv_bfloat16*>(optr) = __float2bfloat16_rn(val);
+        optr += ostep;
+      }
+    } else if (p.out_dtype == DST_OUT_F16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+        if (j < lim) *reinterpret_cast<__half*>(optr) = __float2half_rn(val);
+        optr += ostep;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+        if (j < lim) {
+          float* o = reinterpret_cast<float*>(optr);
+          *o = p.accumulate ? *o + val : val;
+        }
+        optr += ostep;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) mbar_arrive(tempty_bar);
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
 // Shared memory map (dynamic, 1024-byte aligned), per CTA:
-//   [0, nstage * stage_bytes)      B stage ring: 256 token rows x 64 fp16 = 32 KB for one CTA, 128 rows = 16 KB for
-//                                  each CTA of a pair; nstage <= 8 and stage s pairs with A ring slot s in TMEM
-//   then 2 * n_terms * 8 KB        packed-weight slabs: slot-major, one 8 KB slab per stacked term
-//   then 64 KB (TQ1 only)          table of unscaled fp16 trits
-template <int FMT, int CG, int TERMS>
+//   [0, nb * tn_max * 128)          B stage ring: tn_max token rows x 64 fp16 per stage; stage s pairs with A slot s in TMEM
+//   then nslab * n_terms * 8 KB     packed-weight slabs: slot-major, one 8 KB slab per stacked term
+//   then 16 KB (TQ1 only)           table of digit fields, see tq1_table_entry
+//   then 2 x 4 KB                   offs[E + 1], tpre[E + 1] (see tile_seek)
+template <int FMT, int TERMS>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
-  constexpr int SPB = FMT == 2 ? 4 : 5;  // 64-trit stages per 64-byte superblock
-  constexpr int MAX_STAGE = PF_A_RING;
-  constexpr int B_BYTES = PF_B_BYTES / CG;
-  constexpr int STAGE_BYTES = B_BYTES;
-  constexpr int ROUND = CG == 2 ? 32 : 16;  // token rows per tile are padded to this for the MMA N
+  constexpr int SPB = FMT == 2 ? 4 : 5;  // 64-trit stages per 64-byte row-superblock
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int NSTAGE = 1 << p.nstage_log2;
-  const uint32_t smask = (uint32_t)NSTAGE - 1u, sshift = (uint32_t)p.nstage_log2;
-  uint8_t* slabs = smem + NSTAGE * STAGE_BYTES;
-  uint8_t* lut = slabs + 2 * p.n_terms * PF_SLAB;  // TQ1 only
-  __shared__ uint64_t bar_full[MAX_STAGE], bar_afull[MAX_STAGE], bar_empty[MAX_STAGE], bar_tfull[1], bar_tempty[1], bar_pfull[2], bar_pempty[2];
+  const uint32_t NB = (uint32_t)p.nb;
+  const uint32_t stage_bytes = (uint32_t)p.tn_max * 128u;
+  uint8_t* slabs = smem + NB * stage_bytes;
+  uint8_t* lut = slabs + (size_t)p.nslab * p.n_terms * PF_SLAB;  // TQ1 only
+  int* offs = reinterpret_cast<int*>(lut + (FMT == 1 ? PF_LUT_BYTES : 0));
+  int* tpre = offs + (PF_MAX_E + 1);
+  __shared__ uint64_t bar_full[PF_MAX_STAGES], bar_empty[PF_MAX_STAGES], bar_tfull[1], bar_tempty[1], bar_pfull[PF_MAX_SLABS],
+      bar_pempty[PF_MAX_SLABS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;  // 0 = the pair's leader
-  const bool leader = rank == 0;
   if (tid == 0) {
     abort_s = 0;
-    for (int s = 0; s < MAX_STAGE; ++s) {
-      // stage full (leader): the TMA producer's expect_tx arrive + one arrive per warp of the dequant group that owns the stage
-      // + one relayed arrive for the peer's A tile
-      mbar_init(smem_u32(&bar_full[s]), 1 + 4 + (CG - 1));
-      mbar_init(smem_u32(&bar_afull[s]), 4);  // non-leader CTA of a pair: its own A tile is written (4 warps per stage)
-      mbar_init(smem_u32(&bar_empty[s]), 1);  // tcgen05.commit (multicast to both CTAs of a pair)
+    for (int s = 0; s < PF_MAX_STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1 + 4);  // the TMA producer's expect_tx arrive + one arrive per warp of the dequant group that owns the stage
+      mbar_init(smem_u32(&bar_empty[s]), 1);     // tcgen05.commit: the MMAs that read the stage are done
     }
-    mbar_init(smem_u32(&bar_tfull[0]), 1);        // tcgen05.commit after the tile's last MMA
-    mbar_init(smem_u32(&bar_tempty[0]), 4 * CG);  // leader: one arrive per epilogue warp of every CTA of the pair
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bar_pfull[a]), 1);        // bulk-copy producer's expect_tx arrive
-      mbar_init(smem_u32(&bar_pempty[a]), PF_DQ_WARPS);  // one arrive per dequant warp
+    mbar_init(smem_u32(&bar_tfull[0]), 1);             // tcgen05.commit after the tile's last MMA
+    mbar_init(smem_u32(&bar_tempty[0]), PF_EPI_WARPS);  // every epilogue warp has drained its quarter of the accumulator
+    for (int a = 0; a < PF_MAX_SLABS; ++a) {
+      mbar_init(smem_u32(&bar_pfull[a]), 1);         // bulk-copy producer's expect_tx arrive
+      mbar_init(smem_u32(&bar_pempty[a]), 4 * SPB);  // one arrive per (stage of the superblock, warp of its group)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (FMT == 1) {
-    // table of unscaled fp16 trits: [alignment][byte value][replica] x 16 B
-    for (int i = tid; i < 2 * 256 * 8; i += PF_THREADS) {
-      const int odd = i >> 11, v = (i >> 3) & 255;
-      const uint32_t f = tq1_fields((uint32_t)v);
-      uint32_t h[6];
-#pragma unroll
-      for (int d = 0; d < 5; ++d) {
-        const int t = (int)((f >> (2 * d)) & 3u) - 1;
-        h[d + 1] = t > 0 ? 0x3C00u : (t < 0 ? 0xBC00u : 0u);
-      }
-      h[0] = 0u;
-      uint4 ent;
-      if (odd) ent = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), 0u);
-      else ent = make_uint4(h[1] | (h[2] << 16), h[3] | (h[4] << 16), h[5], 0u);
-      *reinterpret_cast<uint4*>(lut + (size_t)i * 16) = ent;
-    }
+    uint32_t* lut32 = reinterpret_cast<uint32_t*>(lut);  // [byte value][replica]
+    for (int i = tid; i < 256 * 16; i += PF_THREADS) lut32[i] = tq1_table_entry((uint32_t)i >> 4);
   }
-  __syncwarp();
-  if (warp == 1) {
-    if (CG == 2) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  for (int i = tid; i <= p.E; i += PF_THREADS) {
+    // offsets that were not validated on the host are clamped so no row index leaves [0, T)
+    int64_t v = p.offsets ? p.offsets[i] : (i == 0 ? 0 : (int64_t)p.T);
+    offs[i] = (int)(v < 0 ? 0 : (v > p.T ? p.T : v));
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // tpre: exclusive prefix sum of the experts' tile counts; each lane takes a contiguous run of experts
+    const int per = (p.E + 31) / 32, b0 = lane * per, b1 = b0 + per < p.E ? b0 + per : p.E;
+    int sum = 0;
+    for (int i = b0; i < b1; ++i) sum += expert_tiles(offs, i, p.tn_max, p.NT);
+    int incl = sum;
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
     }
+    int run = incl - sum;
+    for (int i = b0; i < b1; ++i) {
+      tpre[i] = run;
+      run += expert_tiles(offs, i, p.tn_max, p.NT);
+    }
+    if (lane == 31) tpre[p.E] = incl;
+  } else if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (CG == 2) cluster_sync_all();  // the peer's barriers are initialised before anyone arrives on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_s;
 
-  TileWalker walk;
-  walk.offsets = p.offsets;
-  walk.E = p.E;
-  walk.T = p.T;
-  walk.NT = p.NT / CG;
-  walk.row_round = ROUND;
-  int e, ntp, row0, rows;
+  int e = 0, nt, row0, rows;
   const int nsb = (p.kstages + SPB - 1) / SPB;  // superblocks a tile touches
-  const long long t_first = blockIdx.x / CG, t_step = gridDim.x / CG;
+  const int t_step = (int)gridDim.x, n_tiles = tpre[p.E];
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ producer: TMA for B, bulk copies for packed slabs
+    // ------------------------------------------------------------------ TMA producer for B (activations)
     if (lane == 0) {
-      uint32_t it = 0, pit = 0;  // stage counter, packed-slab counter (both run across tiles)
+      uint32_t s = 0, ph = 0;
       bool ok = true;
-      RT_DECL(w_pempty = 0, w_empty = 0, t_begin = RT_NOW());
-      // One slab (all stacked terms of one superblock) is always requested one superblock ahead of the
-      // stage loads, so the dequant warps find it in shared memory when they get there.
-      TileWalker ahead = walk;
-      int ae, antp, arow0, arows, asb = 0;
-      long long at = t_first;
-      bool have = ahead.seek(at, ae, antp, arow0, arows);
-      auto issue_slab = [&]() -> bool {
-        while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
-        if (!have) return true;
-        const int slot = pit & 1;
-        if (!RT_WAIT(w_pempty, mbar_wait<true>(smem_u32(&bar_pempty[slot]), ((pit >> 1) & 1u) ^ 1u, abort_flag))) return false;
-        const uint32_t full = smem_u32(&bar_pfull[slot]);
-        mbar_arrive_expect_tx(full, (uint32_t)p.n_terms * PF_SLAB);
-        const int64_t off = (((int64_t)ae * p.NT + antp * CG + rank) * p.S + asb) * PF_SLAB;
-        for (int i = 0; i < p.n_terms; ++i)
-          bulk_load(smem_u32(slabs + (slot * p.n_terms + i) * PF_SLAB), p.tiled[i] + off, PF_SLAB, full);
-        ++pit;
-        if (++asb >= nsb) {
-          asb = 0;
-          at += t_step;
-          have = ahead.seek(at, ae, antp, arow0, arows);
-        }
-        return true;
-      };
-      ok = issue_slab();
+      RT_DECL(w_empty = 0, n_it = 0, t_begin = RT_NOW());
       const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]), dst0 = smem_u32(smem);
-      const uint32_t lfull0 = CG == 2 ? mapa(full0, 0) : full0;  // the stage-full barriers of the pair's leader
-      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
-        if (rows <= 0) continue;
-        const int n_eff = (rows + ROUND - 1) / ROUND * ROUND;
-        const int my_rows = n_eff / CG;                    // token rows this CTA stages (a multiple of 16)
-        const int my_row0 = row0 + (int)rank * my_rows;
-        const CUtensorMap* map = &xmaps.m[my_rows / 16 - 1];
-        const uint32_t bytes = (uint32_t)my_rows * 128u;
-        int sbk = 0;
-        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          if (sbk == 0 && !issue_slab()) { ok = false; break; }
-          if (++sbk == SPB) sbk = 0;
-          const uint32_t s = it & smask;
-          if (!RT_WAIT(w_empty, mbar_wait(empty0 + s * 8, ((it >> sshift) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
-          if (CG == 2) {
-            if (leader) mbar_arrive_expect_tx(full0 + s * 8, bytes * 2u);  // both CTAs stage the same number of bytes
-            tma_load_2d_2cta(dst0 + s * STAGE_BYTES, map, ks * 64, my_row0, lfull0 + s * 8);
-          } else {
-            mbar_arrive_expect_tx(full0 + s * 8, bytes);
-            tma_load_2d(dst0 + s * STAGE_BYTES, map, ks * 64, my_row0, full0 + s * 8);
-          }
+      for (int t = (int)blockIdx.x; ok && t < n_tiles; t += t_step) {
+        tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+        const int n_eff = tile_neff(rows);
+        const int h = n_eff > 256 ? n_eff >> 1 : n_eff;  // token rows per TMA box and per MMA (a multiple of 16)
+        const CUtensorMap* map = &xmaps.m[h / 16 - 1];
+        const uint32_t bytes = (uint32_t)n_eff * 128u;
+        for (int ks = 0; ks < p.kstages; ++ks) {
+          if (!RT_WAIT(w_empty, mbar_wait(empty0 + s * 8, ph ^ 1u, abort_flag))) { ok = false; break; }
+          mbar_arrive_expect_tx(full0 + s * 8, bytes);
+          tma_load_2d(dst0 + s * stage_bytes, map, ks * 64, row0, full0 + s * 8);
+          if (h != n_eff) tma_load_2d(dst0 + s * stage_bytes + (uint32_t)h * 128u, map, ks * 64, row0 + h, full0 + s * 8);
+          if (++s == NB) { s = 0; ph ^= 1u; }
+#ifdef DST_ROLE_TIMERS
+          ++n_it;
+#endif
         }
       }
-      RT_ADD(0, RT_NOW() - t_begin); RT_ADD(1, w_pempty); RT_ADD(2, w_empty); RT_ADD(3, it); RT_ADD(4, 1);
+      RT_ADD(0, RT_NOW() - t_begin); RT_ADD(2, w_empty); RT_ADD(3, n_it); RT_ADD(4, 1);
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ bulk-copy producer for the packed slabs
+    if (lane == 0) {
+      uint32_t slot = 0, ph = 0;
+      bool ok = true;
+      RT_DECL(w_pempty = 0, t_begin = RT_NOW());
+      for (int t = (int)blockIdx.x; ok && t < n_tiles; t += t_step) {
+        tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+        const int64_t off0 = ((int64_t)e * p.NT + nt) * p.S * PF_SLAB;
+        for (int sb = 0; sb < nsb; ++sb) {
+          if (!RT_WAIT(w_pempty, mbar_wait<true>(smem_u32(&bar_pempty[slot]), ph ^ 1u, abort_flag))) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_pfull[slot]);
+          mbar_arrive_expect_tx(full, (uint32_t)p.n_terms * PF_SLAB);
+          for (int i = 0; i < p.n_terms; ++i)
+            bulk_load(smem_u32(slabs + ((size_t)slot * p.n_terms + i) * PF_SLAB), p.tiled[i] + off0 + (int64_t)sb * PF_SLAB, PF_SLAB, full);
+          if (++slot == (uint32_t)p.nslab) { slot = 0; ph ^= 1u; }
+        }
+      }
+      RT_ADD(5, RT_NOW() - t_begin); RT_ADD(1, w_pempty);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (the leader CTA of a pair only)
-    if (lane == 0 && leader) {
-      uint32_t it = 0, tile = 0;
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0, tile = 0;
       bool ok = true;
       const uint64_t b_desc0 = umma_desc(smem_u32(smem));
       const uint32_t b_desc_lo = (uint32_t)b_desc0, b_desc_hi = (uint32_t)(b_desc0 >> 32);
-      RT_DECL(w_tempty = 0, w_full = 0, t_begin = RT_NOW());
-      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
-        if (rows <= 0) continue;
-        // one accumulator: the epilogue of the previous tile must have drained it
+      RT_DECL(w_tempty = 0, w_full = 0, n_it = 0, t_begin = RT_NOW());
+      for (int t = (int)blockIdx.x; ok && t < n_tiles; t += t_step) {
+        tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+        // one accumulator: the previous tile must have been drained
         if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t n_eff = (uint32_t)((rows + ROUND - 1) / ROUND * ROUND);
+        const uint32_t n_eff = (uint32_t)tile_neff(rows);
+        const uint32_t h = n_eff > 256u ? n_eff >> 1 : n_eff;
+        const bool two = h != n_eff;
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-        const uint32_t idesc = (1u << 4) | ((n_eff >> 3) << 17) | (((128u * CG) >> 4) << 24);
-        const uint32_t d_tmem = tmem;
-        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          const int s = (int)(it & smask);
-          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), (it >> sshift) & 1u, abort_flag))) { ok = false; break; }
+        const uint32_t idesc = (1u << 4) | ((h >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t half_off = (h * 128u) >> 4;  // second half of the rows: descriptor start-address units
+        for (int ks = 0; ks < p.kstages; ++ks) {
+          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_tmem = tmem + PF_TN + s * PF_A_COLS;  // this stage's slot of the A ring
-          // only the start-address field of the B descriptor changes with the stage and the K step
-          const uint32_t b_lo = b_desc_lo + (uint32_t)s * (STAGE_BYTES >> 4);
+          const uint32_t a_tmem = tmem + PF_TN_MAX + s * PF_A_COLS;  // this stage's slot of the A ring
+          // only the start-address field of the B descriptor changes with the stage, the K step and the half
+          const uint32_t b_lo = b_desc_lo + s * (stage_bytes >> 4);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
             uint64_t db;
             asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2), "r"(b_desc_hi));
-            if (CG == 2) umma_f16_ts_2cta(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-            else umma_f16_ts(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-          }
-          // frees the stage (in both CTAs of a pair) when these MMAs have read it
-          if (CG == 2) umma_commit_2cta(smem_u32(&bar_empty[s]));
-          else umma_commit(smem_u32(&bar_empty[s]));
-        }
-        if (ok) {
-          if (CG == 2) umma_commit_2cta(smem_u32(&bar_tfull[0]));
-          else umma_commit(smem_u32(&bar_tfull[0]));
-        }
-        ++tile;
-      }
-      RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, it); RT_ADD(12, 1); RT_ADD(13, tile);
-    } else if (CG == 2 && lane == 0) {
-      // non-leader CTA of a pair: when this CTA's dequant warps have written their A tile of a stage, tell the
-      // leader's stage-full barrier (one cluster-scope arrive per stage instead of one per dequant warp)
-      uint32_t it = 0;
-      bool ok = true;
-      for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
-        if (rows <= 0) continue;
-        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          const int s = (int)(it & smask);
-          if (!mbar_wait(smem_u32(&bar_afull[s]), (it >> sshift) & 1u, abort_flag)) { ok = false; break; }
-          mbar_arrive_cluster(mapa(smem_u32(&bar_full[s]), 0));
-        }
-      }
-    }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t tile = 0;
-    RT_DECL(w_tfull = 0, t_begin = RT_NOW());
-    for (long long t = t_first; walk.seek(t, e, ntp, row0, rows); t += t_step) {
-      if (rows <= 0) continue;
-      if (!RT_WAIT(w_tfull, mbar_wait<true>(smem_u32(&bar_tfull[0]), tile & 1u, abort_flag))) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int n = (ntp * CG + (int)rank) * 128 + q * 32 + lane;
-      const bool n_ok = n < p.N;
-      const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16);
-      const int n_eff = (rows + 15) & ~15;
-      // this thread owns output column n; consecutive token rows are p.N elements apart
-      const size_t esz = p.out_dtype == DST_OUT_F32 ? 4 : 2;
-      uint8_t* optr = static_cast<uint8_t*>(p.out) + ((size_t)row0 * p.N + (n_ok ? n : 0)) * esz;
-      const size_t ostep = (size_t)p.N * esz;
-      for (int c0 = 0; c0 < n_eff; c0 += 32) {
-        uint32_t v[32];
-        if (c0 + 32 <= n_eff) {
-          TMEM_LD_32(v, taddr0 + c0);
-        } else {
-          TMEM_LD_16(v, taddr0 + c0);
-#pragma unroll
-          for (int j = 16; j < 32; ++j) v[j] = 0u;
-        }
-        const float rs_lane = (p.row_scale && c0 + lane < rows) ? p.row_scale[row0 + c0 + lane] : 1.f;
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int lim = n_ok ? rows - c0 : 0;  // token rows of this chunk that exist (and a column that exists)
-        if (p.out_dtype == DST_OUT_BF16) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
-            if (j < lim) *reinterpret_cast<__nv_bfloat16*>(optr + j * ostep) = __float2bfloat16_rn(val);
-          }
-        } else if (p.out_dtype == DST_OUT_F16) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
-            if (j < lim) *reinterpret_cast<__half*>(optr + j * ostep) = __float2half_rn(val);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
-            if (j < lim) {
-              float* o = reinterpret_cast<float*>(optr + j * ostep);
-              *o = p.accumulate ? *o + val : val;
+            umma_f16_ts(tmem, a_tmem + kk * 8, db, idesc, acc);
+            if (two) {
+              asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2 + half_off), "r"(b_desc_hi));
+              umma_f16_ts(tmem + h, a_tmem + kk * 8, db, idesc, acc);
             }
           }
+          umma_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs have read it
+          if (++s == NB) { s = 0; ph ^= 1u; }
+#ifdef DST_ROLE_TIMERS
+          ++n_it;
+#endif
         }
-        optr += 32 * ostep;
+        if (ok) umma_commit(smem_u32(&bar_tfull[0]));
+        ++tile;
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        if (CG == 2) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[0]), 0));
-        else mbar_arrive(smem_u32(&bar_tempty[0]));
-      }
-      ++tile;
+      RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, n_it); RT_ADD(12, 1); RT_ADD(13, tile);
     }
-    if (warp == 2 && lane == 0) { RT_ADD(16, RT_NOW() - t_begin); RT_ADD(17, w_tfull); RT_ADD(18, 1); }
+  } else if (warp < PF_DQ_WARP0) {
+    // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
+    const int r = (warp & 3) * 32 + lane;  // a warp may only read the TMEM lanes of its own quarter (warp id % 4)
+    uint32_t tile = 0;
+    for (int t = (int)blockIdx.x; t < n_tiles; t += t_step, ++tile) {
+      tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+      if (!drain_tile(p, tmem, 0, 32, r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]), abort_flag, nt, row0, rows, tile)) break;
+    }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
-    // A warp may only write the TMEM lanes of its own quarter (warp id % 4): it owns those 32 weight rows.
-    const int r = (warp & 3) * 32 + lane;
-    const uint32_t grp = (uint32_t)(warp - 6) >> 2;  // this warp dequantises the stages with (stage index & 3) == grp
+    // A warp may only touch the TMEM lanes of its own quarter (warp id % 4): it owns those 32 weight rows.
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t grp = (uint32_t)(warp - PF_DQ_WARP0) >> 2;
     const int swz = (r >> 1) & 3;  // swizzle of the tiled layout: logical word w sits at physical word (((w & 3) ^ swz) << 2) | (w >> 2)
-    const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 7) * 16u;
+    const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 15) * 4u;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const bool vec_scales = (p.G & 7) == 0;  // rows of 8 k scales are 16-byte aligned
-    uint32_t it = 0, pit = 0;
+    const int kstages = p.kstages;
+    uint32_t own = grp;  // global index (counted over all tiles of this CTA) of this group's next stage
+    uint32_t s = grp % NB, ph = (grp / NB) & 1u;
+    uint32_t it0 = 0, gs0 = 0;  // first stage / first slab of the current tile
     bool ok = true;
-    RT_DECL(w_pfull = 0, w_dempty = 0, w_tail = 0, t_begin = RT_NOW());
-    // scales of the row for 8 groups (16 stages) at a time, fetched one block ahead (also across tiles)
-    uint4 sc_next[TERMS];
-    TileWalker ahead = walk;
-    int ae, antp, arow0, arows;
-    long long at = t_first;
-    bool have = ahead.seek(at, ae, antp, arow0, arows);
-    while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
+    RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, n_it = 0, t_begin = RT_NOW());
+
+    // scales of the row: 8 groups (16 stages) per 128-bit load, the block of the group's next stage fetched one stage ahead
+    uint4 sc[TERMS], scn[TERMS];
+    int cur_t = -1, nxt_t = -1, cur_b = -1, nxt_b = -1;  // (tile, block of 8 groups) held in sc / requested into scn
     auto load_scales = [&](int ee, int nn, int g0, uint4* dst) {
       const bool n_ok = nn < p.N;
 #pragma unroll
@@ -616,95 +581,132 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         }
       }
     };
-    if (have) load_scales(ae, (antp * CG + (int)rank) * 128 + r, 0, sc_next);
-    for (long long t = t_first; ok && walk.seek(t, e, ntp, row0, rows); t += t_step) {
-      if (rows <= 0) continue;
-      const int nt = ntp * CG + (int)rank;
-      // the tile after this one (for the scale prefetch at the end of this tile)
-      at = t + t_step;
-      have = ahead.seek(at, ae, antp, arow0, arows);
-      while (have && arows <= 0) { at += t_step; have = ahead.seek(at, ae, antp, arow0, arows); }
-      uint4 sc[TERMS];
-      int sbk = -1;
-      for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-        if (++sbk == SPB) sbk = 0;
-        const int s = (int)(it & smask);
-        if ((ks & 15) == 0) {
-#pragma unroll
-          for (int i = 0; i < TERMS; ++i) sc[i] = sc_next[i];
-          if (ks + 16 < p.kstages) load_scales(e, nt * 128 + r, (ks + 16) >> 1, sc_next);
-          else if (have) load_scales(ae, (antp * CG + (int)rank) * 128 + r, 0, sc_next);
+    int t = (int)blockIdx.x - t_step;  // tile being dequantised; before the first one here
+    bool in_tile = false;
+    int n = 0;
+    for (;;) {
+      if (!(in_tile && (int32_t)(own - it0) < kstages)) {
+        // past the end of the current tile (or before the first): look up the next one
+        if (in_tile) {
+          it0 += (uint32_t)kstages;
+          gs0 += (uint32_t)nsb;
+          in_tile = false;
         }
-        const uint32_t slot = pit & 1u;
-        if (sbk == 0 && !RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), (pit >> 1) & 1u, abort_flag))) { ok = false; break; }
-        const uint8_t* slab = slabs + (size_t)slot * p.n_terms * PF_SLAB + r * 64;
-        const bool last_of_slab = sbk == SPB - 1 || ks == p.kstages - 1;
-        if ((it & 3u) != grp) {  // another group's stage: only keep the slab ring's bookkeeping in step
-          if (last_of_slab) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
-            ++pit;
+        if (t + t_step >= n_tiles) break;
+        t += t_step;
+        tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+        n = nt * 128 + r;
+        in_tile = true;
+        continue;
+      }
+      const int ks = (int)(own - it0);
+        const int sb = ks / SPB, sbk = ks - sb * SPB;
+        const uint32_t gs = gs0 + (uint32_t)sb;
+        const uint32_t slot = p.nslab == 2 ? (gs & 1u) : gs % 3u, sround = p.nslab == 2 ? (gs >> 1) : gs / 3u;
+        // scales
+        const int blk = ks >> 4;
+        if (!(cur_t == t && cur_b == blk)) {
+          if (nxt_t == t && nxt_b == blk) {
+#pragma unroll
+            for (int i = 0; i < TERMS; ++i) sc[i] = scn[i];
+          } else {
+            load_scales(e, n, blk * 8, sc);
           }
-          continue;
+          cur_t = t;
+          cur_b = blk;
+        }
+        {
+          int nks = ks + PF_GROUPS, pe = e, pn = n, pt = t;
+          if (nks >= kstages) {  // in the next tile (looked up here once per tile; e is a valid search hint)
+            nks -= kstages;
+            pt = t + t_step < n_tiles ? t + t_step : -1;
+            if (pt >= 0 && nks < kstages) {
+              int x_nt, x_row0, x_rows;
+              tile_seek(p, offs, tpre, pt, pe, x_nt, x_row0, x_rows);
+              pn = x_nt * 128 + r;
+            }
+          }
+          if (pt >= 0 && nks < kstages) {
+            const int b2 = nks >> 4;
+            if (!(pt == cur_t && b2 == cur_b) && !(pt == nxt_t && b2 == nxt_b)) {
+              load_scales(pe, pn, b2 * 8, scn);
+              nxt_t = pt;
+              nxt_b = b2;
+            }
+          }
         }
         const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
-        uint32_t v[32];               // the row's 64 weights of this stage: 32 fp16 pairs = 32 TMEM columns
+
+        // packed words of this row for this stage, then the slab can go back to the producer
+        if (!RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), sround & 1u, abort_flag))) { ok = false; break; }
+        uint32_t w[TERMS][4];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          __half2 acc[8];
-          if (FMT == 2) {
-            const int boff = ((q4 ^ swz) << 4) + sbk * 4;  // logical word 4 sbk + q4
+        for (int i = 0; i < TERMS; ++i) {
+          if (i < p.n_terms) {
+            const uint32_t* wp = reinterpret_cast<const uint32_t*>(slabs + ((size_t)slot * p.n_terms + i) * PF_SLAB + r * 64);
 #pragma unroll
-            for (int i = 0; i < TERMS; ++i) {
-              if (i < p.n_terms) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB + boff);
-                const __half2 s2 = pick_scale(sc[i], g);
-                if (i == 0) tq2_word<true>(w, s2, acc);
-                else tq2_word<false>(w, s2, acc);
-              }
-            }
-          } else {
-            const int qq = sbk * 4 + q4;  // 16-trit slot 0..19 inside the 320-trit superblock
-            const int tau = qq * 16, b0 = tau / 5, o = tau - b0 * 5;
-            const int wi = b0 >> 2, sh = (b0 & 3) * 8;
-#pragma unroll
-            for (int i = 0; i < TERMS; ++i) {
-              if (i < p.n_terms) {
-                const uint32_t* wp = reinterpret_cast<const uint32_t*>(slab + i * PF_SLAB);
-                const uint32_t w0 = wp[(((wi & 3) ^ swz) << 2) | (wi >> 2)];
-                const uint32_t w1 = wi + 1 < 16 ? wp[((((wi + 1) & 3) ^ swz) << 2) | ((wi + 1) >> 2)] : 0u;
-                const uint32_t win = __funnelshift_r(w0, w1, sh);  // bytes b0 .. b0 + 3 of the row-superblock
-                const __half2 s2 = pick_scale(sc[i], g);
-                if (i == 0) tq1_dispatch<true>(o, win, lut_addr, s2, acc);
-                else tq1_dispatch<false>(o, win, lut_addr, s2, acc);
-              }
+            for (int j = 0; j < 4; ++j) {
+              const int lw = FMT == 2 ? 4 * sbk + j : (j < 3 ? 3 * sbk + j : 15);  // logical word of the row-superblock
+              w[i][j] = wp[(((lw & 3) ^ swz) << 2) | (lw >> 2)];
             }
           }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[q4 * 8 + j] = h2_bits(acc[j]);
-        }
-        if (last_of_slab) {  // last read of this slab: hand the slot back
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[slot]));
-          ++pit;
-        }
-        if (!RT_WAIT(w_dempty, mbar_wait<true>(smem_u32(&bar_empty[s]), ((it >> sshift) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
-        RT_DECL(t_tail = RT_NOW());
-        {
-          const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + PF_TN + s * PF_A_COLS;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) tmem_st_8(taddr + q4 * 8, v + q4 * 8);
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(CG == 2 && !leader ? &bar_afull[s] : &bar_full[s]));
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_pempty[slot]));
+          // the tile's last superblock may hold fewer than SPB stages: make up for the stages that do not exist
+          if (ks == kstages - 1)
+            for (int x = nsb * SPB - kstages; x > 0; --x) mbar_arrive(smem_u32(&bar_pempty[slot]));
+        }
+
+        RT_DECL(t_c = RT_NOW());
+        __half2 acc[32];
+#pragma unroll
+        for (int i = 0; i < TERMS; ++i) {
+          if (i < p.n_terms) {
+            const __half2 s2 = pick_scale(sc[i], g);
+            if (FMT == 2) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (i == 0) tq2_word<true>(w[i][j], s2, acc + 8 * j);
+                else tq2_word<false>(w[i][j], s2, acc + 8 * j);
+              }
+            } else {
+              if (i == 0) tq1_stage<true>(w[i], sbk, lut_addr, s2, acc);
+              else tq1_stage<false>(w[i], sbk, lut_addr, s2, acc);
+            }
+          }
+        }
+        uint32_t v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = h2_bits(acc[j]);
 #ifdef DST_ROLE_TIMERS
-        w_tail += RT_NOW() - t_tail;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) asm volatile("" : "+r"(v[j]));
+        RT_SPAN(w_comp, t_c);
+        ++n_it;
 #endif
-      }
+        // the A slot must be free (the MMAs that last read it are done) before the store into it
+        if (!RT_WAIT(w_dempty, mbar_wait<true>(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
+        __syncwarp();  // re-converge after the polling loop: tcgen05.st is .sync.aligned
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem + lane_base + PF_TN_MAX + s * PF_A_COLS;
+        tmem_st_8(taddr, v);
+        tmem_st_8(taddr + 8, v + 8);
+        tmem_st_8(taddr + 16, v + 16);
+        tmem_st_8(taddr + 24, v + 24);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+        own += PF_GROUPS;
+        s += PF_GROUPS;
+        while (s >= NB) { s -= NB; ph ^= 1u; }
     }
-    if (warp == 6 && lane == 0) { RT_ADD(24, RT_NOW() - t_begin); RT_ADD(25, w_pfull); RT_ADD(26, w_dempty); RT_ADD(27, it); RT_ADD(28, 1); RT_ADD(29, w_tail); }
+    if (warp == PF_DQ_WARP0 && lane == 0) {
+      RT_ADD(24, RT_NOW() - t_begin); RT_ADD(25, w_pfull); RT_ADD(26, w_dempty); RT_ADD(27, n_it); RT_ADD(28, 1);
+      RT_ADD(29, w_drain); RT_ADD(30, w_comp);
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -715,11 +717,9 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (CG == 2) cluster_sync_all();  // neither CTA leaves while its peer may still read its shared memory or signal it
   if (warp == 1) {
     __syncwarp();
-    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
-    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
   }
   if (tid == 0 && abort_s) atomicExch(&g_device_status, DST_ERR_TIMEOUT);
 }
@@ -771,49 +771,37 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int FMT, int CG, int TERMS>
-int launch_fmt(const TmaMaps& maps, PrefillParams p, long long tiles_upper, cudaStream_t st) {
-  // deepest stage ring the shared-memory budget allows next to the packed slabs and the TQ1 table
-  const size_t stage_bytes = PF_B_BYTES / CG;
-  const size_t fixed = 1024 + (size_t)2 * p.n_terms * PF_SLAB + (FMT == 1 ? PF_LUT_BYTES : 0);
-  const int fit = (int)((PF_SMEM_MAX - fixed) / stage_bytes);
-  if (fit < 2) return DST_ERR_UNSUPPORTED;
-  p.nstage_log2 = fit >= 8 ? 3 : (fit >= 4 ? 2 : 1);  // a power of two, so ring indices are a mask and a shift
-  const int nstage = 1 << p.nstage_log2;
-  const size_t smem = fixed + (size_t)nstage * stage_bytes;
-  auto kernel = prefill_kernel<FMT, CG, TERMS>;
+template <int FMT, int TERMS>
+int launch_fmt(const TmaMaps& maps, PrefillParams p, cudaStream_t st) {
+  // Shared-memory plan: the largest token tile (up to 320 rows) that still leaves a stage ring of depth 4, then
+  // a third packed-slab slot if there is room for it.
+  const long long budget = PF_SMEM_MAX - PF_SMEM_STATIC;
+  const long long fixed = 1024 + (FMT == 1 ? PF_LUT_BYTES : 0) + 2 * (PF_MAX_E + 1) * 4;
+  const long long slab2 = 2LL * p.n_terms * PF_SLAB;
+  p.tn_max = 0;
+  for (int tn = PF_TN_MAX; tn >= 64; tn -= 32) {
+    const long long nb = (budget - fixed - slab2) / (tn * 128LL);
+    if (nb >= 4 || tn == 64) {
+      p.tn_max = tn;
+      p.nb = (int)(nb > PF_MAX_STAGES ? PF_MAX_STAGES : nb);
+      break;
+    }
+  }
+  if (p.tn_max == 0 || p.nb < 2) return DST_ERR_UNSUPPORTED;
+  p.nslab = fixed + 3LL * p.n_terms * PF_SLAB + (long long)p.nb * p.tn_max * 128 <= budget ? 3 : 2;
+  const size_t smem = (size_t)(fixed + (long long)p.nslab * p.n_terms * PF_SLAB + (long long)p.nb * p.tn_max * 128);
+  auto kernel = prefill_kernel<FMT, TERMS>;
   DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   DST_CUDA_TRY(cudaGetDevice(&dev));
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(PF_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  int n_attr = 0;
-  long long units = tiles_upper / CG;  // tiles (CG = 1) or pair tiles (CG = 2) at most
-  if (units < 1) units = 1;
-  int groups = sms / CG;
-  if (CG == 2) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    n_attr = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3((unsigned)sms / 2 * 2, 1, 1);
-    int max_clusters = 0;
-    DST_CUDA_TRY(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg));
-    if (max_clusters < 1) return DST_ERR_UNSUPPORTED;
-    groups = max_clusters < groups ? max_clusters : groups;
-  }
-  if (units < groups) groups = (int)units;
-  cfg.gridDim = dim3((unsigned)(groups * CG), 1, 1);
-  cfg.attrs = n_attr ? attr : nullptr;
-  cfg.numAttrs = n_attr;
-  DST_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, p));
+  // persistent CTAs, one per SM, fewer when there cannot be that many tiles
+  long long tiles_upper = ((long long)cdiv64(p.T, p.tn_max) + p.E) * p.NT;
+  if (tiles_upper >= (1LL << 30)) return DST_ERR_UNSUPPORTED;  // tile indices are 32-bit in the kernel
+  if (tiles_upper < 1) tiles_upper = 1;
+  const unsigned grid = (unsigned)(tiles_upper < sms ? tiles_upper : sms);
+  prefill_kernel<FMT, TERMS><<<grid, PF_THREADS, smem, st>>>(maps, p);
+  DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }
 
@@ -890,28 +878,33 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.NT = (int)cdiv64(a.N, 128);
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.kstages = (int)(a.K / 64);
-  const long long tiles_upper = ((long long)cdiv64(a.T, PF_TN) + a.E) * p.NT;
-  // CTA pairs (cta_group::2) need an even number of 128-row weight tiles. They are correct but measured SLOWER
-  // than single CTAs here (2.51 M vs 1.58 M cycles per launch on the same case): the cross-CTA barrier traffic
-  // (remote arrives, multicast commits) costs more than the halved activation traffic saves while the kernel is
-  // bound by its per-stage handshakes. Kept compiled and tested behind this switch for when that changes.
-  const bool pairs = kUseCtaPairs && a.N % 256 == 0;
-#define DST_PF_LAUNCH(FMT_, CG_)                                                                          \
-  (a.terms.n == 1 ? launch_fmt<FMT_, CG_, 1>(maps, p, tiles_upper, stream)                       \
-                  : a.terms.n == 2 ? launch_fmt<FMT_, CG_, 2>(maps, p, tiles_upper, stream)      \
-                                   : launch_fmt<FMT_, CG_, 4>(maps, p, tiles_upper, stream))
-  if (a.fmt == DST_FMT_TQ2) return pairs ? DST_PF_LAUNCH(2, 2) : DST_PF_LAUNCH(2, 1);
-  return pairs ? DST_PF_LAUNCH(1, 2) : DST_PF_LAUNCH(1, 1);
+#define DST_PF_LAUNCH(FMT_)                                                            \
+  (a.terms.n == 1 ? launch_fmt<FMT_, 1>(maps, p, stream)                               \
+                  : a.terms.n == 2 ? launch_fmt<FMT_, 2>(maps, p, stream) : launch_fmt<FMT_, 4>(maps, p, stream))
+  // The kernel keeps per-expert tables in shared memory: more experts than fit there are served by one launch
+  // per run of PF_MAX_E experts (offsets are absolute token rows, so only the per-expert pointers move).
+  const int64_t tiled_per_expert = (int64_t)p.NT * p.S * PF_SLAB, scales_per_expert = a.N * a.G;
+  for (int64_t e0 = 0; e0 < a.E; e0 += PF_MAX_E) {
+    p.E = (int)(a.E - e0 < PF_MAX_E ? a.E - e0 : PF_MAX_E);
+    p.offsets = a.offsets ? a.offsets + e0 : nullptr;
+    for (int i = 0; i < a.terms.n; ++i) {
+      p.tiled[i] = a.terms.packed[i] + e0 * tiled_per_expert;
+      p.scale[i] = static_cast<const __half*>(a.terms.scale[i]) + e0 * scales_per_expert;
+    }
+    const int rc = a.fmt == DST_FMT_TQ2 ? DST_PF_LAUNCH(2) : DST_PF_LAUNCH(1);
+    if (rc != DST_OK) return rc;
+  }
+  return DST_OK;
 #undef DST_PF_LAUNCH
 }
 
 }  // namespace dst
 
 #ifdef DST_ROLE_TIMERS
-// Profiling builds only: copies (and optionally clears) the 64 role-timer slots. Slots: 0-4 producer (total
-// cycles, wait packed-slot free, wait stage free, stages, threads), 8-13 MMA issuer (total, wait accumulator
-// free, wait stage full, stages, threads, tiles), 16-18 epilogue warp (total, wait accumulator full, threads),
-// 24-29 one dequant warp (total, wait packed slab, wait stage free, stages, threads, store+fence+arrive).
+// Profiling builds only: copies (and optionally clears) the 64 role-timer slots. Slots: 0-5 producers (B producer
+// total cycles, slab producer wait slot free, B producer wait stage free, stages, threads, slab producer total),
+// 8-13 MMA issuer (total, wait accumulator free, wait stage full, stages, threads, tiles), 24-30 one dequant warp
+// (total, wait packed slab, wait stage free, own stages, threads, accumulator drain, dequant arithmetic).
 extern "C" int dst_role_timers(unsigned long long* out, int reset) {
   DST_CUDA_TRY(cudaDeviceSynchronize());
   DST_CUDA_TRY(cudaMemcpyFromSymbol(out, dst::g_role_timers, sizeof(unsigned long long) * 64));

@@ -12,7 +12,12 @@
 // loads and a whole slab can be fetched with one bulk copy. Rows beyond N and trits beyond K are
 // padding digits (t = 0). K is padded to whole superblocks: TQ1 K = 4096 -> 4160 trits (+1.6 %).
 //
-//   TQ1: byte i of a row-superblock is the canonical base-3 byte of trits 320 sb + 5 i .. + 4.
+//   TQ1: the 320 trits of a row-superblock are five 64-trit MMA stages; 64 is not a multiple of 5, so the
+//        trits are RE-GROUPED into base-3 bytes (same digit weights 1, 3, 9, 27, 81 as the canonical format)
+//        such that every stage decodes from whole bytes: bytes 12 s .. 12 s + 11 hold trits 0..59 of stage s
+//        in order (byte m = trits 5 m .. 5 m + 4), and byte 60 + m (m = 0..3) holds trit 60 + m of each of the
+//        five stages (digit s = stage s). A canonical byte >= 243 (never written by the packer; all trits 0
+//        by definition) is re-encoded as five zero trits, so it comes back from dst_untile_weights as 121.
 //   TQ2: 32-bit word q of a row-superblock holds trits k = 256 sb + 16 q + (0..15), re-ordered so that a
 //        (low half, high half) pair is two consecutive trits: trit 2j sits in bits [2j, 2j+1], trit 2j+1
 //        in bits [16+2j, 17+2j]. One AND then yields an fp16x2 of adjacent weights.
@@ -37,6 +42,24 @@ namespace {
 // digit 1 there), fields beyond the last byte are padding digits.
 __device__ __forceinline__ uint32_t tq2_digit(const uint8_t* row, int64_t k, int64_t Kp) {
   return k < 4 * Kp ? (uint32_t)((row[k >> 2] >> ((k & 3) * 2)) & 3) : 1u;
+}
+
+// Digit (0..2) of trit k of a canonical TQ1 row; trits beyond the row's last byte are padding digits.
+__device__ __forceinline__ uint32_t tq1_digit(const uint8_t* row, int64_t k, int64_t Kp) {
+  const int64_t b = k / 5;
+  return b < Kp ? (tq1_fields(row[b]) >> (2 * (int)(k - b * 5))) & 3u : 1u;
+}
+
+// Position of trit kk (0..319) of a row-superblock in the tiled TQ1 grouping: byte index and digit index.
+__device__ __forceinline__ void tq1_tiled_pos(int kk, int& byte, int& digit) {
+  const int s = kk >> 6, j = kk & 63;
+  if (j < 60) {
+    byte = 12 * s + j / 5;
+    digit = j % 5;
+  } else {
+    byte = j;  // 60 + (j - 60)
+    digit = s;
+  }
 }
 
 // One thread per 32-bit word of the tiled buffer.
@@ -69,8 +92,16 @@ __global__ void tile_kernel(const uint8_t* __restrict__ canon, int64_t E, int64_
         w = 0;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int64_t cb = sb * 64 + q * 4 + b;
-          w |= (uint32_t)(cb < Kp ? row[cb] : 121) << (8 * b);
+          const int bi = q * 4 + b;
+          uint32_t v = 0, pw = 1;
+#pragma unroll
+          for (int d = 0; d < 5; ++d) {
+            // trit of the superblock that lives in digit d of tiled byte bi
+            const int kk = bi < 60 ? 64 * (bi / 12) + 5 * (bi % 12) + d : 64 * d + bi;
+            v += tq1_digit(row, sb * 320 + kk, Kp) * pw;
+            pw *= 3;
+          }
+          w |= v << (8 * b);
         }
       }
     }
@@ -90,9 +121,20 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int64_t E, int6
     const int64_t nt = n >> 7, r = n & 127;
     uint8_t v;
     if (FMT == 1) {
-      const int64_t sb = b >> 6;
-      const int bi = (int)(b & 63), w = bi >> 2;
-      v = tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + ((((w & 3) ^ ((int)(r >> 1) & 3)) << 4) | ((w >> 2) << 2) | (bi & 3))];
+      uint32_t acc = 0, pw = 1;
+#pragma unroll
+      for (int d = 0; d < 5; ++d) {
+        const int64_t k = b * 5 + d;
+        const int64_t sb = k / 320;
+        int bi, di;
+        tq1_tiled_pos((int)(k - sb * 320), bi, di);
+        const int w = bi >> 2;
+        const uint8_t tb =
+            tiled[(((e * NT + nt) * S + sb) * 128 + r) * 64 + ((((w & 3) ^ ((int)(r >> 1) & 3)) << 4) | ((w >> 2) << 2) | (bi & 3))];
+        acc += ((tq1_fields(tb) >> (2 * di)) & 3u) * pw;
+        pw *= 3;
+      }
+      v = (uint8_t)acc;
     } else {
       uint32_t acc = 0;
 #pragma unroll

@@ -75,13 +75,15 @@ def test_pack_roundtrip_large_and_empty(fmt, N, K):
 @pytest.mark.parametrize("E,N,K", [(1, 128, 256), (3, 70, 4160), (2, 300, 4096), (1, 5, 7), (4, 2048, 2048)])
 def test_tiled_layout_roundtrip_bit_exact(kb, fmt, E, N, K):
     """canonical -> tiled -> canonical restores every byte, also for rows and K that need padding and for
-    byte values the packer never writes."""
+    byte values the packer never writes. TQ1 bytes >= 243 (five zero trits by definition) are re-grouped as
+    trits and therefore come back as the canonical byte of five zero trits, 121."""
     rng = np.random.default_rng(E * N + K)
     Kp = O.packed_cols(fmt, K)
     p = rng.integers(0, 256, (E, N, Kp), dtype=np.uint8)
     tw = kb.tile_weights(torch.from_numpy(p).to(DEV), fmt, K)
     assert tw.data.numel() == E * -(-N // 128) * -(-K // (256 if fmt == "tq2" else 320)) * 8192
-    assert np.array_equal(tw.untile().cpu().numpy(), p)
+    expect = np.where(p >= 243, 121, p).astype(np.uint8) if fmt == "tq1" else p
+    assert np.array_equal(tw.untile().cpu().numpy(), expect)
 
 
 # ------------------------------------------------------------------------------------------ linear, bf16 acts
@@ -265,11 +267,12 @@ def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo):
 def test_prefill_many_tiles_per_cta(kb, fmt):
     """More tiles than SMs, so every persistent CTA of the tcgen05 kernel walks several tiles (ring phases, the
     packed-slab ring and the accumulator hand-over all wrap across tile borders); ragged rows per expert around the
-    256-row tile size, one empty expert. Checked on sampled experts against the oracle, all rows for finiteness."""
-    E, N, K = 12, 2048, 1024
+    one-MMA (256 rows) and the tile (320 rows) limits, one empty expert. Checked on sampled experts against the
+    oracle, all rows for finiteness."""
+    E, N, K = 15, 2048, 1024
     rng = np.random.default_rng(77)
     terms = make_terms(rng, N, K, 128, fmt, 1, lead=(E,))
-    counts = np.array([257, 300, 0, 129, 256, 512, 31, 270, 255, 1, 513, 240])
+    counts = np.array([257, 300, 0, 129, 256, 512, 31, 270, 255, 1, 513, 240, 320, 321, 641])
     offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
     x = O.synth_acts(rng, (int(offsets[-1]), K))
     tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), fmt, K)]
@@ -279,9 +282,29 @@ def test_prefill_many_tiles_per_cta(kb, fmt):
     assert kb.ext().dst_check_device_status(None) == 0
     y = y.cpu().numpy()
     assert np.isfinite(y).all()
-    for e in (0, 5, 9, 10):
+    for e in (0, 5, 9, 10, 12, 13, 14):
         a, b = int(offsets[e]), int(offsets[e + 1])
         check_gemm(y[a:b], x[a:b], [(terms[0][0][e], terms[0][1][e])], K, 128, fmt)
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_prefill_more_experts_than_one_launch_holds(kb, fmt):
+    """The tcgen05 kernel keeps per-expert tables for at most 1023 experts in shared memory; a call with more is
+    split into launches over runs of experts. 1030 experts with 0..3 rows each, every row checked."""
+    E, N, K = 1030, 128, 256
+    rng = np.random.default_rng(5)
+    terms = make_terms(rng, N, K, 128, fmt, 1, lead=(E,))
+    counts = rng.integers(0, 4, E)
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = O.synth_acts(rng, (int(offsets[-1]), K))
+    tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), fmt, K)]
+    y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), torch.from_numpy(offsets).to(DEV), tiled, [torch.from_numpy(terms[0][1]).to(DEV)],
+                                     K, 128, fmt, algo="prefill")
+    torch.cuda.synchronize()
+    assert kb.ext().dst_check_device_status(None) == 0
+    y = y.cpu().numpy()
+    ref = O.grouped_gemm_f32(O.bf16_round(x), offsets, terms[0][0], terms[0][1].astype(np.float32), K, 128, fmt)
+    assert O.rel_fro(y, ref) < 2e-3 and O.cosine(y, ref) > 0.99999
 
 
 def test_native_entry_rejects_malformed_tensors(kb):
