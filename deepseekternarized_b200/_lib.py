@@ -15,7 +15,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_PATH = CSRC / "libdst_b200.so"
-SOURCES = ["api.cu", "format_kernels.cu", "layout_kernels.cu", "gemm_generic.cu", "gemm_decode.cu", "gemm_prefill.cu",
+SOURCES = ["api.cu", "format_kernels.cu", "layout_kernels.cu", "gemm_generic.cu", "gemm_decode.cu", "gemm_decode_tq1.cu", "gemm_prefill.cu",
            "moe_kernels.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC"]

@@ -244,6 +244,7 @@ decode_kernel(const DecodeParams p) {
 }  // namespace
 
 bool decode_supports(const GemmArgs& a) {
+  if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
   return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 256 == 0 &&
          a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) &&
          (size_t)16 * (a.K * 2 + 16) + (size_t)16 * (a.G + 1) * 4 <= 200 * 1024 && a.T < (int64_t(1) << 31);
@@ -251,6 +252,7 @@ bool decode_supports(const GemmArgs& a) {
 
 int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   if (a.T == 0 || a.N == 0 || a.E == 0) return DST_OK;
+  if (a.fmt == DST_FMT_TQ1) return launch_decode_tq1(a, stream);
   if (!decode_supports(a)) return DST_ERR_UNSUPPORTED;
   for (int i = 0; i < a.terms.n; ++i)
     if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 1) != 0)

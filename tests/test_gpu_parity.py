@@ -19,10 +19,10 @@ DEV = "cuda"
 
 
 def fast_algos(K, group, scale_dtype=np.float16, fmt="tq1"):
-    """Kernels that must accept a shape: the tcgen05 kernel covers group 128, K % 128 == 0, fp16 scales; the
-    decode GEMV additionally needs TQ2 and K % 256 == 0."""
+    """Kernels that must accept a shape: the tcgen05 kernel and the TQ1 decode GEMV cover group 128, K % 128 == 0,
+    fp16 scales; the TQ2 decode GEMV additionally needs K % 256 == 0."""
     ok = group == 128 and K % 128 == 0 and scale_dtype == np.float16
-    return ["generic", "auto"] + (["prefill"] if ok else []) + (["decode"] if ok and fmt == "tq2" and K % 256 == 0 else [])
+    return ["generic", "auto"] + (["prefill"] if ok else []) + (["decode"] if ok and (fmt == "tq1" or K % 256 == 0) else [])
 
 
 @pytest.fixture(scope="module")
@@ -243,10 +243,11 @@ def test_reference_cuda_parity_shapes(kb, fmt, T):
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=2e-3)
 
 
+@pytest.mark.parametrize("fmt", ["tq2", "tq1"])
 @pytest.mark.parametrize("algo", ["decode", "prefill", "auto"])
-def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo):
+def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo, fmt):
     """Grouped GEMV as a MoE decode step sees it: few rows per expert, some experts empty, one above 16 rows."""
-    E, N, K, fmt = 7, 200, 1024, "tq2"
+    E, N, K = 7, 200, 1024
     rng = np.random.default_rng(21)
     terms = make_terms(rng, N, K, 128, fmt, 2, lead=(E,))
     counts = np.array([1, 0, 8, 3, 19, 0, 2])
