@@ -254,7 +254,7 @@ def time_cuda(fn, iters: int, warmup: int = 3) -> float:
     return a.elapsed_time(b) / iters
 
 
-def gemm_microbench(device, peaks) -> dict:
+def gemm_microbench(device, peaks, which="all") -> dict:
     """Decode GEMV (BASELINE configs 0/1) and prefill grouped GEMM (config 2) at N = 1.
 
     Decode: one launch is a grouped GEMV over `copies` distinct weight sets of the same shape
@@ -274,8 +274,9 @@ def gemm_microbench(device, peaks) -> dict:
         s = torch.exp(torch.randn(E, N, K // GROUP, generator=g, device=device) * 0.3 - 4.0).half()
         return kb.tile_weights(p, fmt, K), s  # tiled once, as a loaded model holds them
 
-    for fmt, N, K, Ms in (("tq2", 4096, 4096, (1, 16)), ("tq1", 2048, 4096, (1, 8)), ("tq1", 4096, 4096, (1, 4, 8, 32)),
-                          ("tq1", 11008, 4096, (1, 8))):
+    decode_cases = (("tq2", 4096, 4096, (1, 16)), ("tq1", 2048, 4096, (1, 8)), ("tq1", 4096, 4096, (1, 4, 8, 32)),
+                    ("tq1", 11008, 4096, (1, 8)))
+    for fmt, N, K, Ms in (decode_cases if which in ("all", "decode") else ()):
         wbytes = N * packed_cols(fmt, K) + N * (K // GROUP) * 2  # canonical packed bytes + fp16 scales: the algorithmic bytes
         copies = max(2, int(np.ceil(400e6 / wbytes)))
         p, s = weights(copies, N, K, fmt)
@@ -293,7 +294,7 @@ def gemm_microbench(device, peaks) -> dict:
     E, rows = N_EXPERTS, 4096 * TOP_K
     ids = torch.randn(4096, E, generator=g, device=device).topk(TOP_K, -1)[1].reshape(-1)
     order, offs = kb.sort_by_expert(ids, E)
-    for (N, K) in ((2 * INTER, HIDDEN), (HIDDEN, INTER)):
+    for (N, K) in (((2 * INTER, HIDDEN), (HIDDEN, INTER)) if which in ("all", "prefill") else ()):
         p, s = weights(E, N, K, FMT)
         x = torch.randn(rows, K, generator=g, device=device).bfloat16()
         fn = lambda: kb.grouped_ternary_gemm_bf16(x, offs, [p], [s], K, GROUP, FMT, out_dtype=torch.bfloat16, validate_offsets=False)
@@ -357,6 +358,9 @@ def main():
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel decode/prefill numbers")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--micro-only", default=None, choices=["decode", "prefill", "all"],
+                    help="run only the single-kernel numbers (decode GEMV sweep and/or prefill grouped GEMM) and print them: "
+                    "for profiler captures of those kernels; not a bench line")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per step over all ranks (default: BASELINE config 4)")
     ap.add_argument("--experts", type=int, default=N_EXPERTS, help="routed experts (default: BASELINE config 4); smaller "
                     "values give a reduced case for profiler captures and are named in the JSON line")
@@ -365,6 +369,11 @@ def main():
     globals()["TOKENS"], globals()["N_EXPERTS"], globals()["FMT"] = args.tokens, args.experts, args.fmt
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.micro_only:
+        device = torch.device("cuda:0")
+        torch.cuda.set_device(device)
+        print(json.dumps({"micro_only": args.micro_only, "gemm": gemm_microbench(device, measured_peaks(), which=args.micro_only)}))
+        return
 
     import torch.distributed as dist
 

@@ -59,16 +59,12 @@ __device__ __forceinline__ int field_shift(int j) { return j < 5 ? j : j - 5; }
 //   xsum[m][g] = sum over group g of the values the tensor core will see, undone to x * 2^-e_m
 //   xexp[m] = 2^e_m * row_scale[m]
 template <int MT, typename XT>
-__device__ void stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, float* xsum, float* xexp) {
+__device__ void stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, float* xsum, float* xexp,
+                             int* xex) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int m = warp; m < MT; m += DC_WARPS) {
-    __half* dst = reinterpret_cast<__half*>(xs + (size_t)m * p.xstride);
-    if (m >= mc) {  // unused token slots read as zero
-      for (int k = lane * 2; k < p.K; k += 64) *reinterpret_cast<uint32_t*>(dst + k) = 0u;
-      for (int g = lane; g < p.G; g += 32) xsum[m * p.G + g] = 0.f;
-      if (lane == 0) xexp[m] = 0.f;
-      continue;
-    }
+  // pass 1, one warp per token row: the row's power of two. Token slots beyond mc are never read (their B
+  // fragments are zero registers), so nothing is written for them.
+  for (int m = warp; m < mc; m += DC_WARPS) {
     const XT* row = x + (m0 + m) * p.K;
     float amax = 0.f;
     for (int k = lane; k < p.K; k += 32) amax = fmaxf(amax, fabsf((float)row[k]));
@@ -78,25 +74,33 @@ __device__ void stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
       (void)frexpf(amax, &ex);
       ex -= 8;  // amax * 2^-ex in [128, 256)
     }
-    // one 128-trit group per step: 32 lanes x 4 consecutive k
-    for (int g = 0; g < p.G; ++g) {
-      const int k = g * 128 + lane * 4;
-      float part = 0.f;
-      uint32_t packed[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int kk = k + 2 * h;
-        const int f = field_shift((kk & 15) >> 1);
-        const float mul = ldexpf(1.f, 7 - ex - 2 * f), undo = ldexpf(1.f, 2 * f - 7);
-        const __half v0 = __float2half_rn((float)row[kk] * mul), v1 = __float2half_rn((float)row[kk + 1] * mul);
-        part += (__half2float(v0) + __half2float(v1)) * undo;
-        packed[h] = (uint32_t)__half_as_ushort(v0) | ((uint32_t)__half_as_ushort(v1) << 16);
-      }
-      *reinterpret_cast<uint2*>(dst + k) = make_uint2(packed[0], packed[1]);
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      if (lane == 0) xsum[m * p.G + g] = part;
+    if (lane == 0) {
+      xex[m] = ex;
+      xexp[m] = ldexpf(1.f, ex) * (p.row_scale ? p.row_scale[m0 + m] : 1.f);
     }
-    if (lane == 0) xexp[m] = ldexpf(1.f, ex) * (p.row_scale ? p.row_scale[m0 + m] : 1.f);
+  }
+  __syncthreads();
+  // pass 2, one warp per (token row, 128-trit group): 32 lanes x 4 consecutive k
+  for (int u = warp; u < mc * p.G; u += DC_WARPS) {
+    const int m = u / p.G, g = u - m * p.G;
+    const XT* row = x + (m0 + m) * p.K;
+    __half* dst = reinterpret_cast<__half*>(xs + (size_t)m * p.xstride);
+    const int ex = xex[m];
+    const int k = g * 128 + lane * 4;
+    float part = 0.f;
+    uint32_t packed[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int kk = k + 2 * h;
+      const int f = field_shift((kk & 15) >> 1);
+      const float mul = ldexpf(1.f, 7 - ex - 2 * f), undo = ldexpf(1.f, 2 * f - 7);
+      const __half v0 = __float2half_rn((float)row[kk] * mul), v1 = __float2half_rn((float)row[kk + 1] * mul);
+      part += (__half2float(v0) + __half2float(v1)) * undo;
+      packed[h] = (uint32_t)__half_as_ushort(v0) | ((uint32_t)__half_as_ushort(v1) << 16);
+    }
+    *reinterpret_cast<uint2*>(dst + k) = make_uint2(packed[0], packed[1]);
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    if (lane == 0) xsum[m * p.G + g] = part;
   }
 }
 
@@ -108,6 +112,7 @@ decode_kernel(const DecodeParams p) {
   uint8_t* xs = dsm;                                                // MT staged token rows
   float* xsum = reinterpret_cast<float*>(dsm + (size_t)MT * p.xstride);  // [MT][G]
   float* xexp = xsum + MT * p.G;                                    // [MT]
+  int* xex = reinterpret_cast<int*>(xexp + MT);                     // [MT] exponent of the row's power of two
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
 
   // contiguous range of (expert, row tile) items for this CTA
@@ -125,8 +130,8 @@ decode_kernel(const DecodeParams p) {
       const int mc = (int)(rb - m0 < NB * 8 ? rb - m0 : NB * 8);
       if (staged_e != e || staged_m0 != m0) {
         __syncthreads();  // everyone is done with the previous rows
-        if (p.act_dtype == DST_ACT_BF16) stage_tokens<MT>(p, static_cast<const __nv_bfloat16*>(p.x), m0, mc, xs, xsum, xexp);
-        else stage_tokens<MT>(p, static_cast<const __half*>(p.x), m0, mc, xs, xsum, xexp);
+        if (p.act_dtype == DST_ACT_BF16) stage_tokens<MT>(p, static_cast<const __nv_bfloat16*>(p.x), m0, mc, xs, xsum, xexp, xex);
+        else stage_tokens<MT>(p, static_cast<const __half*>(p.x), m0, mc, xs, xsum, xexp, xex);
         __syncthreads();
         staged_e = e;
         staged_m0 = m0;
@@ -177,9 +182,15 @@ decode_kernel(const DecodeParams p) {
               uint4 q[NB][2];
 #pragma unroll
               for (int b = 0; b < NB; ++b) {
-                const uint8_t* xr = xs + (size_t)(b * 8 + g8) * p.xstride + koff;
-                q[b][0] = *reinterpret_cast<const uint4*>(xr);
-                q[b][1] = *reinterpret_cast<const uint4*>(xr + 16);
+                // token columns that do not exist are zero registers: no shared-memory traffic for them
+                if (b * 8 + g8 < mc) {
+                  const uint8_t* xr = xs + (size_t)(b * 8 + g8) * p.xstride + koff;
+                  q[b][0] = *reinterpret_cast<const uint4*>(xr);
+                  q[b][1] = *reinterpret_cast<const uint4*>(xr + 16);
+                } else {
+                  q[b][0] = zero4;
+                  q[b][1] = zero4;
+                }
               }
 #pragma unroll
               for (int jj = 0; jj < 4; ++jj) {
@@ -247,7 +258,7 @@ bool decode_supports(const GemmArgs& a) {
   if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
   return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 256 == 0 &&
          a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) &&
-         (size_t)16 * (a.K * 2 + 16) + (size_t)16 * (a.G + 1) * 4 <= 200 * 1024 && a.T < (int64_t(1) << 31);
+         (size_t)16 * (a.K * 2 + 16) + (size_t)16 * (a.G + 2) * 4 <= 200 * 1024 && a.T < (int64_t(1) << 31);
 }
 
 int launch_decode(const GemmArgs& a, cudaStream_t stream) {
@@ -285,7 +296,7 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const long long items = (long long)p.E * p.NT;
   const int nb = rows_hint <= 8 ? 1 : 2;
-  const size_t smem = (size_t)nb * 8 * p.xstride + (size_t)nb * 8 * (p.G + 1) * 4;
+  const size_t smem = (size_t)nb * 8 * p.xstride + (size_t)nb * 8 * (p.G + 2) * 4;
   // as many CTAs per SM as the staged token rows allow (up to 3: 24 warps keep enough loads in flight)
   int per_sm = (int)((220 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);

@@ -7,7 +7,7 @@
 // hardware), the token rows are staged once per expert in shared memory pre-scaled by 4^-f, and the per-(token,
 // group) sums of x remove the u = t + 1 offset. What TQ1 adds:
 //
-//   bytes -> fields   a 16 KB shared-memory table (the one the tcgen05 kernel uses, gemm_prefill.cu) maps a byte
+//   bytes -> fields   a shared-memory table (the entries the tcgen05 kernel uses, gemm_prefill.cu) maps a byte
 //                     to its five digits as 2-bit fields, placed for both positions a byte can take in a pair of
 //                     bytes; one AND-OR merges two entries into a word of five (even, odd) trit pairs, and five
 //                     ANDs give five A registers. Per byte: one table read and ~4.5 integer instructions, which
@@ -38,7 +38,7 @@ namespace {
 constexpr int D1_WARPS = 16;
 constexpr int D1_THREADS = D1_WARPS * 32;
 constexpr int D1_MT = 8;                       // token rows staged per pass
-constexpr int D1_LUT_BYTES = 256 * 16 * 4;     // 256 byte values x 16 bank replicas x 4 B
+constexpr int D1_LUT_BYTES = 256 * 32 * 4;     // 256 byte values x 32 bank replicas x 4 B: every lane reads its own bank
 constexpr int D1_EVEN_REGS = 5 * 48 + 3 * 16;  // 32-bit activation slots of an even superblock, per token
 constexpr int D1_ODD_REGS = 6 * 48 + 16 + 32 + 32;
 constexpr uint32_t D1_FIRST_MASK = 0x000F003Fu, D1_SECOND_MASK = 0x03F003C0u;
@@ -142,17 +142,12 @@ __host__ __device__ inline void d1_slot(int p, int r, int& klo, int& khi, int& f
 //   xexp[m]    = 2^e_m * row_scale[m]
 template <typename XT>
 __device__ void d1_stage_tokens(const Decode1Params& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, float* xsum,
-                                float* xexp) {
+                                float* xexp, int* xex) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int regs = d1_token_regs(p.S);
-  for (int m = warp; m < D1_MT; m += D1_WARPS) {
-    uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)m * p.xstride);
-    if (m >= mc) {  // unused token slots read as zero
-      for (int r = lane; r < regs; r += 32) dst[r] = 0u;
-      for (int g = lane; g < p.G; g += 32) xsum[m * p.G + g] = 0.f;
-      if (lane == 0) xexp[m] = 0.f;
-      continue;
-    }
+  // pass 1, one warp per token row: the row's power of two. Token slots beyond mc are never read (their B
+  // fragments are zero registers), so nothing is written for them.
+  for (int m = warp; m < mc; m += D1_WARPS) {
     const XT* row = x + (m0 + m) * p.K;
     float amax = 0.f;
     for (int k = lane; k < p.K; k += 32) amax = fmaxf(amax, fabsf((float)row[k]));
@@ -162,38 +157,47 @@ __device__ void d1_stage_tokens(const Decode1Params& p, const XT* __restrict__ x
       (void)frexpf(amax, &ex);
       ex -= 8;  // amax * 2^-ex in [128, 256)
     }
-    // group sums in natural k order: 32 lanes x 4 consecutive k per 128-trit group
-    for (int g = 0; g < p.G; ++g) {
-      float part = 0.f;
+    if (lane == 0) {
+      xex[m] = ex;
+      xexp[m] = ldexpf(1.f, ex) * (p.row_scale ? p.row_scale[m0 + m] : 1.f);
+    }
+  }
+  __syncthreads();
+  // pass 2, one warp per (token row, group): group sums in natural k order, 32 lanes x 4 consecutive k
+  for (int u = warp; u < mc * p.G; u += D1_WARPS) {
+    const int m = u / p.G, g = u - m * p.G;
+    const XT* row = x + (m0 + m) * p.K;
+    const int ex = xex[m];
+    float part = 0.f;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const int k = g * 128 + lane * 4 + h;
-        const int f = d1_trit_field((k % 320) >> 6, k & 63);
-        const __half v = __float2half_rn((float)row[k] * ldexpf(1.f, 7 - ex - 2 * f));
-        part += __half2float(v) * ldexpf(1.f, 2 * f - 7);
-      }
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      if (lane == 0) xsum[m * p.G + g] = part;
+    for (int h = 0; h < 4; ++h) {
+      const int k = g * 128 + lane * 4 + h;
+      const int f = d1_trit_field((k % 320) >> 6, k & 63);
+      const __half v = __float2half_rn((float)row[k] * ldexpf(1.f, 7 - ex - 2 * f));
+      part += __half2float(v) * ldexpf(1.f, 2 * f - 7);
     }
-    // the slots, in consumption order
-    for (int r = lane; r < regs; r += 32) {
-      const int pair = r / (D1_EVEN_REGS + D1_ODD_REGS), rr = r - pair * (D1_EVEN_REGS + D1_ODD_REGS);
-      const int par = rr >= D1_EVEN_REGS ? 1 : 0, sb = 2 * pair + par;
-      int klo, khi, f;
-      d1_slot(par, par ? rr - D1_EVEN_REGS : rr, klo, khi, f);
-      const float mul = ldexpf(1.f, 7 - ex - 2 * f);
-      uint32_t lo = 0u, hi = 0u;
-      if (klo >= 0 && sb * 320 + klo < p.K) lo = __half_as_ushort(__float2half_rn((float)row[sb * 320 + klo] * mul));
-      if (khi >= 0 && sb * 320 + khi < p.K) hi = __half_as_ushort(__float2half_rn((float)row[sb * 320 + khi] * mul));
-      dst[r] = lo | (hi << 16);
-    }
-    if (lane == 0) xexp[m] = ldexpf(1.f, ex) * (p.row_scale ? p.row_scale[m0 + m] : 1.f);
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    if (lane == 0) xsum[m * p.G + g] = part;
+  }
+  // pass 3, one thread per slot: the rows in consumption order (zeros where a lane sits out a set)
+  for (int idx = threadIdx.x; idx < mc * regs; idx += D1_THREADS) {
+    const int m = idx / regs, r = idx - m * regs;
+    const XT* row = x + (m0 + m) * p.K;
+    const int pair = r / (D1_EVEN_REGS + D1_ODD_REGS), rr = r - pair * (D1_EVEN_REGS + D1_ODD_REGS);
+    const int par = rr >= D1_EVEN_REGS ? 1 : 0, sb = 2 * pair + par;
+    int klo, khi, f;
+    d1_slot(par, par ? rr - D1_EVEN_REGS : rr, klo, khi, f);
+    const float mul = ldexpf(1.f, 7 - xex[m] - 2 * f);
+    uint32_t lo = 0u, hi = 0u;
+    if (klo >= 0 && sb * 320 + klo < p.K) lo = __half_as_ushort(__float2half_rn((float)row[sb * 320 + klo] * mul));
+    if (khi >= 0 && sb * 320 + khi < p.K) hi = __half_as_ushort(__float2half_rn((float)row[sb * 320 + khi] * mul));
+    reinterpret_cast<uint32_t*>(xs + (size_t)m * p.xstride)[r] = lo | (hi << 16);
   }
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
 __device__ __forceinline__ uint32_t d1_lookup(uint32_t lut_addr, uint32_t word, int byte) {
-  const uint32_t idx = byte == 0 ? (word << 6) & 0x3FC0u : (word >> (8 * byte - 6)) & 0x3FC0u;  // byte value * 64
+  const uint32_t idx = byte == 0 ? (word << 7) & 0x7F80u : (word >> (8 * byte - 7)) & 0x7F80u;  // byte value * 128
   uint32_t v;
   asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lut_addr + idx));
   return v;
@@ -212,9 +216,15 @@ __device__ __forceinline__ void d1_word_regs(uint32_t word, uint32_t lut_addr, u
 }
 
 // One regular set: five MMAs of this lane's ten A registers (two weight rows) against its twelve-slot block.
-__device__ __forceinline__ void d1_set(float* acc, const uint32_t* al, const uint32_t* ah, const uint8_t* xblock) {
-  const uint4 b0 = *reinterpret_cast<const uint4*>(xblock), b1 = *reinterpret_cast<const uint4*>(xblock + 16);
-  const uint2 b2 = *reinterpret_cast<const uint2*>(xblock + 32);
+// live: this lane's token column exists; the others feed zero registers and cause no shared-memory traffic.
+__device__ __forceinline__ void d1_set(float* acc, const uint32_t* al, const uint32_t* ah, const uint8_t* xblock, bool live) {
+  uint4 b0 = make_uint4(0u, 0u, 0u, 0u), b1 = b0;
+  uint2 b2 = make_uint2(0u, 0u);
+  if (live) {
+    b0 = *reinterpret_cast<const uint4*>(xblock);
+    b1 = *reinterpret_cast<const uint4*>(xblock + 16);
+    b2 = *reinterpret_cast<const uint2*>(xblock + 32);
+  }
   mma_f16(acc, al[0], ah[0], al[1], ah[1], b0.x, b0.y);
   mma_f16(acc, al[2], ah[2], al[3], ah[3], b0.z, b0.w);
   mma_f16(acc, al[4], ah[4], al[5], ah[5], b1.x, b1.y);
@@ -226,8 +236,8 @@ __device__ __forceinline__ void d1_set(float* acc, const uint32_t* al, const uin
 // xsb: this token row's slots of the superblock, already offset by the lane's quad position (c * 48 bytes for
 // the regular sets is added here, as are the shared sets' offsets).
 template <int P>
-__device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4, const uint8_t* xsb, int c, uint32_t lut_addr,
-                                              float (&acc)[3][4]) {
+__device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4, const uint8_t* xsb, int c, bool live,
+                                              uint32_t lut_addr, float (&acc)[3][4]) {
   const uint32_t wl[4] = {wl4.x, wl4.y, wl4.z, wl4.w}, wh[4] = {wh4.x, wh4.y, wh4.z, wh4.w};
   const uint8_t* xreg = xsb + c * 48;
   int q = 0;
@@ -239,10 +249,10 @@ __device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4
     // groups that the four lanes' words of this step belong to (compile-time, see d1_slot)
     const int a_first = P == 0 ? (j == 0 ? 0 : j == 1 ? 0 : j == 2 ? 1 : 2) : (j == 0 ? 0 : j == 1 ? 1 : j == 2 ? 1 : 2);
     const bool two = P == 0 ? j == 1 : (j == 0 || j == 2);
-    d1_set(acc[a_first], al, ah, xreg + q * 192);
+    d1_set(acc[a_first], al, ah, xreg + q * 192, live);
     ++q;
     if (two) {
-      d1_set(acc[a_first + 1], al, ah, xreg + q * 192);
+      d1_set(acc[a_first + 1], al, ah, xreg + q * 192, live);
       ++q;
     }
   }
@@ -254,7 +264,7 @@ __device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4
 #pragma unroll
     for (int a = 0; a < 3; ++a) {
       const uint32_t mask = a == 0 ? 0x00030003u : a == 1 ? 0x000C000Cu : 0x00000030u;  // digits (2a, 2a+1) of a "first byte" entry
-      const uint4 b = *reinterpret_cast<const uint4*>(xsh + a * 64);
+      const uint4 b = live ? *reinterpret_cast<const uint4*>(xsh + a * 64) : make_uint4(0u, 0u, 0u, 0u);
       mma_f16(acc[a], sl[0] & mask, sh[0] & mask, sl[1] & mask, sh[1] & mask, b.x, b.y);
       mma_f16(acc[a], sl[2] & mask, sh[2] & mask, sl[3] & mask, sh[3] & mask, b.z, b.w);
     }
@@ -262,7 +272,7 @@ __device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4
     // digit masks of a "first byte" entry: d0 0x3, d1 0x30000, d2 0xC, d3 0xC0000, d4 0x30
     const uint8_t* x0 = xsb + 288 * 4 + c * 16;
     {
-      const uint4 b = *reinterpret_cast<const uint4*>(x0);
+      const uint4 b = live ? *reinterpret_cast<const uint4*>(x0) : make_uint4(0u, 0u, 0u, 0u);
       mma_f16(acc[0], sl[0] & 0x3u, sh[0] & 0x3u, sl[1] & 0x3u, sh[1] & 0x3u, b.x, b.y);
       mma_f16(acc[0], sl[2] & 0x3u, sh[2] & 0x3u, sl[3] & 0x3u, sh[3] & 0x3u, b.z, b.w);
     }
@@ -270,7 +280,8 @@ __device__ __forceinline__ void d1_superblock(const uint4& wl4, const uint4& wh4
     for (int a = 0; a < 2; ++a) {  // group 1: digits 1, 2; group 2: digits 3, 4 (slot t: byte t >> 1, first or second digit)
       const uint32_t me = a == 0 ? 0x00030000u : 0x000C0000u, mo = a == 0 ? 0x0000000Cu : 0x00000030u;
       const uint8_t* xa = xsb + (288 + 16) * 4 + a * 128 + c * 32;
-      const uint4 b0 = *reinterpret_cast<const uint4*>(xa), b1 = *reinterpret_cast<const uint4*>(xa + 16);
+      const uint4 b0 = live ? *reinterpret_cast<const uint4*>(xa) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 b1 = live ? *reinterpret_cast<const uint4*>(xa + 16) : make_uint4(0u, 0u, 0u, 0u);
       mma_f16(acc[1 + a], sl[0] & me, sh[0] & me, sl[0] & mo, sh[0] & mo, b0.x, b0.y);
       mma_f16(acc[1 + a], sl[1] & me, sh[1] & me, sl[1] & mo, sh[1] & mo, b0.z, b0.w);
       mma_f16(acc[1 + a], sl[2] & me, sh[2] & me, sl[2] & mo, sh[2] & mo, b1.x, b1.y);
@@ -286,12 +297,13 @@ decode_tq1_kernel(const Decode1Params p) {
   uint8_t* xs = dsm + D1_LUT_BYTES;                                              // D1_MT staged token rows
   float* xsum = reinterpret_cast<float*>(xs + (size_t)D1_MT * p.xstride);        // [D1_MT][G]
   float* xexp = xsum + D1_MT * p.G;                                              // [D1_MT]
+  int* xex = reinterpret_cast<int*>(xexp + D1_MT);                               // [D1_MT] exponent of the row's power of two
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
   {
     uint32_t* lut32 = reinterpret_cast<uint32_t*>(lut);  // [byte value][replica]
-    for (int i = threadIdx.x; i < 256 * 16; i += D1_THREADS) lut32[i] = d1_table_entry((uint32_t)i >> 4);
+    for (int i = threadIdx.x; i < 256 * 32; i += D1_THREADS) lut32[i] = d1_table_entry((uint32_t)i >> 5);
   }
-  const uint32_t lut_addr = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)(lane & 15) * 4u;
+  const uint32_t lut_addr = (uint32_t)__cvta_generic_to_shared(lut) + (uint32_t)lane * 4u;
 
   // work items: (expert, pair of neighbouring 128-row tiles); a contiguous range per CTA
   const int NTP = (p.NT + 1) >> 1;
@@ -310,8 +322,8 @@ decode_tq1_kernel(const Decode1Params p) {
       const int mc = (int)(rb - m0 < D1_MT ? rb - m0 : D1_MT);
       if (staged_e != e || staged_m0 != m0) {
         __syncthreads();  // everyone is done with the previous rows (and the table is written)
-        if (p.act_dtype == DST_ACT_BF16) d1_stage_tokens(p, static_cast<const __nv_bfloat16*>(p.x), m0, mc, xs, xsum, xexp);
-        else d1_stage_tokens(p, static_cast<const __half*>(p.x), m0, mc, xs, xsum, xexp);
+        if (p.act_dtype == DST_ACT_BF16) d1_stage_tokens(p, static_cast<const __nv_bfloat16*>(p.x), m0, mc, xs, xsum, xexp, xex);
+        else d1_stage_tokens(p, static_cast<const __half*>(p.x), m0, mc, xs, xsum, xexp, xex);
         __syncthreads();
         staged_e = e;
         staged_m0 = m0;
@@ -321,6 +333,7 @@ decode_tq1_kernel(const Decode1Params p) {
       const int swz = (r0 >> 1) & 3;
       const int n_lo = nt * 128 + r0, n_hi = n_lo + 8;
       const uint8_t* xtok = xs + (size_t)g8 * p.xstride;  // the token column this lane feeds (B fragment column g8)
+      const bool live = g8 < mc;
       float y[4] = {0.f, 0.f, 0.f, 0.f};
 
       auto flush = [&](const float* acc, int grp, float sl, float sh) {
@@ -363,7 +376,7 @@ decode_tq1_kernel(const Decode1Params p) {
           for (int a = 0; a < 3; ++a)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[a][i] = 0.f;
-          d1_superblock<0>(cl0, ch0, xtok + (size_t)d1_sb_offset(sb) * 4, c, lut_addr, acc);
+          d1_superblock<0>(cl0, ch0, xtok + (size_t)d1_sb_offset(sb) * 4, c, live, lut_addr, acc);
           flush(acc[0], gb, sl[0], sh[0]);
           flush(acc[1], gb + 1, sl[1], sh[1]);
 #pragma unroll
@@ -372,7 +385,7 @@ decode_tq1_kernel(const Decode1Params p) {
             acc[1][i] = 0.f;
             acc[2][i] = 0.f;
           }
-          if (sb + 1 < p.S) d1_superblock<1>(cl1, ch1, xtok + (size_t)d1_sb_offset(sb + 1) * 4, c, lut_addr, acc);
+          if (sb + 1 < p.S) d1_superblock<1>(cl1, ch1, xtok + (size_t)d1_sb_offset(sb + 1) * 4, c, live, lut_addr, acc);
           flush(acc[0], gb + 2, sl[2], sh[2]);
           flush(acc[1], gb + 3, sl[3], sh[3]);
           flush(acc[2], gb + 4, sl[4], sh[4]);
@@ -406,7 +419,7 @@ int d1_xstride(int S) {
   return bytes;
 }
 
-size_t d1_smem(int S, int G) { return (size_t)D1_LUT_BYTES + (size_t)D1_MT * d1_xstride(S) + (size_t)D1_MT * (G + 1) * 4; }
+size_t d1_smem(int S, int G) { return (size_t)D1_LUT_BYTES + (size_t)D1_MT * d1_xstride(S) + (size_t)D1_MT * (G + 2) * 4; }
 
 }  // namespace
 
