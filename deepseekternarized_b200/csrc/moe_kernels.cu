@@ -230,6 +230,112 @@ __device__ __forceinline__ int norm_exponent(float amax) {
   return ex;
 }
 
+// Eight bf16 (one 128-bit load) <-> floats, eight floats -> eight fp16 / bf16 (one 128-bit store).
+__device__ __forceinline__ void bf16x8_to_float(const uint4& q, float* f) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 float8_to_f16(const float* f, float mul) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(f[2 * i] * mul, f[2 * i + 1] * mul);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ uint4 float8_to_bf16(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Single-pass forms of the two kernels below for rows of K % 8 == 0, K <= 2048 J elements: a thread keeps its J
+// 16-byte chunks in registers between the maximum and the store, so every byte is read once, 128 bits at a time.
+template <int J>
+__global__ void __launch_bounds__(256)
+gather_rows_norm_vec_kernel(const __nv_bfloat16* __restrict__ src, const int64_t* __restrict__ order, int64_t K, int top_k,
+                            __half* __restrict__ dst, float* __restrict__ factor) {
+  __shared__ float red[32];
+  const int64_t p = blockIdx.x;
+  const int64_t t = order ? order[p] / top_k : p;
+  const uint4* s = reinterpret_cast<const uint4*>(src + t * K);
+  const int chunks = (int)(K >> 3);
+  float v[J][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) {
+      bf16x8_to_float(s[c], v[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+    }
+  }
+  const int ex = norm_exponent(block_max(amax, red));
+  const float down = ldexpf(1.f, -ex);
+  uint4* d = reinterpret_cast<uint4*>(dst + p * K);
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) d[c] = float8_to_f16(v[j], down);
+  }
+  if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
+}
+
+template <int J>
+__global__ void __launch_bounds__(256)
+swiglu_norm_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route_weights, const int64_t* __restrict__ order,
+                       int64_t inter, float limit, __half* __restrict__ h, float* __restrict__ factor) {
+  __shared__ float red[32];
+  const int64_t p = blockIdx.x;
+  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const uint4* g = reinterpret_cast<const uint4*>(gu + p * 2 * inter);
+  const uint4* u = reinterpret_cast<const uint4*>(gu + p * 2 * inter + inter);
+  const int chunks = (int)(inter >> 3);
+  float v[J][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) {
+      float gate[8], up[8];
+      bf16x8_to_float(g[c], gate);
+      bf16x8_to_float(u[c], up);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float ga = gate[i], uu = up[i];
+        if (limit > 0.f) {
+          uu = fminf(fmaxf(uu, -limit), limit);
+          ga = fminf(ga, limit);
+        }
+        float x = (ga / (1.f + expf(-ga))) * uu;
+        if (route_weights) x = w * x;
+        x = __bfloat162float(__float2bfloat16_rn(x));  // the reference's rounding point
+        v[j][i] = x;
+        amax = fmaxf(amax, fabsf(x));
+      }
+    }
+  }
+  const int ex = norm_exponent(block_max(amax, red));
+  const float down = ldexpf(1.f, -ex);
+  uint4* d = reinterpret_cast<uint4*>(h + p * inter);
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) d[c] = float8_to_f16(v[j], down);
+  }
+  if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
+}
+
 // dst[p, :] = fp16(src[order[p] / top_k, :] * 2^-e_p), factor[p] = 2^e_p; one block per row, K <= 8 * 1024 per thread loop
 __global__ void gather_rows_norm_kernel(const __nv_bfloat16* __restrict__ src, const int64_t* __restrict__ order, int64_t K,
                                         int top_k, __half* __restrict__ dst, float* __restrict__ factor) {
@@ -329,6 +435,43 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ down, const int
   }
 }
 
+
+// combine_kernel for hidden % 8 == 0: 128-bit loads and stores.
+__global__ void __launch_bounds__(256)
+combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int top_k,
+                   int64_t hidden, __nv_bfloat16* __restrict__ y) {
+  const int64_t t = blockIdx.x;
+  int64_t pos[8];
+  int eid[8];
+  for (int s = 0; s < top_k; ++s) {
+    pos[s] = inv[t * top_k + s];
+    eid[s] = ids[t * top_k + s];
+  }
+  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
+    const int e = eid[i];
+    const int64_t p = pos[i];
+    int j = i - 1;
+    while (j >= 0 && eid[j] > e) {
+      eid[j + 1] = eid[j];
+      pos[j + 1] = pos[j];
+      --j;
+    }
+    eid[j + 1] = e;
+    pos[j + 1] = p;
+  }
+  const int chunks = (int)(hidden >> 3);
+  for (int c = threadIdx.x; c < chunks; c += 256) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < top_k; ++s) {
+      float f[8];
+      bf16x8_to_float(reinterpret_cast<const uint4*>(down + pos[s] * hidden)[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    reinterpret_cast<uint4*>(y + t * hidden)[c] = float8_to_bf16(acc);
+  }
+}
+
 }  // namespace
 }  // namespace dst
 
@@ -413,6 +556,17 @@ extern "C" int dst_gather_rows_norm(const void* src_bf16, const int64_t* order, 
   if (n_rows == 0) return DST_OK;
   if (!src_bf16 || !dst_f16 || !row_factor) return DST_ERR_BAD_ARG;
   if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  const bool vec = K % 8 == 0 && K <= 8192 && (reinterpret_cast<uintptr_t>(src_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst_f16) & 15) == 0;
+  if (vec) {
+    auto st = static_cast<cudaStream_t>(stream);
+    auto a = static_cast<const __nv_bfloat16*>(src_bf16);
+    auto d = static_cast<__half*>(dst_f16);
+    if (K <= 2048) gather_rows_norm_vec_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(a, order, K, top_k, d, row_factor);
+    else if (K <= 4096) gather_rows_norm_vec_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(a, order, K, top_k, d, row_factor);
+    else gather_rows_norm_vec_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(a, order, K, top_k, d, row_factor);
+    DST_CUDA_TRY(cudaGetLastError());
+    return DST_OK;
+  }
   gather_rows_norm_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src_bf16), order, K, top_k, static_cast<__half*>(dst_f16), row_factor);
   DST_CUDA_TRY(cudaGetLastError());
@@ -425,6 +579,17 @@ extern "C" int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, 
   if (n_rows == 0) return DST_OK;
   if (!gu_bf16 || !h_f16 || !row_factor) return DST_ERR_BAD_ARG;
   if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  const bool vec = inter % 8 == 0 && inter <= 8192 && (reinterpret_cast<uintptr_t>(gu_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(h_f16) & 15) == 0;
+  if (vec) {
+    auto st = static_cast<cudaStream_t>(stream);
+    auto a = static_cast<const __nv_bfloat16*>(gu_bf16);
+    auto d = static_cast<__half*>(h_f16);
+    if (inter <= 2048) swiglu_norm_vec_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
+    else if (inter <= 4096) swiglu_norm_vec_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
+    else swiglu_norm_vec_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
+    DST_CUDA_TRY(cudaGetLastError());
+    return DST_OK;
+  }
   swiglu_norm_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gu_bf16), route_weights, order, inter, limit, static_cast<__half*>(h_f16), row_factor);
   DST_CUDA_TRY(cudaGetLastError());
@@ -441,8 +606,12 @@ extern "C" int dst_combine(const void* down_bf16, const int64_t* order, const in
   const int64_t n = T * top_k;
   invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
   DST_CUDA_TRY(cudaGetLastError());
-  combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
-                                             static_cast<__nv_bfloat16*>(y_bf16));
+  if (hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(down_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(y_bf16) & 15) == 0)
+    combine_vec_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
+                                                   static_cast<__nv_bfloat16*>(y_bf16));
+  else
+    combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
+                                               static_cast<__nv_bfloat16*>(y_bf16));
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }
