@@ -15,20 +15,21 @@
 //                    dequantised tile never passes through shared memory
 //   B (activations)  fp16 rows fetched by one thread with cp.async.bulk.tensor (TMA) into K-major,
 //                    128-byte-swizzled shared-memory stages (one box for up to 256 rows, two for more)
-//   D (accumulator)  fp32 in TMEM columns 0..319 (tiles of more than 256 token rows are two MMAs per K step,
-//                    each over half of the rows); columns 320..511 hold the A ring (stage s = slot s)
+//   D (accumulator)  fp32 in TMEM columns 0..319 (two MMAs per K step, each over half of the token rows, from two
+//                    issuing threads); columns 320..511 hold the A ring (stage s = slot s)
 // Shared-memory bandwidth is what bounds this kernel when A goes through shared memory (measured: the MMA
 // issuer stalled ~1100 cycles per 512-cycle stage); with A in TMEM only B is written and read there.
 // bf16 activations are converted once to fp16 with a power-of-two factor per row (exact for every
 // element within 2^-22 of the row's absolute maximum); the factor comes back through row_scale.
 // tcgen05 kind::f16 refuses an fp16 A with a bf16 B (illegal instruction), hence the conversion.
 //
-// Warp roles (736 threads, one CTA per SM, persistent over tiles):
+// Warp roles (896 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer for B (one thread)
-//   warp 1      MMA issuer (one thread), owns the TMEM allocation
+//   warp 1, 3   MMA issuers (one thread each, each over half of a tile's token rows); warp 1 owns the TMEM allocation
 //   warp 2      bulk-copy producer of the packed slabs (one thread)
-//   warps 3-6   epilogue: TMEM -> registers -> global, one warp per TMEM lane quarter (warp id % 4)
-//   warps 7-22  dequant producers for A, in four groups of four warps: group g owns the stages with global
+//   warps 4-11  epilogue: TMEM -> registers -> global, two warps per TMEM lane quarter (warp id % 4) taking
+//               alternate 32-column chunks
+//   warps 12-27 dequant producers for A, in four groups of four warps: group g owns the stages with global
 //               index = g (mod 4), so four stages are dequantised at once (each warp's instruction stream is a
 //               long dependent chain; one group per stage could not keep up with the MMAs); inside a group
 //               the warp with id % 4 == q owns the 32 weight rows of TMEM lane quarter q, one thread per row
@@ -50,8 +51,8 @@
 namespace dst {
 namespace {
 
-constexpr int PF_CTRL_WARPS = 3;
-constexpr int PF_EPI_WARPS = 4;              // accumulator drain, one warp per TMEM lane quarter
+constexpr int PF_CTRL_WARPS = 4;
+constexpr int PF_EPI_WARPS = 8;              // accumulator drain, two warps per TMEM lane quarter
 constexpr int PF_GROUPS = 4;                 // dequant warp groups (4 warps each, one per TMEM lane quarter)
 constexpr int PF_DQ_WARPS = 4 * PF_GROUPS;
 constexpr int PF_DQ_WARP0 = PF_CTRL_WARPS + PF_EPI_WARPS;
@@ -392,9 +393,9 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     abort_s = 0;
     for (int s = 0; s < PF_MAX_STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1 + 4);  // the TMA producer's expect_tx arrive + one arrive per warp of the dequant group that owns the stage
-      mbar_init(smem_u32(&bar_empty[s]), 1);     // tcgen05.commit: the MMAs that read the stage are done
+      mbar_init(smem_u32(&bar_empty[s]), 2);     // one tcgen05.commit per MMA issuer: the MMAs that read the stage are done
     }
-    mbar_init(smem_u32(&bar_tfull[0]), 1);             // tcgen05.commit after the tile's last MMA
+    mbar_init(smem_u32(&bar_tfull[0]), 2);             // one tcgen05.commit per MMA issuer after the tile's last MMA
     mbar_init(smem_u32(&bar_tempty[0]), PF_EPI_WARPS);  // every epilogue warp has drained its quarter of the accumulator
     for (int a = 0; a < PF_MAX_SLABS; ++a) {
       mbar_init(smem_u32(&bar_pfull[a]), 1);         // bulk-copy producer's expect_tx arrive
@@ -487,9 +488,15 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
       }
       RT_ADD(5, RT_NOW() - t_begin); RT_ADD(1, w_pempty);
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Two threads (in two warps, on two scheduler partitions) issue the MMAs of a stage: each owns half of the token
+    // rows (its own accumulator columns and its own half of the B stage), so a stage costs each of them four
+    // instructions instead of eight; a single thread could not issue them as fast as the tensor pipe runs them.
+    // Tiles whose row count (padded to 16) is not a multiple of 32, or below 64, are issued by the first thread
+    // alone; the second then only adds its arrivals to the barriers.
     if (lane == 0) {
+      const uint32_t who = warp == 1 ? 0u : 1u;
       uint32_t s = 0, ph = 0, tile = 0;
       bool ok = true;
       const uint64_t b_desc0 = umma_desc(smem_u32(smem));
@@ -501,29 +508,29 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t n_eff = (uint32_t)tile_neff(rows);
-        const uint32_t h = n_eff > 256u ? n_eff >> 1 : n_eff;
-        const bool two = h != n_eff;
+        const bool split = n_eff >= 64u && (n_eff & 31u) == 0u;  // tiles above 256 rows are padded to 32: always split
+        const uint32_t h = split ? n_eff >> 1 : n_eff;           // token rows per MMA (a multiple of 16, at most 256)
+        const bool active = split || who == 0u;
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
         const uint32_t idesc = (1u << 4) | ((h >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t half_off = (h * 128u) >> 4;  // second half of the rows: descriptor start-address units
+        const uint32_t mine = split ? who * h : 0u;              // first token row (= accumulator column) of this thread's MMAs
+        const uint32_t d_tmem = tmem + mine;
+        const uint32_t b_off = (mine * 128u) >> 4;               // descriptor start-address units
         for (int ks = 0; ks < p.kstages; ++ks) {
           if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_tmem = tmem + PF_TN_MAX + s * PF_A_COLS;  // this stage's slot of the A ring
-          // only the start-address field of the B descriptor changes with the stage, the K step and the half
-          const uint32_t b_lo = b_desc_lo + s * (stage_bytes >> 4);
+          if (active) {
+            const uint32_t a_tmem = tmem + PF_TN_MAX + s * PF_A_COLS;  // this stage's slot of the A ring
+            // only the start-address field of the B descriptor changes with the stage, the K step and the half
+            const uint32_t b_lo = b_desc_lo + s * (stage_bytes >> 4) + b_off;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-            uint64_t db;
-            asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2), "r"(b_desc_hi));
-            umma_f16_ts(tmem, a_tmem + kk * 8, db, idesc, acc);
-            if (two) {
-              asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2 + half_off), "r"(b_desc_hi));
-              umma_f16_ts(tmem + h, a_tmem + kk * 8, db, idesc, acc);
+            for (int kk = 0; kk < 4; ++kk) {
+              uint64_t db;
+              asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2), "r"(b_desc_hi));
+              umma_f16_ts(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
             }
           }
-          umma_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs have read it
+          umma_commit(smem_u32(&bar_empty[s]));  // this thread's MMAs (if any) have read the stage
           if (++s == NB) { s = 0; ph ^= 1u; }
 #ifdef DST_ROLE_TIMERS
           ++n_it;
@@ -532,7 +539,9 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         if (ok) umma_commit(smem_u32(&bar_tfull[0]));
         ++tile;
       }
-      RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, n_it); RT_ADD(12, 1); RT_ADD(13, tile);
+      if (who == 0u) {
+        RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, n_it); RT_ADD(12, 1); RT_ADD(13, tile);
+      }
     }
   } else if (warp < PF_DQ_WARP0) {
     // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
@@ -540,7 +549,10 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     uint32_t tile = 0;
     for (int t = (int)blockIdx.x; t < n_tiles; t += t_step, ++tile) {
       tile_seek(p, offs, tpre, t, e, nt, row0, rows);
-      if (!drain_tile(p, tmem, 0, 32, r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]), abort_flag, nt, row0, rows, tile)) break;
+      // the two warps of a lane quarter take alternate 32-column chunks
+      if (!drain_tile(p, tmem, ((warp - PF_CTRL_WARPS) >> 2) * 32, 32 * (PF_EPI_WARPS / 4), r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]),
+                      abort_flag, nt, row0, rows, tile))
+        break;
     }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
