@@ -11,7 +11,7 @@ namespace {
 // rounds of warp arg-max (equal scores: lower expert id wins), then renormalised.
 constexpr int ROUTE_MAX_PER_LANE = 32;  // E <= 1024
 
-__global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E, int top_k, float route_scale,
+__global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E, int top_k, int renorm, float route_scale,
                              float* __restrict__ weights, int32_t* __restrict__ ids) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -65,9 +65,9 @@ __global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E,
     wsum += wsel[r];
   }
   if (lane == 0) {
-    const float d = top_k > 1 ? 1.f / (wsum + 1e-20f) : 1.f;
+    const float d = (renorm && top_k > 1) ? 1.f / (wsum + 1e-20f) : 1.f;
     for (int r = 0; r < top_k; ++r) {
-      weights[t * top_k + r] = (top_k > 1 ? wsel[r] * d : wsel[r]) * route_scale;
+      weights[t * top_k + r] = ((renorm && top_k > 1) ? wsel[r] * d : wsel[r]) * route_scale;
       ids[t * top_k + r] = isel[r];
     }
   }
@@ -472,20 +472,96 @@ combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __rest
   }
 }
 
+
+// ---------------------------------------------------------------------- standard (OLMoE-style) flavour
+// boilerplate/engine/standard.py:149-176 keeps every intermediate in the model dtype (bf16): the expert output is
+// down( bf16( bf16(silu(gate)) * up ) ), multiplied by the bf16 routing weight (rounded to bf16) and added into a
+// bf16 output row, one rounding per addition, experts in increasing id.
+template <bool NORM>
+__global__ void swiglu_std_kernel(const __nv_bfloat16* __restrict__ gu, int64_t inter, __nv_bfloat16* __restrict__ h_bf16,
+                                  __half* __restrict__ h_f16, float* __restrict__ factor) {
+  __shared__ float red[32];
+  const int64_t p = blockIdx.x;
+  const __nv_bfloat16* g = gu + p * 2 * inter;
+  const __nv_bfloat16* u = g + inter;
+  auto value = [&](int64_t i) {
+    const float gate = __bfloat162float(g[i]);
+    const float sg = __bfloat162float(__float2bfloat16_rn(gate / (1.f + expf(-gate))));  // silu in fp32, stored as bf16
+    return __bfloat162float(__float2bfloat16_rn(sg * __bfloat162float(u[i])));           // bf16 * bf16 -> bf16
+  };
+  if (!NORM) {
+    for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) h_bf16[p * inter + i] = __float2bfloat16_rn(value(i));
+    return;
+  }
+  float amax = 0.f;
+  for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) amax = fmaxf(amax, fabsf(value(i)));
+  const int ex = norm_exponent(block_max(amax, red));
+  const float down = ldexpf(1.f, -ex);
+  for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) h_f16[p * inter + i] = __float2half_rn(value(i) * down);
+  if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
+}
+
+// One block per token: y = sum over its slots in increasing expert id of bf16(down * bf16(weight)), every partial
+// sum rounded to bf16 (the reference accumulates with index_add_ into a bf16 tensor).
+__global__ void combine_weighted_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv,
+                                        const int32_t* __restrict__ ids, const float* __restrict__ weights, int top_k, int64_t hidden,
+                                        __nv_bfloat16* __restrict__ y) {
+  const int64_t t = blockIdx.x;
+  int64_t pos[8];
+  int eid[8];
+  float wv[8];
+  for (int s = 0; s < top_k; ++s) {
+    pos[s] = inv[t * top_k + s];
+    eid[s] = ids[t * top_k + s];
+    wv[s] = __bfloat162float(__float2bfloat16_rn(weights[t * top_k + s]));
+  }
+  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
+    const int e = eid[i];
+    const int64_t p = pos[i];
+    const float w = wv[i];
+    int j = i - 1;
+    while (j >= 0 && eid[j] > e) {
+      eid[j + 1] = eid[j];
+      pos[j + 1] = pos[j];
+      wv[j + 1] = wv[j];
+      --j;
+    }
+    eid[j + 1] = e;
+    pos[j + 1] = p;
+    wv[j + 1] = w;
+  }
+  for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < top_k; ++s) {
+      const float r = __bfloat162float(__float2bfloat16_rn(__bfloat162float(down[pos[s] * hidden + c]) * wv[s]));
+      acc = __bfloat162float(__float2bfloat16_rn(acc + r));
+    }
+    y[t * hidden + c] = __float2bfloat16_rn(acc);
+  }
+}
+
 }  // namespace
 }  // namespace dst
 
 using namespace dst;
 
+extern "C" int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
+                                         float* weights, int32_t* ids, dst_stream_t stream);
+
 extern "C" int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
                                       float* weights, int32_t* ids, dst_stream_t stream) {
+  return dst_route_softmax_topk_ex(logits, T, E, top_k, 1, route_scale, weights, ids, stream);
+}
+
+extern "C" int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
+                                         float* weights, int32_t* ids, dst_stream_t stream) {
   if (T < 0 || E <= 0 || top_k <= 0) return DST_ERR_BAD_ARG;
   if (E > 32 * ROUTE_MAX_PER_LANE || top_k > 8 || top_k > E) return DST_ERR_UNSUPPORTED;
   if (T == 0) return DST_OK;
   if (!logits || !weights || !ids) return DST_ERR_BAD_ARG;
   const int warps = 4;
   route_kernel<<<(unsigned)cdiv64(T, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, T, (int)E, top_k, route_scale, weights, ids);
+      logits, T, (int)E, top_k, renorm, route_scale, weights, ids);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }
@@ -612,6 +688,45 @@ extern "C" int dst_combine(const void* down_bf16, const int64_t* order, const in
   else
     combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
                                                static_cast<__nv_bfloat16*>(y_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_swiglu_std(const void* gu_bf16, int64_t n_rows, int64_t inter, void* h_bf16, dst_stream_t stream) {
+  if (n_rows < 0 || inter <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!gu_bf16 || !h_bf16) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  swiglu_std_kernel<false><<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu_bf16), inter, static_cast<__nv_bfloat16*>(h_bf16), nullptr, nullptr);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_swiglu_std_norm(const void* gu_bf16, int64_t n_rows, int64_t inter, void* h_f16, float* row_factor,
+                                   dst_stream_t stream) {
+  if (n_rows < 0 || inter <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows == 0) return DST_OK;
+  if (!gu_bf16 || !h_f16 || !row_factor) return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  swiglu_std_kernel<true><<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu_bf16), inter, nullptr, static_cast<__half*>(h_f16), row_factor);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_combine_weighted(const void* down_bf16, const int64_t* order, const int32_t* ids, const float* weights, int64_t T,
+                                    int top_k, int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream) {
+  if (T < 0 || top_k <= 0 || top_k > 8 || hidden <= 0) return DST_ERR_BAD_ARG;
+  if (T == 0) return DST_OK;
+  if (!down_bf16 || !order || !ids || !weights || !inv || !y_bf16) return DST_ERR_BAD_ARG;
+  if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t n = T * top_k;
+  invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
+  DST_CUDA_TRY(cudaGetLastError());
+  combine_weighted_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, weights, top_k, hidden,
+                                                      static_cast<__nv_bfloat16*>(y_bf16));
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

@@ -86,15 +86,15 @@ class B200Ops:
     def _lib():
         return kb._require("auto")
 
-    def route(self, logits: torch.Tensor, top_k: int, route_scale: float):
+    def route(self, logits: torch.Tensor, top_k: int, route_scale: float, renorm: bool = True):
         lib = self._lib()
         logits = logits.float().contiguous()
         T, E = logits.shape
         w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
         ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
         with torch.cuda.device(logits.device):
-            _lib.check(lib.dst_route_softmax_topk(logits.data_ptr(), T, E, top_k, ctypes.c_float(route_scale), w.data_ptr(),
-                                                  ids.data_ptr(), kb._stream(logits)))
+            _lib.check(lib.dst_route_softmax_topk_ex(logits.data_ptr(), T, E, top_k, 1 if renorm else 0, ctypes.c_float(route_scale),
+                                                     w.data_ptr(), ids.data_ptr(), kb._stream(logits)))
         return w, ids
 
     def sort(self, ids: torch.Tensor, n_experts: int):
@@ -142,6 +142,34 @@ class B200Ops:
                                       ctypes.c_float(limit), h.data_ptr(), kb._stream(gu)))
         return h
 
+    def swiglu_std(self, gu: torch.Tensor, inter: int, for_weights=None):
+        """boilerplate/engine/standard.py:149-152: bf16(bf16(silu(gate)) * up), no routing weight."""
+        lib = self._lib()
+        if for_weights is not None and self._norm_ok(for_weights, gu.size(0)):
+            h = torch.empty(gu.size(0), inter, dtype=torch.float16, device=gu.device)
+            fac = torch.empty(gu.size(0), dtype=torch.float32, device=gu.device)
+            with torch.cuda.device(gu.device):
+                _lib.check(lib.dst_swiglu_std_norm(gu.data_ptr(), gu.size(0), inter, h.data_ptr(), fac.data_ptr(), kb._stream(gu)))
+            return kb.NormRows(h, fac)
+        h = torch.empty(gu.size(0), inter, dtype=torch.bfloat16, device=gu.device)
+        with torch.cuda.device(gu.device):
+            _lib.check(lib.dst_swiglu_std(gu.data_ptr(), gu.size(0), inter, h.data_ptr(), kb._stream(gu)))
+        return h
+
+    def combine_weighted(self, down: torch.Tensor, order: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, T: int,
+                         top_k: int) -> torch.Tensor:
+        """boilerplate/engine/standard.py:172-175: bf16 products with the bf16 routing weight, bf16 accumulation."""
+        lib = self._lib()
+        hidden = down.size(1)
+        inv = torch.empty(T * top_k, dtype=torch.int64, device=down.device)
+        y = torch.empty(T, hidden, dtype=torch.bfloat16, device=down.device)
+        ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        w = weights.reshape(-1).float().contiguous()
+        with torch.cuda.device(down.device):
+            _lib.check(lib.dst_combine_weighted(down.data_ptr(), order.data_ptr(), ids32.data_ptr(), w.data_ptr(), T, top_k, hidden,
+                                                inv.data_ptr(), y.data_ptr(), kb._stream(down)))
+        return y
+
     def combine(self, down: torch.Tensor, order: torch.Tensor, ids: torch.Tensor, T: int, top_k: int) -> torch.Tensor:
         lib = self._lib()
         hidden = down.size(1)
@@ -155,11 +183,30 @@ class B200Ops:
 
 
 class MoELayer:
-    """Single-device routed-expert layer over ``ExpertWeights``."""
+    """Single-device routed-expert layer over ``ExpertWeights``.
 
-    def __init__(self, weights: ExpertWeights, top_k: int, route_scale: float = 1.0, swiglu_limit: float = 0.0, ops=None):
+    ``flavour="v4"`` follows boilerplate/engine/model.py:372-422 (routing weight before w2, fp32 accumulation over
+    a token's experts); ``flavour="standard"`` follows boilerplate/engine/standard.py:154-176 (OLMoE-style: every
+    intermediate in bf16, weight applied to the expert output, bf16 accumulation, ``norm_topk_prob`` optional).
+    """
+
+    def __init__(self, weights: ExpertWeights, top_k: int, route_scale: float = 1.0, swiglu_limit: float = 0.0, ops=None,
+                 flavour: str = "v4", norm_topk_prob: bool = True):
+        if flavour not in ("v4", "standard"):
+            raise ValueError(f"flavour must be 'v4' or 'standard', got {flavour!r}")
         self.w, self.top_k, self.route_scale, self.swiglu_limit = weights, top_k, route_scale, swiglu_limit
+        self.flavour, self.norm_topk_prob = flavour, norm_topk_prob
         self.ops = ops if ops is not None else B200Ops()
+
+    def _forward_standard(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        w, T = self.w, x.size(0)
+        weights, ids = self.ops.route(logits, self.top_k, 1.0, renorm=self.norm_topk_prob)
+        order, offsets = self.ops.sort(ids, w.n_experts)
+        xs = self.gather_for_experts(x, order, self.top_k)
+        gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
+        h = self.ops.swiglu_std(gu, w.inter, for_weights=w.w2_packed)
+        down = self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
+        return self.ops.combine_weighted(down, order, ids, weights, T, self.top_k)
 
     def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order) -> torch.Tensor:
         """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows."""
@@ -179,6 +226,8 @@ class MoELayer:
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """x [T, hidden] bf16, router logits [T, E] f32 -> y [T, hidden] bf16."""
+        if self.flavour == "standard":
+            return self._forward_standard(x, logits)
         T = x.size(0)
         weights, ids = self.ops.route(logits, self.top_k, self.route_scale)
         order, offsets = self.ops.sort(ids, self.w.n_experts)

@@ -167,6 +167,10 @@ int dst_sort_by_expert(const void* ids, int ids_are_i32, int64_t n, int64_t E, i
  */
 int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
                            float* weights, int32_t* ids, dst_stream_t stream);
+/* The same with the renormalisation optional (renorm = 0: the softmax scores of the selected experts as they are):
+ * the `norm_topk_prob` switch of boilerplate/engine/standard.py:159-165. */
+int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
+                              float* weights, int32_t* ids, dst_stream_t stream);
 
 /*
  * Gather token rows into expert-sorted order: dst[p, :] = src[order[p] / top_k, :] (16-bit elements,
@@ -203,6 +207,19 @@ int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64
  */
 int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
                 int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
+
+/*
+ * The standard (OLMoE-style) MoE flavour, boilerplate/engine/standard.py:149-176, which keeps every intermediate in
+ * bf16: h = bf16( bf16(silu(gate)) * up ) without a routing weight (dst_swiglu_std: bf16 rows;
+ * dst_swiglu_std_norm: the DST_ACT_F16_NORM format), and the combine
+ * y[t] = sum over the token's slots in increasing expert id of bf16( down * bf16(weight) ), every partial sum
+ * rounded to bf16 (index_add_ into a bf16 tensor). `weights` [T * top_k] f32 as the router wrote them.
+ */
+int dst_swiglu_std(const void* gu_bf16, int64_t n_rows, int64_t inter, void* h_bf16, dst_stream_t stream);
+int dst_swiglu_std_norm(const void* gu_bf16, int64_t n_rows, int64_t inter, void* h_f16, float* row_factor,
+                        dst_stream_t stream);
+int dst_combine_weighted(const void* down_bf16, const int64_t* order, const int32_t* ids, const float* weights, int64_t T,
+                         int top_k, int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
 
 /*
  * The grouped GEMM for callers that must not allocate device memory. (This entry has no counterpart

@@ -303,6 +303,36 @@ def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_li
     return bf16_round(y)
 
 
+def moe_layer_standard(x, logits, experts, top_k, hidden, inter, group, fmt, norm_topk_prob=True):
+    """boilerplate/engine/standard.py:154-176 (OLMoE-style layer) with bf16 as the model dtype: softmax over all
+    experts -> top-k -> optional renormalisation -> weights to bf16; per expert in increasing id
+    ``down(silu(gate(x)) * up(x)) * w`` with every intermediate a bf16 tensor; ``index_add_`` into a bf16 output.
+    Returns (y as float32 holding bf16 values, weights [T, k] float32 before the bf16 cast, indices)."""
+    x = _c(x, np.float32)
+    logits = _c(logits, np.float32)
+    z = logits - logits.max(-1, keepdims=True)
+    ez = np.exp(z, dtype=np.float32)
+    scores = (ez / ez.sum(-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    idx = np.argsort(-scores, axis=-1, kind="stable")[:, :top_k]
+    w = np.take_along_axis(scores, idx, -1)
+    if norm_topk_prob:
+        w = (w / w.sum(-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    wb = bf16_round(w)
+    y = np.zeros_like(x, dtype=np.float32)
+    for e in range(len(experts)):
+        tok, slot = np.nonzero(idx == e)
+        if tok.size == 0:
+            continue
+        w1, w2, w3 = experts[e]
+        gate = ternary_linear(x[tok], w1, hidden, group, fmt)
+        up = ternary_linear(x[tok], w3, hidden, group, fmt)
+        h = bf16_round(bf16_round(silu(gate)) * up)
+        d = ternary_linear(h, w2, inter, group, fmt)
+        r = bf16_round(d * wb[tok, slot, None])
+        y[tok] = bf16_round(y[tok] + r)
+    return y, w, idx.astype(np.int64)
+
+
 def moe_layer_f64(x, weights, indices, experts, hidden, inter, group, fmt):
     """The same layer in fp64 with no intermediate rounding (dequantized weights, boilerplate/ternary/ops.py:51-58):
     the yardstick for how much of a layer-level difference is bf16 rounding noise."""

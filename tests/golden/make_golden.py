@@ -10,7 +10,8 @@ Every expectation is produced by reference functions, unmodified, imported from 
 act="bf16", backend="cpp"; quant_act_int8), ``boilerplate.kernels.ternary_cuda`` (ternary_gemm_ref,
 grouped_ternary_gemm, sort_by_expert), the C++ kernel ``boilerplate.kernels.cpu.ext().ternary_gemm``
 and ``boilerplate.engine.model.V4Model`` (route / swiglu / moe, called on a stand-in object that
-carries only the attributes those three methods read).
+carries only the attributes those three methods read) and ``boilerplate.engine.standard.StandardDecoder._moe``
+(the OLMoE-style layer, on a stand-in likewise).
 
 Inputs come from numpy generators with fixed seeds so the tests can rebuild them without the
 reference; the fixtures hold the inputs that are cheap to store and every expected output
@@ -61,6 +62,7 @@ def main():
     sys.path.insert(0, args.reference)
 
     from boilerplate.engine.model import V4Model
+    from boilerplate.engine.standard import StandardDecoder
     from boilerplate.kernels.cpu import ext
     from boilerplate.kernels.ternary_cuda import grouped_ternary_gemm, sort_by_expert, ternary_gemm, ternary_gemm_ref
     from boilerplate.ternary.ops import PackedTerm, TernaryLinear, quant_act_int8
@@ -228,6 +230,51 @@ def main():
         m_out[pre + "route_indices"] = indices.numpy()
         m_out[pre + "y_bits"] = bits(y)
     np.savez_compressed(HERE / "moe_layer.npz", **m_out)
+
+    # ---------------------------------------------------------------- 5b. MoE layer (standard / OLMoE flavour)
+    s_out = {}
+    for ci, (fmt, k_terms, renorm) in enumerate((("tq1", 1, True), ("tq2", 2, False))):
+        T, hidden, inter, E, topk, group = 24, 256, 128, 8, 2, 128
+        rng = np.random.default_rng(5500 + ci)
+        x = acts_of(rng, (T, hidden))
+        gate_w = torch.from_numpy(rng.standard_normal((E, hidden)).astype(np.float32) * 0.2)
+
+        def make_s(Nw, Kw):
+            terms = []
+            for i in range(k_terms):
+                t = trits_of(rng, (Nw, Kw))
+                s = scales_of(rng, (Nw, Kw // group))
+                if i == 1:
+                    s = (s.astype(np.float32) * 0.25).astype(np.float16)
+                terms.append((pack(torch.from_numpy(t), fmt).numpy(), s))
+            return terms
+
+        experts = [(make_s(inter, hidden), make_s(hidden, inter), make_s(inter, hidden)) for _ in range(E)]  # gate, down, up
+
+        def lin_s(terms, Kw):
+            return TernaryLinear([PackedTerm(torch.from_numpy(p), torch.from_numpy(s)) for p, s in terms], Kw, fmt, group,
+                                 act="bf16", backend="cpp")
+
+        built = [(lin_s(w1, hidden), lin_s(w3, hidden), lin_s(w2, inter)) for w1, w2, w3 in experts]  # (gate, up, down)
+        logits = x.float() @ gate_w.T
+        fake = types.SimpleNamespace(hidden=hidden, config={"num_experts_per_tok": topk, "norm_topk_prob": renorm, "num_experts": E},
+                                     expert_cache=types.SimpleNamespace(get=lambda key, factory: built[key[1]], touch=lambda key: None))
+        fake._run_mlp = StandardDecoder._run_mlp
+        layer = types.SimpleNamespace(prefix="l", router=lambda v: logits)
+        routing = []
+        y = StandardDecoder._moe(fake, layer, x, routing)
+        pre = f"{fmt}_"
+        s_out[pre + "meta"] = np.array([T, hidden, inter, E, topk, group, k_terms, int(renorm)], np.int64)
+        s_out[pre + "x_bits"] = bits(x)
+        s_out[pre + "logits"] = logits.numpy()
+        for e, ws in enumerate(experts):
+            for wi, terms in zip(("w1", "w2", "w3"), ws):
+                for i, (p, s) in enumerate(terms):
+                    s_out[pre + f"e{e}_{wi}_packed{i}"] = p
+                    s_out[pre + f"e{e}_{wi}_scale{i}"] = s
+        s_out[pre + "route_indices"] = routing[0].numpy()
+        s_out[pre + "y_bits"] = bits(y)
+    np.savez_compressed(HERE / "moe_layer_standard.npz", **s_out)
 
     # ---------------------------------------------------------------- 6. BASELINE config-0/1 shapes (hash + sample)
     big = {}

@@ -350,6 +350,37 @@ def test_moe_layer_against_reference_golden(golden, fmt):
     check_layer(bf16_numpy(y), want, y64)
 
 
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_moe_layer_standard_flavour_against_reference_golden(golden, fmt):
+    """The OLMoE-style layer of boilerplate/engine/standard.py:154-176 on the GPU against the reference's output."""
+    from deepseekternarized_b200.moe import B200Ops, ExpertWeights, MoELayer
+
+    g = golden("moe_layer_standard")
+    T, hidden, inter, E, topk, group, k_terms, renorm = (int(v) for v in g[f"{fmt}_meta"])
+    x = O.from_bf16_bits(g[f"{fmt}_x_bits"])
+    experts = [tuple([(g[f"{fmt}_e{e}_{wn}_packed{i}"], g[f"{fmt}_e{e}_{wn}_scale{i}"]) for i in range(k_terms)]
+                     for wn in ("w1", "w2", "w3")) for e in range(E)]
+    logits = torch.from_numpy(g[f"{fmt}_logits"]).to(DEV)
+    _, w_ref, idx_ref = O.moe_layer_standard(x, g[f"{fmt}_logits"], experts, topk, hidden, inter, group, fmt, bool(renorm))
+    w, ids = B200Ops().route(logits, topk, 1.0, renorm=bool(renorm))
+    assert np.array_equal(ids.cpu().numpy(), g[f"{fmt}_route_indices"])
+    np.testing.assert_allclose(w.cpu().numpy(), w_ref, rtol=1e-5, atol=1e-7)
+    ew = ExpertWeights(*stack_experts(experts, k_terms, DEV), hidden, inter, group, fmt)
+    y = MoELayer(ew, topk, flavour="standard", norm_topk_prob=bool(renorm))(bf16_tensor(x, DEV), logits)
+    want = O.from_bf16_bits(g[f"{fmt}_y_bits"])
+    check_layer(bf16_numpy(y), want, O.moe_layer_f64(x, w_ref, idx_ref, experts, hidden, inter, group, fmt))
+    # larger case (the tcgen05 kernel and the fused fp16 rows): against the oracle
+    T2, E2 = 700, 4
+    rng = np.random.default_rng(17)
+    experts2 = make_experts(rng, E2, hidden, inter, group, fmt, k_terms)
+    x2 = O.synth_acts(rng, (T2, hidden))
+    lg2 = rng.standard_normal((T2, E2)).astype(np.float32)
+    want2, w2, idx2 = O.moe_layer_standard(x2, lg2, experts2, 2, hidden, inter, group, fmt, bool(renorm))
+    ew2 = ExpertWeights(*stack_experts(experts2, k_terms, DEV), hidden, inter, group, fmt).prepare()
+    y2 = MoELayer(ew2, 2, flavour="standard", norm_topk_prob=bool(renorm))(bf16_tensor(x2, DEV), torch.from_numpy(lg2).to(DEV))
+    check_layer(bf16_numpy(y2), want2, O.moe_layer_f64(x2, w2, idx2, experts2, hidden, inter, group, fmt))
+
+
 @pytest.mark.parametrize("fmt,k_terms", [("tq1", 1), ("tq2", 2)])
 def test_moe_layer_steps_against_oracle(fmt, k_terms):
     """A mid-sized layer (T=300, 16 experts, top-6): every step against the oracle."""

@@ -120,3 +120,20 @@ def test_baseline_shapes_hash(golden):
         y = O.gemm_f32(x, p, s.astype(np.float32), K, 128, fmt)
         assert np.array_equal(y.reshape(-1)[::61], g[f"c{c}_sample"])
         assert hashlib.sha256(y.tobytes()).digest() == g[f"c{c}_sha256"].tobytes()
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_moe_layer_standard_flavour_matches_reference(golden, fmt):
+    """boilerplate/engine/standard.py:154-176 (OLMoE-style: bf16 intermediates, weight after the down projection,
+    bf16 accumulation; norm_topk_prob on for the TQ1 case, off for the TQ2 k = 2 case)."""
+    g = golden("moe_layer_standard")
+    T, hidden, inter, E, topk, group, k_terms, renorm = (int(v) for v in g[f"{fmt}_meta"])
+    x = O.from_bf16_bits(g[f"{fmt}_x_bits"])
+    experts = [tuple([(g[f"{fmt}_e{e}_{wn}_packed{i}"], g[f"{fmt}_e{e}_{wn}_scale{i}"]) for i in range(k_terms)]
+                     for wn in ("w1", "w2", "w3")) for e in range(E)]
+    y, w, idx = O.moe_layer_standard(x, g[f"{fmt}_logits"], experts, topk, hidden, inter, group, fmt, norm_topk_prob=bool(renorm))
+    assert np.array_equal(idx, g[f"{fmt}_route_indices"])
+    want = O.from_bf16_bits(g[f"{fmt}_y_bits"])
+    assert O.rel_fro(y, want) < 2e-3
+    mism = np.mean(O.bf16_bits(y) != g[f"{fmt}_y_bits"])
+    assert mism < 0.02, mism
