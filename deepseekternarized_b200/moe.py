@@ -297,8 +297,11 @@ class ExpertParallelMoE:
         order2, offsets2 = self.ops.sort(local_ids, El)
         xs2 = self.local.gather_for_experts(xr, order2, 1)
         down2 = self.local.experts_forward(xs2, offsets2, wr, order2)
-        back = torch.empty_like(down2)
-        back[order2] = down2  # undo the local sort: row p of down2 is received row order2[p]
+        # undo the local sort (row p of down2 is received row order2[p]) with the row-gather kernel through the
+        # inverse permutation; a scatter through torch's index_put took 0.8 ms for 49 152 rows of 8 KB
+        inv2 = torch.empty_like(order2)
+        inv2[order2] = torch.arange(R, device=x.device, dtype=order2.dtype)
+        back = self.ops.gather(down2, inv2, 1)
 
         down = torch.empty(xs.size(0), back.size(1), dtype=back.dtype, device=x.device)
         dist.all_to_all_single(down, back, send_l, recv_l, group=self.pg)
