@@ -15,7 +15,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_PATH = CSRC / "libdst_b200.so"
-SOURCES = ["api.cu", "format_kernels.cu", "layout_kernels.cu", "gemm_generic.cu", "gemm_decode.cu", "gemm_decode_tq1.cu", "gemm_prefill.cu",
+SOURCES = ["api.cu", "format_kernels.cu", "layout_kernels.cu", "gemm_generic.cu", "gemm_decode.cu", "gemm_decode_tq1.cu", "gemm_prefill.cu", "ep_kernels.cu",
            "moe_kernels.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC"]
@@ -28,6 +28,7 @@ OUT_F32, OUT_BF16, OUT_F16 = 0, 1, 2
 ACT_BF16, ACT_F16, ACT_I8, ACT_F16_NORM = 0, 1, 2, 3
 ALGO_AUTO, ALGO_GENERIC, ALGO_DECODE, ALGO_PREFILL = 0, 1, 2, 3
 MAX_TERMS = 4
+MAX_PEERS = 16
 LAYOUT_CANONICAL, LAYOUT_TILED = 0, 1
 
 
@@ -106,6 +107,12 @@ _SIGNATURES = {
                                   ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
                                    ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_ep_push_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
+    "dst_ep_combine_pull": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
     "dst_check_device_status": (ctypes.c_int, [ctypes.c_void_p]),
 }
 

@@ -1,0 +1,221 @@
+// Expert-parallel dispatch and combine over peer memory (NVLink / NVSwitch, plain P2P loads and stores).
+//
+// Each rank holds the routed experts [rank * El, (rank + 1) * El) and its own tokens. After routing and the
+// stable sort by global expert, every rank knows from an all-gather of the per-expert counts where each of its
+// sorted rows belongs in the destination rank's expert-sorted receive buffer:
+//     row p of expert g  ->  rank g / El, row dst_start[g] + (p - offsets[g])
+// (dst_start[g] = rows of the destination's earlier experts from all ranks + rows of expert g from lower ranks).
+//
+//   ep_push_kernel     gathers the token row of sorted row p, normalises it to the tcgen05 kernel's fp16 row
+//                      format (power of two per row, DST_ACT_F16_NORM) and STORES it, with its row factor and its
+//                      routing weight, straight into the destination GPU's buffers: gather + conversion +
+//                      dispatch in one pass, no staging copy, no re-sort on the receiver.
+//   ep_combine_kernel  per token, LOADS its top_k expert outputs from the GPUs that computed them, in increasing
+//                      expert id, sums in fp32 and writes bf16: inverse dispatch + combine in one pass.
+//
+// The buffers are mapped into every rank (torch symmetric memory); the steps are separated by stream-ordered
+// collectives on the host side, so no kernel here waits on another GPU. No TMA, no multicast.
+#include "dst_common.cuh"
+
+namespace dst {
+namespace {
+
+struct PeerPtrs {
+  void* p[DST_MAX_PEERS];
+};
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& q, float* f) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// index of the expert whose row range [offsets[g], offsets[g + 1]) holds row p (offsets nondecreasing, E + 1 entries)
+__device__ __forceinline__ int expert_of_row(const int64_t* __restrict__ offsets, int E, int64_t p) {
+  int lo = 0, hi = E;  // invariant: offsets[lo] <= p < offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= p) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+template <int J>  // 16-byte chunks per thread: rows of K <= 2048 J elements
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ order, const int64_t* __restrict__ offsets,
+               const float* __restrict__ route_weights, const int64_t* __restrict__ dst_start, int E, int El, int top_k, int64_t K,
+               PeerPtrs rows, PeerPtrs fac, PeerPtrs wts) {
+  __shared__ float red[32];
+  __shared__ int64_t s_dst[2];
+  const int64_t p = blockIdx.x;
+  const int64_t slot = order[p];
+  if (threadIdx.x == 0) {
+    const int g = expert_of_row(offsets, E, p);
+    s_dst[0] = g / El;
+    s_dst[1] = dst_start[g] + (p - offsets[g]);
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(x + (slot / top_k) * K);
+  const int chunks = (int)(K >> 3);
+  float v[J][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) {
+      bf16x8_to_float(s[c], v[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+    }
+  }
+  // block maximum (also publishes s_dst)
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  int ex = 0;
+  if (amax > 0.f && isfinite(amax)) {
+    (void)frexpf(amax, &ex);
+    ex -= 8;  // amax * 2^-ex in [128, 256)
+  }
+  const float down = ldexpf(1.f, -ex);
+  const int d = (int)s_dst[0];
+  const int64_t dr = s_dst[1];
+  uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(rows.p[d]) + dr * K);
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 h = __floats2half2_rn(v[j][2 * i] * down, v[j][2 * i + 1] * down);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      out[c] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (threadIdx.x == 0) {
+    static_cast<float*>(fac.p[d])[dr] = ldexpf(1.f, ex);
+    static_cast<float*>(wts.p[d])[dr] = route_weights[slot];
+  }
+}
+
+__global__ void ep_invert_order_kernel(const int64_t* __restrict__ order, int64_t n, int64_t* __restrict__ inv) {
+  const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (p < n) {
+    const int64_t f = order[p];
+    if (f >= 0 && f < n) inv[f] = p;
+  }
+}
+
+// One block per token: its top_k rows, read from the ranks that own the experts, in increasing expert id.
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, const int64_t* __restrict__ offsets,
+                  const int64_t* __restrict__ dst_start, int El, int top_k, int64_t hidden, __nv_bfloat16* __restrict__ y) {
+  const int64_t t = blockIdx.x;
+  const __nv_bfloat16* src[8];
+  int eid[8];
+  for (int s = 0; s < top_k; ++s) {
+    const int g = ids[t * top_k + s];
+    const int64_t p = inv[t * top_k + s];
+    eid[s] = g;
+    src[s] = static_cast<const __nv_bfloat16*>(down.p[g / El]) + (dst_start[g] + (p - offsets[g])) * hidden;
+  }
+  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
+    const int e = eid[i];
+    const __nv_bfloat16* q = src[i];
+    int j = i - 1;
+    while (j >= 0 && eid[j] > e) {
+      eid[j + 1] = eid[j];
+      src[j + 1] = src[j];
+      --j;
+    }
+    eid[j + 1] = e;
+    src[j + 1] = q;
+  }
+  const int chunks = (int)(hidden >> 3);
+  for (int c = threadIdx.x; c < chunks; c += 256) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < top_k; ++s) {
+      float f[8];
+      bf16x8_to_float(reinterpret_cast<const uint4*>(src[s])[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(y + t * hidden)[c] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+bool fill_peers(PeerPtrs& out, const void* const* ptrs, int world) {
+  for (int i = 0; i < DST_MAX_PEERS; ++i) out.p[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    if (!ptrs[i] || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) != 0) return false;
+    out.p[i] = const_cast<void*>(ptrs[i]);
+  }
+  return true;
+}
+
+}  // namespace
+}  // namespace dst
+
+using namespace dst;
+
+extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
+                                const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
+                                const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
+                                int world, dst_stream_t stream) {
+  if (n_rows < 0 || E <= 0 || experts_per_rank <= 0 || top_k <= 0 || K <= 0 || world < 1 || world > DST_MAX_PEERS) return DST_ERR_BAD_ARG;
+  if (E > DST_MAX_EXPERTS || experts_per_rank * world < E) return DST_ERR_BAD_SHAPE;
+  if (K % 8 != 0 || K > 8192) return DST_ERR_UNSUPPORTED;
+  if (n_rows == 0) return DST_OK;
+  if (!x_bf16 || !order || !offsets || !route_weights || !dst_start || !peer_rows_f16 || !peer_row_factor || !peer_row_weight)
+    return DST_ERR_BAD_ARG;
+  if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
+  PeerPtrs rows, fac, wts;
+  if (!fill_peers(rows, peer_rows_f16, world) || !fill_peers(fac, peer_row_factor, world) || !fill_peers(wts, peer_row_weight, world))
+    return DST_ERR_ALIGNMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto xp = static_cast<const __nv_bfloat16*>(x_bf16);
+  if (K <= 2048)
+    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+  else if (K <= 4096)
+    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+  else
+    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
+                                   const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
+                                   void* y_bf16, int world, dst_stream_t stream) {
+  if (T < 0 || experts_per_rank <= 0 || top_k <= 0 || top_k > 8 || hidden <= 0 || world < 1 || world > DST_MAX_PEERS) return DST_ERR_BAD_ARG;
+  if (hidden % 8 != 0) return DST_ERR_UNSUPPORTED;
+  if (T == 0) return DST_OK;
+  if (!peer_down_bf16 || !order || !ids || !offsets || !dst_start || !inv || !y_bf16) return DST_ERR_BAD_ARG;
+  if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(y_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
+  PeerPtrs down;
+  if (!fill_peers(down, peer_down_bf16, world)) return DST_ERR_ALIGNMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t n = T * top_k;
+  ep_invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
+  DST_CUDA_TRY(cudaGetLastError());
+  ep_combine_kernel<<<(unsigned)T, 256, 0, st>>>(down, inv, ids, offsets, dst_start, (int)experts_per_rank, top_k, hidden,
+                                                static_cast<__nv_bfloat16*>(y_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}

@@ -120,9 +120,9 @@ class B200Ops:
                                            kb._stream(x)))
         return out
 
-    def gemm(self, x, offsets, packed, scales, K, group, fmt) -> torch.Tensor:
+    def gemm(self, x, offsets, packed, scales, K, group, fmt, out=None) -> torch.Tensor:
         return kb.grouped_ternary_gemm_bf16(x, offsets, packed, scales, K, group, fmt, out_dtype=torch.bfloat16,
-                                            algo=self.algo, validate_offsets=False)
+                                            algo=self.algo, out=out, validate_offsets=False)
 
     def swiglu(self, gu: torch.Tensor, row_weights: torch.Tensor | None, order: torch.Tensor | None, inter: int,
                limit: float, for_weights=None):
@@ -208,15 +208,17 @@ class MoELayer:
         down = self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
         return self.ops.combine_weighted(down, order, ids, weights, T, self.top_k)
 
-    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order) -> torch.Tensor:
-        """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows."""
+    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order, out=None) -> torch.Tensor:
+        """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows (into ``out`` if given)."""
         w = self.w
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
         if getattr(self.ops, "fused_norm", False):
             h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit, for_weights=w.w2_packed)
         else:
             h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit)
-        return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
+        if out is None:
+            return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
+        return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt, out=out)
 
     def gather_for_experts(self, x: torch.Tensor, order: torch.Tensor, top_k: int):
         """Rows in expert-sorted order, in the format the first expert GEMM reads fastest."""
@@ -244,6 +246,42 @@ def expert_owner_split(n_experts: int, world: int) -> int:
     return n_experts // world
 
 
+def ep_placement(counts_all: torch.Tensor, rank: int, experts_per_rank: int):
+    """Where this rank's routed rows go. ``counts_all`` [W, E]: rows per global expert of every source rank.
+
+    The owner of expert g (rank g // experts_per_rank) keeps its received rows sorted by local expert, and inside
+    an expert by source rank. Returns ``dst_start`` [E] (first row, in the owner's buffer, of THIS rank's rows of
+    each expert) and ``offsets_local`` [experts_per_rank + 1] (the row offsets of this rank's own experts, the
+    grouped GEMM's ``offsets``)."""
+    W, E = counts_all.shape
+    tot = counts_all.sum(0).view(W, experts_per_rank)  # rows per expert from all sources, by owner
+    incl = tot.cumsum(1)
+    base = (incl - tot).reshape(E)  # rows of the owner's earlier experts
+    before = counts_all[:rank].sum(0) if rank > 0 else torch.zeros_like(base)  # rows of the same expert from lower ranks
+    offsets_local = torch.cat([incl.new_zeros(1), incl[rank]])
+    return (base + before).contiguous(), offsets_local.contiguous()
+
+
+class _PeerBuffers:
+    """Symmetric-memory buffers of one step parity: receive rows / factors / weights and the expert outputs."""
+
+    def __init__(self, cap: int, hidden: int, device, group):
+        import torch.distributed._symmetric_memory as symm
+
+        self.cap = cap
+        self.rows = symm.empty((cap, hidden), dtype=torch.float16, device=device)
+        self.fac = symm.empty((cap,), dtype=torch.float32, device=device)
+        self.wts = symm.empty((cap,), dtype=torch.float32, device=device)
+        self.down = symm.empty((cap, hidden), dtype=torch.bfloat16, device=device)
+        world = group.size()
+        self.ptrs = {}
+        for name in ("rows", "fac", "wts", "down"):
+            t = getattr(self, name)
+            hdl = symm.rendezvous(t, group)
+            arr = (ctypes.c_void_p * world)(*[hdl.get_buffer(r, tuple(t.shape), t.dtype).data_ptr() for r in range(world)])
+            self.ptrs[name] = arr
+
+
 class ExpertParallelMoE:
     """Expert-parallel layer: this rank holds experts [rank * E/W, (rank + 1) * E/W) and its own tokens.
 
@@ -253,7 +291,10 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights: ExpertWeights, n_experts_total: int, top_k: int, group=None, route_scale: float = 1.0,
-                 swiglu_limit: float = 0.0, ops=None):
+                 swiglu_limit: float = 0.0, ops=None, transport: str = "auto"):
+        """``transport``: "nccl" = all_to_all_single of rows both ways (any backend, also gloo on CPU);
+        "peer" = the rows are written into / read from the owners' buffers by this library's kernels over NVLink
+        (CUDA, one node, torch symmetric memory, B200Ops); "auto" = "peer" where it can be set up, else "nccl"."""
         import torch.distributed as dist
 
         self.dist = dist
@@ -268,8 +309,83 @@ class ExpertParallelMoE:
         self.ops = self.local.ops
         self.top_k = top_k
         self.last_dispatch_rows = 0
+        if transport not in ("auto", "nccl", "peer"):
+            raise ValueError("transport must be 'auto', 'nccl' or 'peer'")
+        self.transport = transport
+        self._peer = None  # [_PeerBuffers, _PeerBuffers] once set up
+        self._step = 0
+
+    # ------------------------------------------------------------------ peer-memory transport
+    def _peer_setup(self, x: torch.Tensor) -> bool:
+        """Collective: every rank decides the same way (an all-reduced flag) whether the peer transport is usable."""
+        if self._peer is not None:
+            return True
+        if self._peer is False or self.transport == "nccl":
+            return False
+        ok = (x.is_cuda and isinstance(self.ops, B200Ops) and self.ops.fused_norm and self.world <= _lib.MAX_PEERS
+              and x.size(1) % 8 == 0 and x.size(1) <= 8192 and self.dist.get_backend(self.pg) == "nccl")
+        bufs = None
+        if ok:
+            try:
+                cap = int(x.size(0)) * self.top_k * self.world  # every routed row of the step could land on one rank
+                capt = torch.tensor([cap], device=x.device, dtype=torch.int64)
+                self.dist.all_reduce(capt, op=self.dist.ReduceOp.MAX, group=self.pg)
+                pg = self.pg if self.pg is not None else self.dist.group.WORLD
+                bufs = [_PeerBuffers(int(capt.item()), x.size(1), x.device, pg) for _ in range(2)]
+            except Exception as exc:  # symmetric memory not available on this system
+                if self.transport == "peer":
+                    raise RuntimeError(f"peer transport unavailable: {exc}") from exc
+                ok = False
+        flag = torch.tensor([1 if ok else 0], device=x.device if x.is_cuda else "cpu", dtype=torch.int32)
+        self.dist.all_reduce(flag, op=self.dist.ReduceOp.MIN, group=self.pg)
+        if int(flag.item()) == 1:
+            self._peer = bufs
+            self._sync = torch.zeros(1, device=x.device, dtype=torch.int32)
+            return True
+        if self.transport == "peer":
+            raise RuntimeError("peer transport unavailable on some rank")
+        self._peer = False
+        return False
+
+    def _forward_peer(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        dist, W, El = self.dist, self.world, self.El
+        lib = B200Ops._lib()
+        T, hidden = x.size(0), x.size(1)
+        if T * self.top_k * W > self._peer[0].cap:
+            raise RuntimeError("more tokens per step than the peer buffers were sized for")
+        buf = self._peer[self._step & 1]  # two sets: a peer may still read last step's outputs while this step pushes
+        self._step += 1
+        weights, ids = self.ops.route(logits, self.top_k, self.local.route_scale)
+        order, offsets = self.ops.sort(ids, self.E)
+        counts = offsets.diff().to(torch.int64).contiguous()
+        counts_all = torch.empty(W, self.E, dtype=torch.int64, device=x.device)
+        dist.all_gather_into_tensor(counts_all, counts, group=self.pg)
+        dst_start, offsets2 = ep_placement(counts_all, self.rank, El)
+        R = int(offsets2[-1].item())  # the one host sync of the step
+        self.last_dispatch_rows = R
+        x = x.contiguous()
+        wflat = weights.reshape(-1).contiguous()
+        with torch.cuda.device(x.device):
+            _lib.check(lib.dst_ep_push_rows(x.data_ptr(), order.data_ptr(), offsets.data_ptr(), wflat.data_ptr(), dst_start.data_ptr(),
+                                            order.numel(), self.E, El, self.top_k, hidden, buf.ptrs["rows"], buf.ptrs["fac"],
+                                            buf.ptrs["wts"], W, kb._stream(x)))
+        dist.all_reduce(self._sync, group=self.pg)  # every rank's rows have landed
+        if R > 0:
+            xs2 = kb.NormRows(buf.rows[:R], buf.fac[:R])
+            self.local.experts_forward(xs2, offsets2, buf.wts[:R], None, out=buf.down[:R])
+        dist.all_reduce(self._sync, group=self.pg)  # every rank's expert outputs are written
+        inv = torch.empty(T * self.top_k, dtype=torch.int64, device=x.device)
+        y = torch.empty(T, hidden, dtype=torch.bfloat16, device=x.device)
+        ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        with torch.cuda.device(x.device):
+            _lib.check(lib.dst_ep_combine_pull(buf.ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(),
+                                               dst_start.data_ptr(), T, El, self.top_k, hidden, inv.data_ptr(), y.data_ptr(), W,
+                                               kb._stream(x)))
+        return y
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        if x.dtype == torch.bfloat16 and self._peer_setup(x):
+            return self._forward_peer(x, logits)
         dist, W, El = self.dist, self.world, self.El
         T = x.size(0)
         weights, ids = self.ops.route(logits, self.top_k, self.local.route_scale)

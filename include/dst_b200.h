@@ -60,6 +60,7 @@ enum { DST_ALGO_AUTO = 0, DST_ALGO_GENERIC = 1, DST_ALGO_DECODE = 2, DST_ALGO_PR
 enum { DST_LAYOUT_CANONICAL = 0, DST_LAYOUT_TILED = 1 };
 
 #define DST_MAX_TERMS 4
+#define DST_MAX_PEERS 16 /* ranks of one node whose buffers a kernel can address (expert-parallel entries) */
 #define DST_MAX_EXPERTS 65535 /* the reference's bound, ternary_cuda_kernel.cu:128 */
 
 int dst_abi_version(void);
@@ -220,6 +221,27 @@ int dst_swiglu_std_norm(const void* gu_bf16, int64_t n_rows, int64_t inter, void
                         dst_stream_t stream);
 int dst_combine_weighted(const void* down_bf16, const int64_t* order, const int32_t* ids, const float* weights, int64_t T,
                          int top_k, int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
+
+/*
+ * Expert-parallel dispatch and combine over peer memory (the reference has no expert-parallel exchange of routed
+ * rows: its EP form replicates tokens and all-reduces, third_party/deepseek_v41_inference/model.py:897-905; these
+ * two entries serve the sharding of the same file, :869-872, expert e on rank e / experts_per_rank).
+ * The peer_* arrays hold, per rank of the node, the address AS MAPPED IN THIS PROCESS of that rank's buffer
+ * (e.g. torch symmetric memory): receive rows [cap, K] f16, row factors [cap] f32, routing weights [cap] f32,
+ * expert outputs [cap, hidden] bf16. `offsets` [E + 1] is this rank's routing-sort offsets over the GLOBAL experts,
+ * dst_start [E] the first row, in the owning rank's receive buffer, of this rank's rows of each expert.
+ * dst_ep_push_rows: for every sorted row p, the token row order[p] / top_k as fp16 scaled by a power of two
+ * (DST_ACT_F16_NORM) -> the owner's buffers (rows, factor, routing weight route_weights[order[p]]).
+ * dst_ep_combine_pull: y[t] = bf16( sum over the token's slots, in increasing expert id, of the owner's output row ).
+ * Neither waits on another GPU; the caller orders the steps (a stream-ordered collective between them).
+ */
+int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
+                     const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
+                     const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
+                     int world, dst_stream_t stream);
+int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
+                        const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
+                        void* y_bf16, int world, dst_stream_t stream);
 
 /*
  * The grouped GEMM for callers that must not allocate device memory. (This entry has no counterpart

@@ -6,6 +6,8 @@ quantisation; for GEMM outputs the north-star tolerance (relative Frobenius erro
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -420,3 +422,17 @@ def test_sort_large_and_bad_ids(kb):
     assert np.array_equal(order.cpu().numpy(), o_ref)
     order, offsets = kb.sort_by_expert(torch.zeros(0, dtype=torch.int64, device=DEV), 4)
     assert order.numel() == 0 and offsets.cpu().tolist() == [0] * 5
+
+
+def test_expert_parallel_peer_transport_single_rank():
+    """The peer-memory dispatch / combine kernels and the placement arithmetic in a one-rank job (every routed row is
+    local): bit-identical to the single-device layer, also through the all-to-all transport. Runs in a child
+    process because it initialises torch.distributed; several ranks are run by hand (see tests/ep_peer_check.py)."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29541", RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+    res = subprocess.run([sys.executable, str(Path(__file__).with_name("ep_peer_check.py"))], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "EP_PEER_CHECK PASS" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

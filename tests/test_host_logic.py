@@ -76,3 +76,34 @@ def test_ternary_linear_has_no_cpu_or_foreign_backend():
     assert lin.out_features == 4
     with pytest.raises(RuntimeError, match="unavailable"):
         lin(torch.zeros(3, 64, dtype=torch.bfloat16))
+
+
+def test_ep_placement_matches_brute_force():
+    """Peer-memory expert parallelism: every (source rank, expert, row) gets a distinct row of the owner's buffer,
+    sorted by local expert and, inside an expert, by source rank; the owner's offsets are the expert totals."""
+    import numpy as np
+    import torch
+
+    from deepseekternarized_b200.moe import ep_placement
+
+    rng = np.random.default_rng(0)
+    W, El = 3, 4
+    E = W * El
+    counts = rng.integers(0, 5, (W, E))
+    counts[:, 5] = 0  # an expert nobody routes to
+    c = torch.from_numpy(counts)
+    # brute force: the owner lists its rows as (local expert, source rank, index)
+    want_start = np.zeros((W, E), np.int64)
+    want_offsets = np.zeros((W, El + 1), np.int64)
+    for d in range(W):
+        pos = 0
+        for e in range(El):
+            want_offsets[d, e] = pos
+            for s_rank in range(W):
+                want_start[s_rank, d * El + e] = pos
+                pos += counts[s_rank, d * El + e]
+        want_offsets[d, El] = pos
+    for r in range(W):
+        dst_start, offsets_local = ep_placement(c, r, El)
+        assert np.array_equal(dst_start.numpy(), want_start[r])
+        assert np.array_equal(offsets_local.numpy(), want_offsets[r])
