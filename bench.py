@@ -236,7 +236,7 @@ def workload_config(n_gpus: int) -> dict:
     return {"workload": "BASELINE config 4: expert-parallel MoE routed-expert layer" if full else
             "REDUCED case of BASELINE config 4 (fewer tokens/experts, same shapes): for profiler captures only", "tokens_per_step": TOKENS, "hidden": HIDDEN,
             "inter": INTER, "experts": N_EXPERTS, "top_k": TOP_K, "format": FMT, "group": GROUP, "scale_dtype": "fp16",
-            "parallelism": f"ep{n_gpus}", "l2": "weights (2.09 GB) and activations exceed the 126 MB L2; no flush needed"}
+            "parallelism": f"ep{n_gpus}" + (" (dispatch and combine by this library's kernels over peer memory)" if n_gpus > 1 else ""), "l2": "weights (2.09 GB) and activations exceed the 126 MB L2; no flush needed"}
 
 
 # --------------------------------------------------------------------------------------------- single-kernel numbers
@@ -307,46 +307,51 @@ def gemm_microbench(device, peaks, which="all") -> dict:
 
 
 # --------------------------------------------------------------------------------------------- main arm
-class TimedOps:
+def timed_ops(algo):
     """B200Ops plus CUDA events around every grouped GEMM launch and a count of launched kernels."""
+    from deepseekternarized_b200.moe import B200Ops
 
-    def __init__(self, base):
-        self.base, self.events, self.launches, self.flops = base, [], 0, 0.0
-        self.timing = False
+    class _Timed(B200Ops):
+        def __init__(self, algo_):
+            super().__init__(algo_)
+            self.events, self.launches, self.flops, self.timing = [], 0, 0.0, False
 
-    def route(self, *a):
-        self.launches += 1
-        return self.base.route(*a)
+        def count(self, n):  # kernels launched by the layer itself (peer-memory dispatch / combine)
+            self.launches += n
 
-    def sort(self, *a):
-        self.launches += 3
-        return self.base.sort(*a)
+        def route(self, *a, **k):
+            self.launches += 1
+            return super().route(*a, **k)
 
-    fused_norm = True
+        def sort(self, *a):
+            self.launches += 3
+            return super().sort(*a)
 
-    def gather(self, *a, **k):
-        self.launches += 1
-        return self.base.gather(*a, **k)
+        def gather(self, *a, **k):
+            self.launches += 1
+            return super().gather(*a, **k)
 
-    def swiglu(self, *a, **k):
-        self.launches += 1
-        return self.base.swiglu(*a, **k)
+        def swiglu(self, *a, **k):
+            self.launches += 1
+            return super().swiglu(*a, **k)
 
-    def combine(self, *a):
-        self.launches += 2
-        return self.base.combine(*a)
+        def combine(self, *a):
+            self.launches += 2
+            return super().combine(*a)
 
-    def gemm(self, x, offsets, packed, scales, K, group, fmt):
-        self.launches += 1
-        if not self.timing:
-            return self.base.gemm(x, offsets, packed, scales, K, group, fmt)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        y = self.base.gemm(x, offsets, packed, scales, K, group, fmt)
-        b.record()
-        self.events.append((a, b))
-        self.flops += 2.0 * x.size(0) * packed[0].size(1) * K
-        return y
+        def gemm(self, x, offsets, packed, scales, K, group, fmt, out=None):
+            self.launches += 1
+            if not self.timing:
+                return super().gemm(x, offsets, packed, scales, K, group, fmt, out=out)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            y = super().gemm(x, offsets, packed, scales, K, group, fmt, out=out)
+            b.record()
+            self.events.append((a, b))
+            self.flops += 2.0 * x.size(0) * packed[0].size(1) * K
+            return y
+
+    return _Timed(algo)
 
 
 def main():
@@ -395,7 +400,7 @@ def main():
     n_local = N_EXPERTS // world
     t_local = TOKENS // world
     weights = synth_expert_weights(n_local, rank * n_local, device)
-    ops = TimedOps(B200Ops(algo=args.algo))
+    ops = timed_ops(args.algo)
     layer = ExpertParallelMoE(weights, N_EXPERTS, TOP_K, ops=ops) if world > 1 else MoELayer(weights, TOP_K, ops=ops)
     x_host, logits_host = synth_tokens(t_local, rank * t_local)
     x_dev, logits_dev = x_host.to(device), logits_host.to(device)

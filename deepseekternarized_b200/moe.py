@@ -318,10 +318,10 @@ class ExpertParallelMoE:
     # ------------------------------------------------------------------ peer-memory transport
     def _peer_setup(self, x: torch.Tensor) -> bool:
         """Collective: every rank decides the same way (an all-reduced flag) whether the peer transport is usable."""
-        if self._peer is not None:
-            return True
         if self._peer is False or self.transport == "nccl":
             return False
+        if self._peer is not None:
+            return True
         ok = (x.is_cuda and isinstance(self.ops, B200Ops) and self.ops.fused_norm and self.world <= _lib.MAX_PEERS
               and x.size(1) % 8 == 0 and x.size(1) <= 8192 and self.dist.get_backend(self.pg) == "nccl")
         bufs = None
@@ -369,6 +369,7 @@ class ExpertParallelMoE:
             _lib.check(lib.dst_ep_push_rows(x.data_ptr(), order.data_ptr(), offsets.data_ptr(), wflat.data_ptr(), dst_start.data_ptr(),
                                             order.numel(), self.E, El, self.top_k, hidden, buf.ptrs["rows"], buf.ptrs["fac"],
                                             buf.ptrs["wts"], W, kb._stream(x)))
+        getattr(self.ops, "count", lambda n: None)(3)  # kernels launched here rather than through ops (push, invert, combine)
         dist.all_reduce(self._sync, group=self.pg)  # every rank's rows have landed
         if R > 0:
             xs2 = kb.NormRows(buf.rows[:R], buf.fac[:R])
