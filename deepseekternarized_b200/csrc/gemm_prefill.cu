@@ -150,18 +150,23 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
          ((uint64_t)2 << 61);
 }
 
-// A operand from tensor memory (lane = row, 32-bit column = 2 K elements), B from shared memory
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+// tcgen05.mma: A operand from tensor memory (lane = row, 32-bit column = 2 K elements), B from shared memory.
+// Executed by a whole (converged) warp: one elected lane issues. The issuing warps run their loops with
+// all 32 lanes so that addresses and descriptors are warp-uniform values (a single-lane branch keeps them in
+// per-thread registers and every MMA then pays for moving them to the uniform registers the instruction reads).
+__device__ __forceinline__ void umma_f16_ts_elect(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p, e;\nsetp.ne.b32 p, %4, 0;\nelect.sync _|e, 0xffffffff;\n"
+               "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+  asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n"
+               "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(bar) : "memory");
 }
 // 8 consecutive 32-bit columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint32_t* v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -306,7 +311,7 @@ __device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem
                                         uint32_t d_tile) {
   const int lane = r & 31;
   const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
-  if (!mbar_wait<true>(tfull_bar, d_tile & 1u, abort_flag)) return false;
+  if (!mbar_wait(tfull_bar, d_tile & 1u, abort_flag)) return false;
   // Lanes leave the polling loop (and its per-thread sleeps) one by one; the .sync.aligned tcgen05 instructions
   // below must be executed by the whole warp together.
   __syncwarp();
@@ -495,7 +500,8 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     // instructions instead of eight; a single thread could not issue them as fast as the tensor pipe runs them.
     // Tiles whose row count (padded to 16) is not a multiple of 32, or below 64, are issued by the first thread
     // alone; the second then only adds its arrivals to the barriers.
-    if (lane == 0) {
+    {
+      // all 32 lanes run this loop (see umma_f16_ts_elect); the elected lane issues the MMAs and the commits
       const uint32_t who = warp == 1 ? 0u : 1u;
       uint32_t s = 0, ph = 0, tile = 0;
       bool ok = true;
@@ -505,7 +511,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
       for (int t = (int)blockIdx.x; ok && t < n_tiles; t += t_step) {
         tile_seek(p, offs, tpre, t, e, nt, row0, rows);
         // one accumulator: the previous tile must have been drained
-        if (!RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag))) break;
+        if (!__all_sync(0xffffffffu, RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag)))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t n_eff = (uint32_t)tile_neff(rows);
         const bool split = n_eff >= 64u && (n_eff & 31u) == 0u;  // tiles above 256 rows are padded to 32: always split
@@ -513,11 +519,11 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         const bool active = split || who == 0u;
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
         const uint32_t idesc = (1u << 4) | ((h >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t mine = split ? who * h : 0u;              // first token row (= accumulator column) of this thread's MMAs
+        const uint32_t mine = split ? who * h : 0u;              // first token row (= accumulator column) of this warp's MMAs
         const uint32_t d_tmem = tmem + mine;
         const uint32_t b_off = (mine * 128u) >> 4;               // descriptor start-address units
         for (int ks = 0; ks < p.kstages; ++ks) {
-          if (!RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (active) {
             const uint32_t a_tmem = tmem + PF_TN_MAX + s * PF_A_COLS;  // this stage's slot of the A ring
@@ -527,19 +533,19 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
             for (int kk = 0; kk < 4; ++kk) {
               uint64_t db;
               asm volatile("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(b_lo + kk * 2), "r"(b_desc_hi));
-              umma_f16_ts(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+              umma_f16_ts_elect(d_tmem, a_tmem + kk * 8, db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
             }
           }
-          umma_commit(smem_u32(&bar_empty[s]));  // this thread's MMAs (if any) have read the stage
+          umma_commit_elect(smem_u32(&bar_empty[s]));  // this warp's MMAs (if any) have read the stage
           if (++s == NB) { s = 0; ph ^= 1u; }
 #ifdef DST_ROLE_TIMERS
           ++n_it;
 #endif
         }
-        if (ok) umma_commit(smem_u32(&bar_tfull[0]));
+        if (ok) umma_commit_elect(smem_u32(&bar_tfull[0]));
         ++tile;
       }
-      if (who == 0u) {
+      if (who == 0u && lane == 0) {
         RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, n_it); RT_ADD(12, 1); RT_ADD(13, tile);
       }
     }
@@ -569,7 +575,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     uint32_t s = grp % NB, ph = (grp / NB) & 1u;
     uint32_t it0 = 0, gs0 = 0;  // first stage / first slab of the current tile
     bool ok = true;
-    RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, n_it = 0, t_begin = RT_NOW());
+    RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, w_st = 0, w_pre = 0, n_it = 0, t_begin = RT_NOW());
 
     // scales of the row: 8 groups (16 stages) per 128-bit load, the block of the group's next stage fetched one stage ahead
     uint4 sc[TERMS], scn[TERMS];
@@ -612,6 +618,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         continue;
       }
       const int ks = (int)(own - it0);
+        RT_DECL(t_pre = RT_NOW());
         const int sb = ks / SPB, sbk = ks - sb * SPB;
         const uint32_t gs = gs0 + (uint32_t)sb;
         const uint32_t slot = p.nslab == 2 ? (gs & 1u) : gs % 3u, sround = p.nslab == 2 ? (gs >> 1) : gs / 3u;
@@ -650,6 +657,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
 
         // packed words of this row for this stage, then the slab can go back to the producer
+        RT_SPAN(w_pre, t_pre);
         if (!RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), sround & 1u, abort_flag))) { ok = false; break; }
         uint32_t w[TERMS][4];
 #pragma unroll
@@ -699,10 +707,13 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         ++n_it;
 #endif
         // the A slot must be free (the MMAs that last read it are done) before the store into it
-        if (!RT_WAIT(w_dempty, mbar_wait<true>(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
+        // no sleep between polls here: these warps are the critical path, and a sleeping lane wakes up to a
+        // microsecond late (the whole warp then waits for it at the next convergence point)
+        if (!RT_WAIT(w_dempty, mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
         __syncwarp();  // re-converge after the polling loop: tcgen05.st is .sync.aligned
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem + lane_base + PF_TN_MAX + s * PF_A_COLS;
+        RT_DECL(t_st = RT_NOW());
         tmem_st_8(taddr, v);
         tmem_st_8(taddr + 8, v + 8);
         tmem_st_8(taddr + 16, v + 16);
@@ -711,13 +722,14 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+        RT_SPAN(w_st, t_st);
         own += PF_GROUPS;
         s += PF_GROUPS;
         while (s >= NB) { s -= NB; ph ^= 1u; }
     }
     if (warp == PF_DQ_WARP0 && lane == 0) {
       RT_ADD(24, RT_NOW() - t_begin); RT_ADD(25, w_pfull); RT_ADD(26, w_dempty); RT_ADD(27, n_it); RT_ADD(28, 1);
-      RT_ADD(29, w_drain); RT_ADD(30, w_comp);
+      RT_ADD(29, w_drain); RT_ADD(30, w_comp); RT_ADD(31, w_st); RT_ADD(32, w_pre);
     }
   }
 
@@ -916,7 +928,8 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
 // Profiling builds only: copies (and optionally clears) the 64 role-timer slots. Slots: 0-5 producers (B producer
 // total cycles, slab producer wait slot free, B producer wait stage free, stages, threads, slab producer total),
 // 8-13 MMA issuer (total, wait accumulator free, wait stage full, stages, threads, tiles), 24-30 one dequant warp
-// (total, wait packed slab, wait stage free, own stages, threads, accumulator drain, dequant arithmetic).
+// (total, wait packed slab, wait stage free, own stages, threads, accumulator drain, dequant arithmetic, TMEM store +
+// arrive, scale bookkeeping before the slab wait).
 extern "C" int dst_role_timers(unsigned long long* out, int reset) {
   DST_CUDA_TRY(cudaDeviceSynchronize());
   DST_CUDA_TRY(cudaMemcpyFromSymbol(out, dst::g_role_timers, sizeof(unsigned long long) * 64));
