@@ -59,7 +59,7 @@ constexpr int PF_DQ_WARP0 = PF_CTRL_WARPS + PF_EPI_WARPS;
 constexpr int PF_THREADS = 32 * (PF_DQ_WARP0 + PF_DQ_WARPS);
 constexpr int PF_TN_MAX = 320;               // token rows per tile at most = accumulator columns in TMEM
 constexpr int PF_A_COLS = 32;                // TMEM columns of one A stage: 64 fp16 per weight row
-constexpr int PF_MAX_STAGES = 6;             // 320 + 6 * 32 = 512 TMEM columns
+constexpr int PF_MAX_STAGES = 12;            // stage ring depth at most; tn_max + depth * 32 <= 512 TMEM columns
 constexpr int PF_MAX_SLABS = 3;
 constexpr int PF_LUT_BYTES = 256 * 16 * 4;   // TQ1: 256 byte values x 16 bank replicas x 4 B
 constexpr int PF_SLAB = 8192;                // one (row tile, superblock) slab of packed weights
@@ -102,7 +102,8 @@ struct PrefillParams {
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S, kstages;
   // chosen by the host from the shared-memory budget
-  int tn_max;       // token rows per tile at most (a multiple of 32, <= PF_TN_MAX)
+  int tn_max;       // token rows per tile at most (a multiple of 32, <= PF_TN_MAX): accumulator columns 0 .. tn_max - 1, the A ring after them
+  int rows_hint;    // most rows an expert is expected to have (host knowledge or twice the mean), sizes tn_max
   int nb;           // depth of the stage ring (B stage in shared memory + A slot in TMEM), 2..6
   int nslab;        // slots of the packed-slab ring, 2 or 3
 };
@@ -526,7 +527,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
           if (!__all_sync(0xffffffffu, RT_WAIT(w_full, mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (active) {
-            const uint32_t a_tmem = tmem + PF_TN_MAX + s * PF_A_COLS;  // this stage's slot of the A ring
+            const uint32_t a_tmem = tmem + (uint32_t)p.tn_max + s * PF_A_COLS;  // this stage's slot of the A ring
             // only the start-address field of the B descriptor changes with the stage, the K step and the half
             const uint32_t b_lo = b_desc_lo + s * (stage_bytes >> 4) + b_off;
 #pragma unroll
@@ -712,7 +713,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         if (!RT_WAIT(w_dempty, mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag))) { ok = false; break; }
         __syncwarp();  // re-converge after the polling loop: tcgen05.st is .sync.aligned
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmem + lane_base + PF_TN_MAX + s * PF_A_COLS;
+        const uint32_t taddr = tmem + lane_base + (uint32_t)p.tn_max + s * PF_A_COLS;
         RT_DECL(t_st = RT_NOW());
         tmem_st_8(taddr, v);
         tmem_st_8(taddr + 8, v + 8);
@@ -797,15 +798,21 @@ EncodeFn encode_fn() {
 
 template <int FMT, int TERMS>
 int launch_fmt(const TmaMaps& maps, PrefillParams p, cudaStream_t st) {
-  // Shared-memory plan: the largest token tile (up to 320 rows) that still leaves a stage ring of depth 4, then
-  // a third packed-slab slot if there is room for it.
+  // Shared-memory and TMEM plan: the token tile is as large as the experts are expected to need (up to 320 rows) as
+  // long as a stage ring of depth 4 fits; smaller tiles leave room for a deeper ring (each B stage is tn_max * 128
+  // bytes, each A slot 32 TMEM columns next to tn_max accumulator columns), which is what hides the TMA latency
+  // when the MMAs of a stage are short. Then a third packed-slab slot if there is room for it.
   const long long budget = PF_SMEM_MAX - PF_SMEM_STATIC;
   const long long fixed = 1024 + (FMT == 1 ? PF_LUT_BYTES : 0) + 2 * (PF_MAX_E + 1) * 4;
   const long long slab2 = 2LL * p.n_terms * PF_SLAB;
+  int tn_cap = (p.rows_hint + 31) / 32 * 32;
+  tn_cap = tn_cap < 64 ? 64 : (tn_cap > PF_TN_MAX ? PF_TN_MAX : tn_cap);
   p.tn_max = 0;
-  for (int tn = PF_TN_MAX; tn >= 64; tn -= 32) {
-    const long long nb = (budget - fixed - slab2) / (tn * 128LL);
+  for (int tn = tn_cap; tn >= 64; tn -= 32) {
+    long long nb = (budget - fixed - slab2) / (tn * 128LL);
     if (nb >= 4 || tn == 64) {
+      const long long tmem_fit = (512 - tn) / PF_A_COLS;
+      nb = nb > tmem_fit ? tmem_fit : nb;
       p.tn_max = tn;
       p.nb = (int)(nb > PF_MAX_STAGES ? PF_MAX_STAGES : nb);
       break;
@@ -902,6 +909,9 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.NT = (int)cdiv64(a.N, 128);
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.kstages = (int)(a.K / 64);
+  // rows per expert: known when the caller passed host offsets, else assumed below twice the mean
+  p.rows_hint = (int)(a.max_rows >= 0 ? a.max_rows : 2 * cdiv64(a.T, a.E));
+  if (p.rows_hint < 1) p.rows_hint = 1;
 #define DST_PF_LAUNCH(FMT_)                                                            \
   (a.terms.n == 1 ? launch_fmt<FMT_, 1>(maps, p, stream)                               \
                   : a.terms.n == 2 ? launch_fmt<FMT_, 2>(maps, p, stream) : launch_fmt<FMT_, 4>(maps, p, stream))
