@@ -222,13 +222,13 @@ def run_reference_arm(args):
 
 def traffic_per_launch(n_gpus: int):
     """DRAM bytes per grouped-GEMM launch (mean of the gate+up and the down launch): dram__bytes_read.sum +
-    dram__bytes_write.sum of one ncu capture on the reduced case (96 experts x 4096 tokens: 737 MB and 462 MB,
+    dram__bytes_write.sum of one ncu capture on the reduced case (96 experts x 4096 tokens: 733 MB and 457 MB,
     profiles/prefill_kernel_tq1_moe_reduced_case.md), scaled by the experts and rows one launch processes (traffic is
     proportional to both). None for workloads the capture does not describe."""
     if FMT != "tq1" or TOKENS * 96 != 4096 * N_EXPERTS:
         return None
     scale = (N_EXPERTS / 96.0) / n_gpus
-    return 0.5 * (737.4e6 + 462.0e6) * scale
+    return 0.5 * (733.4e6 + 457.1e6) * scale
 
 
 def workload_config(n_gpus: int) -> dict:

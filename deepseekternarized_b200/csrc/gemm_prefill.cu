@@ -846,7 +846,7 @@ size_t prefill_workspace_bytes(int act_dtype, int64_t T, int64_t K) {
 bool prefill_supports(const GemmArgs& a) {
   return a.weight_layout == DST_LAYOUT_TILED && a.group == 128 && a.K % 128 == 0 && a.scale_dtype == DST_SCALE_F16 &&
          ((a.act_dtype == DST_ACT_F16_NORM && a.row_scale != nullptr) ||
-          ((a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) && a.workspace != nullptr &&
+          ((a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16 || a.act_dtype == DST_ACT_I8) && a.workspace != nullptr &&
            a.workspace_bytes >= prefill_workspace_bytes(a.act_dtype, a.T, a.K))) &&
          a.T < (int64_t(1) << 30) &&
          a.N <= (int64_t(1) << 22) && encode_fn() != nullptr;
@@ -872,6 +872,12 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   } else if (a.act_dtype == DST_ACT_BF16)
     convert_rows_kernel<__nv_bfloat16><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.x), a.K, a.row_scale,
                                                                           static_cast<__half*>(a.workspace), const_cast<float*>(rs));
+  else if (a.act_dtype == DST_ACT_I8)
+    // the int8-activation contract (per-token absmax quantisation, row_scale = the token's scale): int8 values are
+    // exact in fp16, scale * trit is exact in fp16, every product is exact in fp32; only the fp32 accumulation
+    // order differs from the reference's integer group sums (relative difference ~1e-6)
+    convert_rows_kernel<int8_t><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const int8_t*>(a.x), a.K, a.row_scale,
+                                                                   static_cast<__half*>(a.workspace), const_cast<float*>(rs));
   else
     convert_rows_kernel<__half><<<(unsigned)a.T, 256, 0, stream>>>(static_cast<const __half*>(a.x), a.K, a.row_scale,
                                                                    static_cast<__half*>(a.workspace), const_cast<float*>(rs));

@@ -126,7 +126,7 @@ def tile_weights(packed: torch.Tensor, fmt: str, K: int) -> TiledWeights:
 
 def fast_path_covers(K: int, group: int, scale_dtype, act_dtype=torch.bfloat16) -> bool:
     """Shapes the decode and prefill kernels accept (everything else runs on the generic kernel)."""
-    return group == 128 and K % 128 == 0 and scale_dtype == torch.float16 and act_dtype in (torch.bfloat16, torch.float16)
+    return group == 128 and K % 128 == 0 and scale_dtype == torch.float16 and act_dtype in (torch.bfloat16, torch.float16, torch.int8)
 
 
 def _stream(t: torch.Tensor):
@@ -248,8 +248,11 @@ def grouped_ternary_gemm(x: torch.Tensor, x_scale: torch.Tensor, offsets, packed
         raise RuntimeError(_UNAVAILABLE + ": activations are not on a CUDA device and this backend has no CPU path")
     out = torch.empty(x.size(0), packed.size(1), dtype=torch.float32, device=x.device)
     ws = w_scale if w_scale.dtype in _SCALE else w_scale.float()
-    return _grouped(lib, x.contiguous(), x_scale.float().contiguous(), offsets, [packed.contiguous()], [ws.contiguous()],
-                    K, group, fmt, out, False, "generic" if algo == "auto" else algo)
+    # fp16 scales and shapes the tcgen05 kernel covers: int8 activations go to the tensor cores (exact products,
+    # fp32 accumulation); anything else to the generic kernel with the reference's integer group sums
+    fast = isinstance(packed, TiledWeights) or fast_path_covers(K, group, ws.dtype, x.dtype)
+    return _grouped(lib, x.contiguous(), x_scale.float().contiguous(), offsets, [packed if isinstance(packed, TiledWeights) else packed.contiguous()],
+                    [ws.contiguous()], K, group, fmt, out, False, ("auto" if fast else "generic") if algo == "auto" else algo)
 
 
 def sort_by_expert(expert_ids: torch.Tensor, n_experts: int) -> tuple[torch.Tensor, torch.Tensor]:

@@ -201,6 +201,25 @@ def test_int8_contract_against_reference_golden(golden, kb):
 
 
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_int8_contract_on_the_tensor_core_path(kb, fmt):
+    """int8 activations with fp16 scales and tiled weights run on the tcgen05 kernel (int8 values and scale * trit are
+    exact in fp16, products exact in fp32): same contract, the reference's own tolerance (tests/test_ternary_cuda.py:80)."""
+    E, N, K, group = 4, 384, 1024, 128
+    rng = np.random.default_rng(31)
+    terms = make_terms(rng, N, K, group, fmt, 1, lead=(E,))
+    counts = np.array([300, 0, 40, 7])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    q, xs = O.quant_act_int8(rng.standard_normal((int(offsets[-1]), K)).astype(np.float32))
+    want = O.grouped_gemm_i8(q, xs, offsets, terms[0][0], terms[0][1].astype(np.float32), K, group, fmt)
+    tiled = kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), fmt, K)
+    for algo in ("auto", "prefill"):
+        got = kb.grouped_ternary_gemm(torch.from_numpy(q).to(DEV), torch.from_numpy(xs).to(DEV), offsets, tiled,
+                                      torch.from_numpy(terms[0][1]).to(DEV), K, group, fmt, algo=algo)
+        np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-3)
+        assert O.rel_fro(got.cpu().numpy(), want) < 1e-5
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
 def test_grouped_and_routing_sort_against_reference_golden(golden, kb, fmt):
     g = golden("grouped")
     ids = torch.from_numpy(g[f"{fmt}_ids"]).to(DEV)
