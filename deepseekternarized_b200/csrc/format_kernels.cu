@@ -85,6 +85,46 @@ int grid_for(int64_t total, int block) {
 }
 
 }  // namespace
+
+// Ternary lookup table rows: out[i, :] = bf16( sum over terms of trit * scale ), fp32 products added in term order
+// (boilerplate/engine/model.py:458-464: unpack(packed[ids]) * scale[ids].repeat_interleave(group), summed, -> bf16).
+// One block per looked-up row; an id outside [0, V) is counted and its row written as zeros.
+template <int FMT>
+__global__ void gather_dequant_kernel(Terms terms, int scale_dtype, const int64_t* __restrict__ ids, int64_t V, int64_t K, int64_t Kp,
+                                      int64_t G, int64_t group, __nv_bfloat16* __restrict__ out, int32_t* __restrict__ bad_count) {
+  constexpr int PER = FMT == 2 ? 4 : 5;
+  const int64_t i = blockIdx.x;
+  const int64_t row = ids[i];
+  __nv_bfloat16* o = out + i * K;
+  if (row < 0 || row >= V) {
+    if (threadIdx.x == 0 && bad_count) atomicAdd(bad_count, 1);
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) o[k] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  for (int64_t b = threadIdx.x; b < Kp; b += blockDim.x) {
+    float acc[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) acc[j] = 0.f;
+    for (int t = 0; t < terms.n; ++t) {
+      const uint32_t v = terms.packed[t][row * Kp + b];
+      const uint32_t f = FMT == 2 ? v : tq1_fields(v);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int64_t k = b * PER + j;
+        if (k < K) {
+          const float val = (float)((int)((f >> (2 * j)) & 3u) - 1) * scale_to_float(terms.scale[t], row * G + k / group, scale_dtype);
+          acc[j] = t == 0 ? val : acc[j] + val;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int64_t k = b * PER + j;
+      if (k < K) o[k] = __float2bfloat16_rn(acc[j]);
+    }
+  }
+}
+
 }  // namespace dst
 
 extern "C" int64_t dst_packed_cols(int fmt, int64_t K) {
@@ -133,6 +173,30 @@ extern "C" int dst_quant_act_int8(const void* x, int x_is_f32, int64_t M, int64_
     dst::quant_act_kernel<float><<<(unsigned)M, 256, 0, st>>>(static_cast<const float*>(x), K, q, s);
   else
     dst::quant_act_kernel<__nv_bfloat16><<<(unsigned)M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, q, s);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_gather_dequant_rows(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
+                                       const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt, void* out_bf16,
+                                       int32_t* bad_count, dst_stream_t stream) {
+  if ((fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2) || K <= 0 || group <= 0 || V < 0 || n_ids < 0) return DST_ERR_BAD_ARG;
+  if (n_terms < 1 || n_terms > DST_MAX_TERMS || scale_dtype < DST_SCALE_F16 || scale_dtype > DST_SCALE_BF16) return DST_ERR_BAD_ARG;
+  if (n_ids == 0) return DST_OK;
+  if (!packed || !scales || !ids || !out_bf16) return DST_ERR_BAD_ARG;
+  if (n_ids > 0x7fffffff || K > (int64_t(1) << 24)) return DST_ERR_BAD_SHAPE;
+  dst::Terms terms;
+  terms.n = n_terms;
+  for (int i = 0; i < n_terms; ++i) {
+    if (!packed[i] || !scales[i]) return DST_ERR_BAD_ARG;
+    terms.packed[i] = static_cast<const uint8_t*>(packed[i]);
+    terms.scale[i] = scales[i];
+  }
+  const int64_t Kp = dst_packed_cols(fmt, K), G = (K + group - 1) / group;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto o = static_cast<__nv_bfloat16*>(out_bf16);
+  if (fmt == DST_FMT_TQ2) dst::gather_dequant_kernel<2><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, G, group, o, bad_count);
+  else dst::gather_dequant_kernel<1><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, G, group, o, bad_count);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

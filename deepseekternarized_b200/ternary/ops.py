@@ -117,3 +117,41 @@ class TernaryLinear:
             out = kb.grouped_ternary_gemm_bf16(xa, None, packed, scales, self.K, self.group, self.fmt, out_dtype=od,
                                                algo=self.algo, backend=self.backend)
         return out.view(*shape[:-1], -1).to(out_dtype)
+
+
+def gather_dequant_rows(terms, ids: torch.Tensor, K: int, fmt: str, group: int) -> torch.Tensor:
+    """Rows ``ids`` of a ternary lookup table as bf16: ``sum_i unpack(packed_i[ids]) * scale_i[ids].repeat(group)``
+    in fp32, then the cast (the engram-table lookup of ``boilerplate/engine/model.py:458-464``).
+
+    ``terms``: PackedTerm list (canonical ``packed`` [V, Kp], ``scale`` [V, G]) on the device of ``ids``."""
+    import ctypes
+
+    from .. import _lib
+    from ..kernels import ternary_b200 as kb
+
+    lib = kb._require("auto")
+    code = kb._fmt_code(fmt)
+    if not ids.is_cuda:
+        raise RuntimeError("the B200 ternary backend is unavailable: ids are not on a CUDA device and this backend has no CPU path")
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    packed = [t.packed.contiguous() for t in terms]
+    scales = [t.scale.contiguous() for t in terms]
+    V = packed[0].size(0)
+    G = -(-K // group)
+    sdt = scales[0].dtype
+    if sdt not in kb._SCALE or any(s.dtype != sdt for s in scales):
+        raise RuntimeError("unexpected table scale dtype")
+    for p_, s_ in zip(packed, scales):
+        if p_.dtype != torch.uint8 or tuple(p_.shape) != (V, kb.packed_cols(fmt, K)) or tuple(s_.shape) != (V, G) or p_.device != flat.device or s_.device != flat.device:
+            raise RuntimeError("inconsistent ternary table shapes")
+    out = torch.empty(flat.numel(), K, dtype=torch.bfloat16, device=flat.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=flat.device)
+    n = len(packed)
+    pk = (ctypes.c_void_p * n)(*[p_.data_ptr() for p_ in packed])
+    sc = (ctypes.c_void_p * n)(*[s_.data_ptr() for s_ in scales])
+    with torch.cuda.device(flat.device):
+        _lib.check(lib.dst_gather_dequant_rows(pk, sc, n, kb._SCALE[sdt], flat.data_ptr(), flat.numel(), V, K, group, code, out.data_ptr(),
+                                               bad.data_ptr(), kb._stream(flat)))
+    if int(bad.item()):
+        raise IndexError("table row index out of range")
+    return out.view(*ids.shape, K)

@@ -223,6 +223,16 @@ int dst_combine_weighted(const void* down_bf16, const int64_t* order, const int3
                          int top_k, int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
 
 /*
+ * Rows of a ternary lookup table (the Mode C/D engram tables): out[i, :] = bf16( sum over terms of
+ * trit[ids[i], :] * scale[ids[i], : / group] ), fp32 products added in term order. packed[t] [V, ceil(K / per)]
+ * canonical rows, scales[t] [V, ceil(K / group)] of scale_dtype. An id outside [0, V) is counted in *bad_count
+ * (device int32, may be NULL) and its row is written as zeros. Replaces boilerplate/engine/model.py:458-464.
+ */
+int dst_gather_dequant_rows(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
+                            const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt, void* out_bf16,
+                            int32_t* bad_count, dst_stream_t stream);
+
+/*
  * Expert-parallel dispatch and combine over peer memory (the reference has no expert-parallel exchange of routed
  * rows: its EP form replicates tokens and all-reduces, third_party/deepseek_v41_inference/model.py:897-905; these
  * two entries serve the sharding of the same file, :869-872, expert e on rank e / experts_per_rank).

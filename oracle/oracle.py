@@ -303,6 +303,20 @@ def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_li
     return bf16_round(y)
 
 
+def gather_dequant_rows(ids, terms, K: int, group: int, fmt: str) -> np.ndarray:
+    """boilerplate/engine/model.py:458-464 (ternary engram-table lookup): for every id the row
+    ``sum_i unpack(packed_i[id]) * scale_i[id].repeat(group)[:K]`` in fp32 (terms added in order), cast to bf16
+    (returned as float32 holding bf16 values)."""
+    flat = np.asarray(ids, np.int64).reshape(-1)
+    vals = None
+    for packed, scale in terms:
+        t = unpack(np.ascontiguousarray(packed[flat]), fmt, K).astype(np.float32)
+        sc = np.repeat(np.asarray(scale)[flat].astype(np.float32), group, axis=-1)[:, :K]
+        v = (t * sc).astype(np.float32)
+        vals = v if vals is None else (vals + v).astype(np.float32)
+    return bf16_round(vals).reshape(*np.asarray(ids).shape, K)
+
+
 def moe_layer_standard(x, logits, experts, top_k, hidden, inter, group, fmt, norm_topk_prob=True):
     """boilerplate/engine/standard.py:154-176 (OLMoE-style layer) with bf16 as the model dtype: softmax over all
     experts -> top-k -> optional renormalisation -> weights to bf16; per expert in increasing id

@@ -276,6 +276,36 @@ def main():
         s_out[pre + "y_bits"] = bits(y)
     np.savez_compressed(HERE / "moe_layer_standard.npz", **s_out)
 
+    # ---------------------------------------------------------------- 5c. ternary lookup-table rows (engram tables)
+    # the expression of boilerplate/engine/model.py:458-464 with the reference's own unpack
+    t_out = {}
+    for ci, (fmt, k_terms, K, group) in enumerate((("tq1", 1, 192, 64), ("tq2", 2, 203, 128))):
+        rng = np.random.default_rng(5800 + ci)
+        V = 50
+        terms = []
+        for i in range(k_terms):
+            t = trits_of(rng, (V, K))
+            s = scales_of(rng, (V, -(-K // group)))
+            if i == 1:
+                s = (s.astype(np.float32) * 0.25).astype(np.float16)
+            terms.append((pack(torch.from_numpy(t), fmt), torch.from_numpy(s)))
+        ids = torch.from_numpy(rng.integers(0, V, (3, 7)))
+        flat = ids.reshape(-1)
+        vals = None
+        for packed, sc in terms:
+            t = unpack(packed.index_select(0, flat), fmt, K).float()
+            v = t * sc.index_select(0, flat).float().repeat_interleave(group, -1)[:, :K]
+            vals = v if vals is None else vals + v
+        vals = vals.to(torch.bfloat16)
+        pre = f"{fmt}_"
+        t_out[pre + "meta"] = np.array([V, K, group, k_terms], np.int64)
+        t_out[pre + "ids"] = ids.numpy()
+        for i, (p, s) in enumerate(terms):
+            t_out[pre + f"packed{i}"] = p.numpy()
+            t_out[pre + f"scale{i}"] = s.numpy()
+        t_out[pre + "vals_bits"] = bits(vals)
+    np.savez_compressed(HERE / "table_rows.npz", **t_out)
+
     # ---------------------------------------------------------------- 6. BASELINE config-0/1 shapes (hash + sample)
     big = {}
     for ci, (fmt, N, K, M) in enumerate([("tq2", 4096, 4096, 1), ("tq2", 4096, 4096, 16), ("tq1", 4096, 4096, 1),

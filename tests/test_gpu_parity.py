@@ -443,6 +443,30 @@ def test_sort_large_and_bad_ids(kb):
     assert order.numel() == 0 and offsets.cpu().tolist() == [0] * 5
 
 
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_table_row_lookup_against_reference_golden(golden, fmt):
+    """Ternary lookup-table rows (boilerplate/engine/model.py:458-464) on the GPU: bit-exact with the reference."""
+    from deepseekternarized_b200.ternary.ops import PackedTerm, gather_dequant_rows
+
+    g = golden("table_rows")
+    V, K, group, k_terms = (int(v) for v in g[f"{fmt}_meta"])
+    terms = [PackedTerm(torch.from_numpy(g[f"{fmt}_packed{i}"]).to(DEV), torch.from_numpy(g[f"{fmt}_scale{i}"]).to(DEV)) for i in range(k_terms)]
+    ids = torch.from_numpy(g[f"{fmt}_ids"]).to(DEV)
+    vals = gather_dequant_rows(terms, ids, K, fmt, group)
+    assert tuple(vals.shape) == (*ids.shape, K) and vals.dtype == torch.bfloat16
+    assert np.array_equal(O.bf16_bits(bf16_numpy(vals)).reshape(-1, K), g[f"{fmt}_vals_bits"])
+    with pytest.raises(IndexError):
+        gather_dequant_rows(terms, torch.tensor([0, V], device=DEV), K, fmt, group)
+    # a larger table against the oracle
+    rng = np.random.default_rng(9)
+    V2, K2 = 3000, 1024
+    big = make_terms(rng, V2, K2, 128, fmt, 2)
+    ids2 = rng.integers(0, V2, 4096)
+    got = gather_dequant_rows([PackedTerm(torch.from_numpy(p).to(DEV), torch.from_numpy(s).to(DEV)) for p, s in big],
+                              torch.from_numpy(ids2).to(DEV), K2, fmt, 128)
+    assert np.array_equal(bf16_numpy(got), O.gather_dequant_rows(ids2, big, K2, 128, fmt))
+
+
 def test_expert_parallel_peer_transport_single_rank():
     """The peer-memory dispatch / combine kernels and the placement arithmetic in a one-rank job (every routed row is
     local): bit-identical to the single-device layer, also through the all-to-all transport. Runs in a child

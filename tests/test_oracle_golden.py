@@ -137,3 +137,14 @@ def test_moe_layer_standard_flavour_matches_reference(golden, fmt):
     assert O.rel_fro(y, want) < 2e-3
     mism = np.mean(O.bf16_bits(y) != g[f"{fmt}_y_bits"])
     assert mism < 0.02, mism
+
+
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_table_row_lookup_matches_reference(golden, fmt):
+    """boilerplate/engine/model.py:458-464: rows of a ternary lookup table, dequantised and summed over terms."""
+    g = golden("table_rows")
+    V, K, group, k_terms = (int(v) for v in g[f"{fmt}_meta"])
+    terms = [(g[f"{fmt}_packed{i}"], g[f"{fmt}_scale{i}"]) for i in range(k_terms)]
+    vals = O.gather_dequant_rows(g[f"{fmt}_ids"], terms, K, group, fmt)
+    assert vals.shape == (*g[f"{fmt}_ids"].shape, K)
+    assert np.array_equal(O.bf16_bits(vals).reshape(-1, K), g[f"{fmt}_vals_bits"])
