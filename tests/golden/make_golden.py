@@ -3,7 +3,7 @@
 Run it where the reference tree is mounted (it cannot travel with the fixtures)::
 
     CXX=/usr/bin/g++ CC=/usr/bin/gcc TORCH_EXTENSIONS_DIR=/tmp/dst_ref_ext \
-        PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--reference /root/reference]
+        PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--reference <path of the reference tree>]
 
 Every expectation is produced by reference functions, unmodified, imported from that tree:
 ``boilerplate.ternary.pack`` (pack/unpack/LUT), ``boilerplate.ternary.ops`` (TernaryLinear with
