@@ -479,3 +479,61 @@ def test_expert_parallel_peer_transport_single_rank():
     res = subprocess.run([sys.executable, str(Path(__file__).with_name("ep_peer_check.py"))], env=env, capture_output=True, text=True,
                          timeout=600)
     assert res.returncode == 0 and "EP_PEER_CHECK PASS" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+@pytest.mark.parametrize("W", [4, 8])
+def test_ep_peer_kernels_with_emulated_ranks(W):
+    """The peer-memory dispatch / combine entries for 4 and 8 ranks on ONE GPU: every "rank" has its own buffers on
+    this device and the ranks' steps run one after the other (none of the kernels waits on another rank), with the
+    same placement arithmetic, pointer tables and grouped GEMMs as ExpertParallelMoE. Result = the single-device layer."""
+    import ctypes
+
+    from deepseekternarized_b200 import _lib
+    from deepseekternarized_b200.kernels import ternary_b200 as kb
+    from deepseekternarized_b200.moe import B200Ops, ExpertWeights, MoELayer, ep_placement
+
+    E, hidden, inter, topk, group, fmt, tl = 16, 256, 128, 4, 128, "tq1", 96
+    El, T = E // W, 96 * W
+    rng = np.random.default_rng(40 + W)
+    experts = make_experts(rng, E, hidden, inter, group, fmt, 1)
+    x = bf16_tensor(O.synth_acts(rng, (T, hidden)), DEV)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    logits[:, 5] = -40.0
+    logits = torch.from_numpy(logits).to(DEV)
+    ops, lib = B200Ops(), kb.ext()
+    cap = tl * topk * W
+    bufs = [dict(rows=torch.empty(cap, hidden, dtype=torch.float16, device=DEV), fac=torch.empty(cap, device=DEV),
+                 wts=torch.empty(cap, device=DEV), down=torch.empty(cap, hidden, dtype=torch.bfloat16, device=DEV)) for _ in range(W)]
+    ptrs = {k: (ctypes.c_void_p * W)(*[b[k].data_ptr() for b in bufs]) for k in ("rows", "fac", "wts", "down")}
+    stream = kb._stream(x)
+    routed = []
+    for r in range(W):  # route and sort per rank; all-gather of the counts = stack
+        w, ids = ops.route(logits[r * tl:(r + 1) * tl], topk, 1.0)
+        order, offsets = ops.sort(ids, E)
+        routed.append((w.reshape(-1).contiguous(), ids, order, offsets))
+    counts_all = torch.stack([o[3].diff() for o in routed])
+    place = [ep_placement(counts_all, r, El) for r in range(W)]
+    for r in range(W):  # push
+        w, ids, order, offsets = routed[r]
+        xr = x[r * tl:(r + 1) * tl].contiguous()
+        _lib.check(lib.dst_ep_push_rows(xr.data_ptr(), order.data_ptr(), offsets.data_ptr(), w.data_ptr(), place[r][0].data_ptr(),
+                                        order.numel(), E, El, topk, hidden, ptrs["rows"], ptrs["fac"], ptrs["wts"], W, stream))
+    for r in range(W):  # experts of rank r on the rows it received
+        offsets2 = place[r][1]
+        R = int(offsets2[-1])
+        wl = ExpertWeights(*stack_experts(experts[r * El:(r + 1) * El], 1, DEV), hidden, inter, group, fmt).prepare()
+        if R:
+            MoELayer(wl, topk).experts_forward(kb.NormRows(bufs[r]["rows"][:R], bufs[r]["fac"][:R]), offsets2, bufs[r]["wts"][:R], None,
+                                               out=bufs[r]["down"][:R])
+    ys = []
+    for r in range(W):  # pull + combine
+        w, ids, order, offsets = routed[r]
+        inv = torch.empty(tl * topk, dtype=torch.int64, device=DEV)
+        y = torch.empty(tl, hidden, dtype=torch.bfloat16, device=DEV)
+        ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        _lib.check(lib.dst_ep_combine_pull(ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(), place[r][0].data_ptr(),
+                                           tl, El, topk, hidden, inv.data_ptr(), y.data_ptr(), W, stream))
+        ys.append(y)
+    w_all = ExpertWeights(*stack_experts(experts, 1, DEV), hidden, inter, group, fmt).prepare()
+    want = torch.cat([MoELayer(w_all, topk)(x[r * tl:(r + 1) * tl].contiguous(), logits[r * tl:(r + 1) * tl].contiguous()) for r in range(W)])
+    assert torch.equal(torch.cat(ys), want)
