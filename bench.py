@@ -100,7 +100,10 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []  # lines: (host time when read, text)
-        self.t0 = self.t1 = None
+        self.t0 = self.t1 = self.t_load = None
+
+    def mark_load(self):
+        self.t_load = time.time()
 
     def mark_begin(self):
         self.t0 = time.time()
@@ -132,6 +135,11 @@ class ClockSampler:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         inside = [ln for ts, ln in self.lines if self.t0 is None or (self.t0 <= ts <= (self.t1 or ts) + 0.05)]
+        window = "timed region"
+        if len(inside) < 3 and self.t_load is not None:
+            # a timed region of a few sampling periods at most: add the samples of the identical steps run right before it
+            inside = [ln for ts, ln in self.lines if self.t_load <= ts <= (self.t1 or ts) + 0.05]
+            window = "timed region and the identical untimed steps directly before it"
         for ln in inside:
             f = [v.strip() for v in ln.split(",")]
             if len(f) < 8:
@@ -145,7 +153,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------------------------- CPU baseline
@@ -437,8 +445,17 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # started ahead of the timed region (nvidia-smi takes a moment to deliver its first sample)
-    for _ in range(20):
-        step_resident()
+    sampler.mark_load()
+    t_load = time.time()
+    while True:  # the same steps, untimed, for at least 0.4 s: clocks settle and the sampler sees the GPU under this load
+        for _ in range(20):
+            step_resident()
+        torch.cuda.synchronize()
+        go = torch.tensor([1 if time.time() - t_load < 0.4 else 0], device=device)
+        if world > 1:
+            dist.all_reduce(go, op=dist.ReduceOp.MAX)  # every rank leaves the loop after the same number of steps
+        if int(go.item()) == 0:
+            break
     ops.launches, ops.timing = 0, True
     sampler.mark_begin()
     total_ms = timed(step_resident, args.steps)
