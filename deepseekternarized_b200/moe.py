@@ -425,3 +425,70 @@ class ExpertParallelMoE:
         return self.ops.combine(down, order, ids, T, self.top_k)
 
     __call__ = forward
+
+
+class HostPipeline:
+    """Feeds a MoE layer from pinned host buffers with the copies of neighbouring batches overlapped with compute.
+
+    The reference engines hand the layer host-resident activations one batch at a time. Here batch ``i``'s
+    host-to-device copy runs on its own stream while batch ``i-1`` computes, and batch ``i-1``'s result returns on a
+    third stream while batch ``i`` computes (a B200 copies in both directions at once). Device input buffers are
+    double-buffered; a slot is rewritten only after the compute that read it has finished. ``submit`` returns as soon
+    as the work is queued; ``join`` makes the current stream wait for every queued result copy, ``drain`` blocks the host.
+    Host buffers must be pinned (a pageable buffer makes the copy synchronous and the overlap is lost, the results are
+    the same).
+    """
+
+    def __init__(self, layer, max_tokens: int, hidden: int, n_experts: int, device, slots: int = 2):
+        if slots < 2:
+            raise ValueError("HostPipeline needs at least two input slots")
+        self.layer, self.dev, self.slots = layer, torch.device(device), slots
+        if self.dev.type != "cuda":
+            raise RuntimeError("HostPipeline: a CUDA device is required (there is no CPU path)")
+        self.h2d, self.d2h = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self.x = [torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=self.dev) for _ in range(slots)]
+        self.logits = [torch.empty(max_tokens, n_experts, dtype=torch.float32, device=self.dev) for _ in range(slots)]
+        self.read_done = [None] * slots  # per slot: event after the compute that read it
+        self.last_copy = None
+        self.n = 0
+
+    def submit(self, x_host: torch.Tensor, logits_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Queue one batch: x_host [T, hidden] bf16, logits_host [T, E] f32 -> y_host [T, hidden] bf16 (written when
+        the batch's result copy completes)."""
+        T = x_host.size(0)
+        if T > self.x[0].size(0) or x_host.size(1) != self.x[0].size(1) or tuple(logits_host.shape) != (T, self.logits[0].size(1)):
+            raise ValueError("HostPipeline.submit: batch does not fit the buffers this pipeline was built with")
+        if tuple(y_host.shape) != tuple(x_host.shape) or y_host.dtype != torch.bfloat16:
+            raise ValueError("HostPipeline.submit: y_host must be bf16 with the shape of x_host")
+        b = self.n % self.slots
+        self.n += 1
+        cur = torch.cuda.current_stream(self.dev)
+        xd, ld = self.x[b][:T], self.logits[b][:T]
+        with torch.cuda.stream(self.h2d):
+            if self.read_done[b] is not None:
+                self.h2d.wait_event(self.read_done[b])
+            xd.copy_(x_host, non_blocking=True)
+            ld.copy_(logits_host, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(self.h2d)
+        cur.wait_event(ready)
+        y = self.layer(xd, ld)
+        done = torch.cuda.Event()
+        done.record(cur)
+        self.read_done[b] = done
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(done)
+            y_host.copy_(y, non_blocking=True)
+            y.record_stream(self.d2h)
+            self.last_copy = torch.cuda.Event()
+            self.last_copy.record(self.d2h)
+
+    def join(self) -> None:
+        """The current stream waits for every result copy queued so far (an event recorded after this covers them)."""
+        if self.last_copy is not None:
+            torch.cuda.current_stream(self.dev).wait_event(self.last_copy)
+
+    def drain(self) -> None:
+        """Block the host until every queued batch's result is in its host buffer."""
+        if self.last_copy is not None:
+            self.last_copy.synchronize()

@@ -431,6 +431,29 @@ def test_moe_layer_steps_against_oracle(fmt, k_terms):
     assert torch.equal(y, y2)
 
 
+def test_host_pipeline_equals_direct_calls():
+    """Batches fed from pinned host buffers through the three-stream pipeline (ragged sizes, more batches than
+    slots, distinct output buffers) equal the layer called on device-resident copies of the same batches."""
+    from deepseekternarized_b200.moe import ExpertWeights, HostPipeline, MoELayer
+
+    hidden, inter, E, topk, group = 512, 256, 16, 6, 128
+    rng = np.random.default_rng(23)
+    experts = make_experts(rng, E, hidden, inter, group, "tq1", 1)
+    layer = MoELayer(ExpertWeights(*stack_experts(experts, 1, DEV), hidden, inter, group, "tq1").prepare(), topk)
+    sizes = [300, 1, 257, 300, 64, 129, 300]
+    pipe = HostPipeline(layer, max(sizes), hidden, E, DEV)
+    xs = [bf16_tensor(O.synth_acts(rng, (t, hidden)), "cpu").pin_memory() for t in sizes]
+    lgs = [torch.from_numpy(rng.standard_normal((t, E)).astype(np.float32)).pin_memory() for t in sizes]
+    ys = [torch.empty(t, hidden, dtype=torch.bfloat16).pin_memory() for t in sizes]
+    for x, lg, y in zip(xs, lgs, ys):
+        pipe.submit(x, lg, y)
+    pipe.drain()
+    for x, lg, y in zip(xs, lgs, ys):
+        assert torch.equal(y, layer(x.to(DEV), lg.to(DEV)).cpu())
+    with pytest.raises(ValueError):
+        pipe.submit(torch.empty(301, hidden, dtype=torch.bfloat16), torch.empty(301, E), torch.empty(301, hidden, dtype=torch.bfloat16))
+
+
 def test_sort_large_and_bad_ids(kb):
     rng = np.random.default_rng(3)
     ids = rng.integers(0, 384, 98304).astype(np.int64)

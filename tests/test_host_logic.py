@@ -107,3 +107,12 @@ def test_ep_placement_matches_brute_force():
         dst_start, offsets_local = ep_placement(c, r, El)
         assert np.array_equal(dst_start.numpy(), want_start[r])
         assert np.array_equal(offsets_local.numpy(), want_offsets[r])
+
+
+def test_host_pipeline_has_no_cpu_path():
+    from deepseekternarized_b200.moe import HostPipeline
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        HostPipeline(lambda x, lg: x, 8, 16, 4, "cpu")
+    with pytest.raises(ValueError):
+        HostPipeline(lambda x, lg: x, 8, 16, 4, "cpu", slots=1)
