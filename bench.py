@@ -58,26 +58,12 @@ def measured_peaks():
 
 # --------------------------------------------------------------------------------------------- synthetic data
 def synth_expert_weights(n_local: int, expert0: int, device, fmt=None, hidden=HIDDEN, inter=INTER):
-    """Seeded random-init experts generated on the device: trits i.i.d. P(0)=0.4, P(+-1)=0.3, scales
-    lognormal(-4, 0.3) in fp16. Expert e's weights depend only on (SEED, e), so every sharding sees the
-    same global model."""
-    from deepseekternarized_b200.moe import ExpertWeights
-    from deepseekternarized_b200.ternary.pack import pack, packed_cols
+    """Seeded random-init experts generated on the device (deepseekternarized_b200/synth.py): trits i.i.d. P(0)=0.4,
+    P(+-1)=0.3, scales lognormal(-4, 0.3) in fp16. Expert e's weights depend only on (SEED, e), so every sharding
+    sees the same global model."""
+    from deepseekternarized_b200.synth import synth_expert_weights as synth
 
-    fmt = FMT if fmt is None else fmt
-    w13p = torch.empty(n_local, 2 * inter, packed_cols(fmt, hidden), dtype=torch.uint8, device=device)
-    w13s = torch.empty(n_local, 2 * inter, hidden // GROUP, dtype=torch.float16, device=device)
-    w2p = torch.empty(n_local, hidden, packed_cols(fmt, inter), dtype=torch.uint8, device=device)
-    w2s = torch.empty(n_local, hidden, inter // GROUP, dtype=torch.float16, device=device)
-    g = torch.Generator(device=device)
-    for i in range(n_local):
-        g.manual_seed(SEED + 1000 * (expert0 + i))
-        for dst_p, dst_s, (Nw, Kw) in ((w13p, w13s, (2 * inter, hidden)), (w2p, w2s, (hidden, inter))):
-            u = torch.rand(Nw, Kw, generator=g, device=device)
-            t = torch.where(u < 0.4, 0, torch.where(u < 0.7, 1, -1)).to(torch.int8)
-            dst_p[i] = pack(t, fmt)
-            dst_s[i] = torch.exp(torch.randn(Nw, Kw // GROUP, generator=g, device=device) * 0.3 - 4.0).half()
-    return ExpertWeights([w13p], [w13s], [w2p], [w2s], hidden, inter, GROUP, fmt).prepare()
+    return synth(n_local, expert0, device, FMT if fmt is None else fmt, hidden, inter, SEED)
 
 
 def synth_tokens(n_tokens: int, token0: int, n_experts=None, hidden=HIDDEN):

@@ -30,6 +30,7 @@ ALGO_AUTO, ALGO_GENERIC, ALGO_DECODE, ALGO_PREFILL = 0, 1, 2, 3
 MAX_TERMS = 4
 MAX_PEERS = 16
 LAYOUT_CANONICAL, LAYOUT_TILED = 0, 1
+SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
 
 
 def nvcc_path() -> str:
@@ -92,6 +93,13 @@ _SIGNATURES = {
                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_route_softmax_topk_ex": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
                                                  ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_route_topk": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_float, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_combine_add": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                       ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_ep_combine_pull_add": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p,
+                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]),
     "dst_swiglu_std": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_swiglu_std_norm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_void_p]),
@@ -125,7 +133,7 @@ def load() -> ctypes.CDLL:
     """dlopen the built library and declare every exported symbol. Raises if it was never built."""
     path = Path(os.environ.get("DST_B200_LIB", str(LIB_PATH)))  # DST_B200_LIB: load a library built elsewhere
     if not path.exists():
-        raise RuntimeError(f"{path} is missing: run __graft_entry__.build() (there is no CPU fallback)")
+        raise RuntimeError(f"{path} is missing: build it with deepseekternarized_b200._lib.build() (there is no CPU fallback)")
     lib = ctypes.CDLL(str(path))
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)

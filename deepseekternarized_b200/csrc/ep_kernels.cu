@@ -52,7 +52,9 @@ ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ 
   __shared__ float red[32];
   __shared__ int64_t s_dst[2];
   const int64_t p = blockIdx.x;
-  const int64_t slot = order[p];
+  if (p >= offsets[E]) return;  // rows past the last expert's range belong to ids the routing sort dropped
+  int64_t slot = order[p];
+  slot = slot < 0 ? 0 : (slot >= (int64_t)gridDim.x ? (int64_t)gridDim.x - 1 : slot);  // never leaves the token rows
   if (threadIdx.x == 0) {
     const int g = expert_of_row(offsets, E, p);
     s_dst[0] = g / El;
@@ -114,10 +116,13 @@ __global__ void ep_invert_order_kernel(const int64_t* __restrict__ order, int64_
   }
 }
 
-// One block per token: its top_k rows, read from the ranks that own the experts, in increasing expert id.
+// One block per token: its top_k rows, read from the ranks that own the experts, in increasing expert id, then the
+// optional local row of `add` (the shared expert's output). A slot whose expert id is outside [0, E) or whose row
+// was dropped by the routing sort (inv = -1) contributes nothing.
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, const int64_t* __restrict__ offsets,
-                  const int64_t* __restrict__ dst_start, int El, int top_k, int64_t hidden, __nv_bfloat16* __restrict__ y) {
+                  const int64_t* __restrict__ dst_start, int E, int El, int top_k, int64_t hidden, const __nv_bfloat16* __restrict__ add,
+                  __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
   const __nv_bfloat16* src[8];
   int eid[8];
@@ -125,7 +130,8 @@ ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t*
     const int g = ids[t * top_k + s];
     const int64_t p = inv[t * top_k + s];
     eid[s] = g;
-    src[s] = static_cast<const __nv_bfloat16*>(down.p[g / El]) + (dst_start[g] + (p - offsets[g])) * hidden;
+    const bool ok = g >= 0 && g < E && p >= 0;
+    src[s] = ok ? static_cast<const __nv_bfloat16*>(down.p[g / El]) + (dst_start[g] + (p - offsets[g])) * hidden : nullptr;
   }
   for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
     const int e = eid[i];
@@ -143,8 +149,15 @@ ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t*
   for (int c = threadIdx.x; c < chunks; c += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < top_k; ++s) {
+      if (src[s] == nullptr) continue;
       float f[8];
       bf16x8_to_float(reinterpret_cast<const uint4*>(src[s])[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    if (add) {
+      float f[8];
+      bf16x8_to_float(reinterpret_cast<const uint4*>(add + t * hidden)[c], f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
@@ -199,23 +212,32 @@ extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const 
   return DST_OK;
 }
 
-extern "C" int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
-                                   const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
-                                   void* y_bf16, int world, dst_stream_t stream) {
+extern "C" int dst_ep_combine_pull_add(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
+                                       const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden,
+                                       int64_t* inv, const void* add_bf16, void* y_bf16, int world, dst_stream_t stream) {
   if (T < 0 || experts_per_rank <= 0 || top_k <= 0 || top_k > 8 || hidden <= 0 || world < 1 || world > DST_MAX_PEERS) return DST_ERR_BAD_ARG;
   if (hidden % 8 != 0) return DST_ERR_UNSUPPORTED;
   if (T == 0) return DST_OK;
   if (!peer_down_bf16 || !order || !ids || !offsets || !dst_start || !inv || !y_bf16) return DST_ERR_BAD_ARG;
-  if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(y_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
+  if (T > 0x7fffffff / top_k || experts_per_rank * world > DST_MAX_EXPERTS) return DST_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(y_bf16) & 15) != 0 || (reinterpret_cast<uintptr_t>(add_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
   PeerPtrs down;
   if (!fill_peers(down, peer_down_bf16, world)) return DST_ERR_ALIGNMENT;
   auto st = static_cast<cudaStream_t>(stream);
   const int64_t n = T * top_k;
+  DST_CUDA_TRY(cudaMemsetAsync(inv, 0xff, (size_t)n * sizeof(int64_t), st));  // -1: the slot has no row
   ep_invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
   DST_CUDA_TRY(cudaGetLastError());
-  ep_combine_kernel<<<(unsigned)T, 256, 0, st>>>(down, inv, ids, offsets, dst_start, (int)experts_per_rank, top_k, hidden,
+  ep_combine_kernel<<<(unsigned)T, 256, 0, st>>>(down, inv, ids, offsets, dst_start, (int)(experts_per_rank * world), (int)experts_per_rank,
+                                                top_k, hidden, static_cast<const __nv_bfloat16*>(add_bf16),
                                                 static_cast<__nv_bfloat16*>(y_bf16));
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
+}
+
+extern "C" int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
+                                   const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
+                                   void* y_bf16, int world, dst_stream_t stream) {
+  return dst_ep_combine_pull_add(peer_down_bf16, order, ids, offsets, dst_start, T, experts_per_rank, top_k, hidden, inv, nullptr, y_bf16,
+                                 world, stream);
 }

@@ -2,254 +2,517 @@
 //
 //     out[m, n] = row_scale[m] * sum_i sum_g scale_i[e, n, g] * sum_{k in g} x[m, k] * trit_i[e, n, k]
 //
-// Every packed byte is read once, with 128-bit loads that are contiguous across a warp (tiled layout, see
-// layout_kernels.cu: a quad of lanes reads one weight row's 64-byte superblock, eight rows are 512 contiguous
-// bytes). The multiply-adds run on mma.sync.m16n8k16 (fp16 in, fp32 accumulate) fed straight from registers:
+// Every packed byte crosses HBM once: one thread per CTA streams the 64-row halves of the tiled layout's 8 KB slabs
+// (layout_kernels.cu) into a shared-memory ring with cp.async.bulk + mbarrier, four consumer warps read them from
+// there with 128-bit loads. The multiply-adds are exact integer arithmetic on mma.sync.m16n8k32 (u8 x s8 -> s32)
+// fed straight from registers:
 //
-//   A fragment  a weight row's packed word ANDed with a 2-bit field mask IS the operand: the fp16 bit pattern
-//               with only mantissa bits set is the denormal u * 4^j * 2^-24 (u = t + 1 in {0,1,2}). The tensor
-//               core takes fp16 denormals exactly on this hardware (measured), so unpacking costs one AND per
-//               two weights and no conversion.
-//   B fragment  the token rows, staged once per expert in shared memory as fp16 multiplied by the matching
-//               4^-j (and a per-token power of two that brings the row's maximum below 256), so the product
-//               is u * x * 2^-17 for every field position.
-//   offset      sum_k u_k x_k = sum_k t_k x_k + sum_k x_k: the per-(token, group) sums of x are computed at
-//               staging time from the same rounded values and subtracted per scale group.
+//   A fragment  a weight row's packed word ANDed with a byte-wise 2-bit field mask IS the operand: four u8 digits
+//               u = t + 1 in {0,1,2} (mask 0x03030303) or four digits times 4 (mask 0x0c0c0c0c); the other two
+//               fields of every byte come from the word shifted right by 4. Unpacking costs one AND per four
+//               weights and one shift per sixteen; the x1 and x4 operands accumulate apart and are merged once per
+//               scale group.
+//   B fragment  the token rows, staged once per expert in shared memory as 15-bit integers q = rint(x / s),
+//               s = rowmax / 16256, split into two s8 columns q = 128 hi + lo (|x - s q| <= rowmax / 32512), laid
+//               out in the order the lanes consume them so a lane's B registers of two MMAs are one 128-bit load.
+//               int8 activations (the reference's CUDA contract) go in as they are (hi = 0): that path is exact.
+//   offset      sum_k u_k q_k = sum_k t_k q_k + sum_k q_k: the per-(token, group) integer sums of q are computed
+//               at staging time and subtracted per scale group.
+//   columns     an MMA has eight B columns = four (hi, lo) pairs. With four or more token rows a pair is a token.
+//               With one (two) token rows the four pairs are four (two) CONSECUTIVE SCALE GROUPS of the same
+//               token: a lane feeds real activations only to the MMAs of its own group and reads zeros for the
+//               others, so four groups accumulate side by side and the per-group epilogue (merge, subtract the
+//               offset, convert, multiply by the group's fp16 scale: the structure of the reference kernels,
+//               boilerplate/kernels/csrc/boilerplate_cpu.cpp:116-124) runs once per four groups, each lane of a
+//               quad doing one of them; the quad's partial results are added with two shuffles at the end of K.
 //
-// One warp owns 16 weight rows of a 128-row tile and walks K in 256-trit superblocks (two scale groups); per
-// 128-trit group the fp32 accumulator is scaled by the group's fp16 scale and added to the row's result, the
-// structure of the reference kernels (boilerplate/kernels/csrc/boilerplate_cpu.cpp:116-124). Work items
-// (expert, row tile) are dealt to CTAs in contiguous ranges so an expert's token rows are staged once per CTA.
+// One consumer warp owns 16 weight rows; a work item is (expert, 64-row half tile) over the whole of K, dealt to
+// CTAs in contiguous, equally sized ranges so an expert's token rows are staged once per CTA and item run.
+// Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all warps leave
+// and the kernel records DST_ERR_TIMEOUT in the status word dst_check_device_status reads.
 //
-// Coverage: TQ2 tiled weights, group 128, K % 256 == 0, fp16 scales, bf16 or fp16 activations, any row count
-// per expert (rows are processed 16 at a time; beyond that the weights are re-read, from L2).
+// Coverage: TQ2 tiled weights, group 128, K % 256 == 0, fp16 scales, bf16 / fp16 / int8 activations, any row
+// count per expert (rows are processed up to 16 at a time; beyond that the weights are streamed again).
 #include "dst_common.cuh"
 
 namespace dst {
 namespace {
 
-constexpr int DC_WARPS = 8;
-constexpr int DC_THREADS = DC_WARPS * 32;
+constexpr int DC_CWARPS = 4;                     // consumer warps, 16 weight rows each
+constexpr int DC_THREADS = (DC_CWARPS + 1) * 32;  // + the producer warp
+constexpr int DC_PART = DC_CWARPS * 16 * 64;      // bytes of one item's share of a slab: 64 rows x 64 B
+constexpr int DC_RING = 6;                        // slots of the slab ring
+constexpr int DC_ZERO = 512;                      // bytes of zeros the lanes without a column read
+constexpr long long DC_WAIT_CYCLES = 4000000000LL;  // ~2 s
+
+__device__ int g_decode_status = 0;
 
 struct DecodeParams {
   const uint8_t* tiled[DST_MAX_TERMS];
   const __half* scale[DST_MAX_TERMS];
   int n_terms;
   const void* x;
-  int act_dtype;
   const float* row_scale;
   const int64_t* offsets;
   void* out;
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S;
-  int xstride;  // bytes between staged token rows: K * 2 + 16 (an odd multiple of 16 bytes: conflict-free B loads)
+  int xstride;  // bytes between staged activation rows: K + 64 (= 64 mod 128: two rows read together hit all banks once)
 };
 
-__device__ __forceinline__ void mma_f16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// ------------------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-
-// Field j (0..7) of a tiled TQ2 word pairs trits 2j (low half) and 2j+1 (high half). Fields 0..4 are used in
-// place (value u * 4^j * 2^-24), fields 5..7 after a shift by 10 (value u * 4^(j-5) * 2^-24).
-__device__ __forceinline__ int field_shift(int j) { return j < 5 ? j : j - 5; }
-
-// Stage the token rows [m0, m0 + mc) of x into shared memory:
-//   xs[m][k] = fp16( x[m][k] * 2^(7 - e_m - 2 f(j)) ),  j = (k % 16) / 2,  e_m = floor(log2(rowmax)) - 7
-//   xsum[m][g] = sum over group g of the values the tensor core will see, undone to x * 2^-e_m
-//   xexp[m] = 2^e_m * row_scale[m]
-template <int MT, typename XT>
-__device__ void stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, float* xsum, float* xexp,
-                             int* xex) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // pass 1, one warp per token row: the row's power of two. Token slots beyond mc are never read (their B
-  // fragments are zero registers), so nothing is written for them.
-  for (int m = warp; m < mc; m += DC_WARPS) {
-    const XT* row = x + (m0 + m) * p.K;
-    float amax = 0.f;
-    for (int k = lane; k < p.K; k += 32) amax = fmaxf(amax, fabsf((float)row[k]));
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    int ex = 0;
-    if (amax > 0.f && isfinite(amax)) {
-      (void)frexpf(amax, &ex);
-      ex -= 8;  // amax * 2^-ex in [128, 256)
-    }
-    if (lane == 0) {
-      xex[m] = ex;
-      xexp[m] = ldexpf(1.f, ex) * (p.row_scale ? p.row_scale[m0 + m] : 1.f);
-    }
-  }
-  __syncthreads();
-  // pass 2, one warp per (token row, 128-trit group): 32 lanes x 4 consecutive k
-  for (int u = warp; u < mc * p.G; u += DC_WARPS) {
-    const int m = u / p.G, g = u - m * p.G;
-    const XT* row = x + (m0 + m) * p.K;
-    __half* dst = reinterpret_cast<__half*>(xs + (size_t)m * p.xstride);
-    const int ex = xex[m];
-    const int k = g * 128 + lane * 4;
-    float part = 0.f;
-    uint32_t packed[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int kk = k + 2 * h;
-      const int f = field_shift((kk & 15) >> 1);
-      const float mul = ldexpf(1.f, 7 - ex - 2 * f), undo = ldexpf(1.f, 2 * f - 7);
-      const __half v0 = __float2half_rn((float)row[kk] * mul), v1 = __float2half_rn((float)row[kk + 1] * mul);
-      part += (__half2float(v0) + __half2float(v1)) * undo;
-      packed[h] = (uint32_t)__half_as_ushort(v0) | ((uint32_t)__half_as_ushort(v1) << 16);
-    }
-    *reinterpret_cast<uint2*>(dst + k) = make_uint2(packed[0], packed[1]);
-    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-    if (lane == 0) xsum[m * p.G + g] = part;
-  }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-
-template <int NB>  // NB = 1: up to 8 token rows per pass, NB = 2: up to 16
-__global__ void __launch_bounds__(DC_THREADS)
-decode_kernel(const DecodeParams p) {
-  extern __shared__ __align__(16) uint8_t dsm[];
-  constexpr int MT = NB * 8;                                        // token rows staged per pass
-  uint8_t* xs = dsm;                                                // MT staged token rows
-  float* xsum = reinterpret_cast<float*>(dsm + (size_t)MT * p.xstride);  // [MT][G]
-  float* xexp = xsum + MT * p.G;                                    // [MT]
-  int* xex = reinterpret_cast<int*>(xexp + MT);                     // [MT] exponent of the row's power of two
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, c = lane & 3;
-
-  // contiguous range of (expert, row tile) items for this CTA
-  const long long items = (long long)p.E * p.NT;
-  const long long per = (items + gridDim.x - 1) / gridDim.x;
-  const long long i0 = (long long)blockIdx.x * per, i1 = i0 + per < items ? i0 + per : items;
-  int staged_e = -1;
-  int64_t staged_m0 = -1;
-
-  for (long long item = i0; item < i1; ++item) {
-    const int e = (int)(item / p.NT), nt = (int)(item - (long long)e * p.NT);
-    int64_t ra, rb;
-    row_range(p.offsets, e, p.T, ra, rb);
-    for (int64_t m0 = ra; m0 < rb; m0 += NB * 8) {
-      const int mc = (int)(rb - m0 < NB * 8 ? rb - m0 : NB * 8);
-      if (staged_e != e || staged_m0 != m0) {
-        __syncthreads();  // everyone is done with the previous rows
-        if (p.act_dtype == DST_ACT_BF16) stage_tokens<MT>(p, static_cast<const __nv_bfloat16*>(p.x), m0, mc, xs, xsum, xexp, xex);
-        else stage_tokens<MT>(p, static_cast<const __half*>(p.x), m0, mc, xs, xsum, xexp, xex);
-        __syncthreads();
-        staged_e = e;
-        staged_m0 = m0;
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > DC_WAIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
       }
-      const int r0 = warp * 16 + g8;  // this lane's rows inside the tile: r0 and r0 + 8 (same swizzle)
-      const int swz = (r0 >> 1) & 3;
-      const int n_lo = nt * 128 + r0, n_hi = n_lo + 8;
-      float y[NB][4];
-#pragma unroll
-      for (int b = 0; b < NB; ++b)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) y[b][i] = 0.f;
+    }
+  }
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// d = a * b + c, u8 x s8 -> s32; ZERO: c = 0
+template <bool ZERO>
+__device__ __forceinline__ void mma_u8s8(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (ZERO)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-      for (int term = 0; term < p.n_terms; ++term) {
-        const uint8_t* wbase = p.tiled[term] + (((int64_t)e * p.NT + nt) * p.S) * 8192 + ((c ^ swz) << 4);
-        const __half* s_lo = p.scale[term] + ((int64_t)e * p.N + (n_lo < p.N ? n_lo : 0)) * p.G;
-        const __half* s_hi = p.scale[term] + ((int64_t)e * p.N + (n_hi < p.N ? n_hi : 0)) * p.G;
-        // words c, 4 + c, 8 + c, 12 + c of rows r0 and r0 + 8, prefetched two superblocks ahead
-        const uint8_t* wl_ptr = wbase + (size_t)r0 * 64;
-        const uint8_t* wh_ptr = wbase + (size_t)(r0 + 8) * 64;
-        const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-        uint4 w_lo = *reinterpret_cast<const uint4*>(wl_ptr), w_hi = *reinterpret_cast<const uint4*>(wh_ptr);
-        uint4 w_lo2 = p.S > 1 ? *reinterpret_cast<const uint4*>(wl_ptr + 8192) : zero4;
-        uint4 w_hi2 = p.S > 1 ? *reinterpret_cast<const uint4*>(wh_ptr + 8192) : zero4;
-        for (int sb = 0; sb < p.S; ++sb) {
-          const uint4 cur_lo = w_lo, cur_hi = w_hi;
-          w_lo = w_lo2;
-          w_hi = w_hi2;
-          if (sb + 2 < p.S) {
-            w_lo2 = *reinterpret_cast<const uint4*>(wl_ptr + (size_t)(sb + 2) * 8192);
-            w_hi2 = *reinterpret_cast<const uint4*>(wh_ptr + (size_t)(sb + 2) * 8192);
-          }
-          const uint32_t wl[4] = {cur_lo.x, cur_lo.y, cur_lo.z, cur_lo.w}, wh[4] = {cur_hi.x, cur_hi.y, cur_hi.z, cur_hi.w};
+// ------------------------------------------------------------------------------------------ work items
+// Item -> (expert, 64-row half tile). Rows of the expert and passes over them (MT token rows per pass).
+struct Item {
+  int e, nt, half;
+  int64_t ra, rb;
+};
+__device__ __forceinline__ Item item_of(const DecodeParams& p, long long item) {
+  Item it;
+  const int nh = p.NT * 2;
+  it.e = (int)(item / nh);
+  const int ht = (int)(item - (long long)it.e * nh);
+  it.nt = ht >> 1;
+  it.half = ht & 1;
+  row_range(p.offsets, it.e, p.T, it.ra, it.rb);
+  return it;
+}
+
+// ------------------------------------------------------------------------------------------ staging
+// Two adjacent activations (k, k + 1) as floats, one 32-bit (16-bit for int8) load.
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+__device__ __forceinline__ float2 load_pair(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+__device__ __forceinline__ float2 load_pair(const int8_t* p) {
+  const uint16_t w = *reinterpret_cast<const uint16_t*>(p);
+  return make_float2((float)(int8_t)(w & 0xff), (float)(int8_t)(w >> 8));
+}
+// Largest magnitude of 8 adjacent 16-bit activations (one 128-bit load); non-finite values come back as +inf or NaN
+__device__ __forceinline__ float amax8(const __nv_bfloat16* p) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  float m = 0.f;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {  // one 128-trit scale group: chunks 2 half, 2 half + 1
-            const int grp = sb * 2 + half;
-            float acc[NB][4];
+  for (int i = 0; i < 4; ++i) {
+    const float a = fabsf(__uint_as_float(w[i] << 16)), b = fabsf(__uint_as_float(w[i] & 0xFFFF0000u));
+    m = (a > m || a != a) ? a : m;  // keeps a NaN once seen
+    m = (b > m || b != b) ? b : m;
+  }
+  return m;
+}
+__device__ __forceinline__ float amax8(const __half* p) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  float m = 0.f;
 #pragma unroll
-            for (int b = 0; b < NB; ++b)
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    const float a = fabsf(f.x), b = fabsf(f.y);
+    m = (a > m || a != a) ? a : m;
+    m = (b > m || b != b) ? b : m;
+  }
+  return m;
+}
+__device__ __forceinline__ float amax8(const int8_t*) { return 0.f; }
+
+// Token rows [m0, m0 + mc) of x -> shared memory, by the consumer warps:
+//   xs[(2 tok + part)][..]  s8, part 0 = hi, 1 = lo of q = rint(x / s_tok); byte order inside a 256-trit superblock:
+//                           position q4 * 64 + c * 16 + (m & 1) * 8 + h * 4 + b holds trit 16 (c + 4 (2 gi + h)) + tw,
+//                           tw = {2 j, 8 + 2 j, 2 j + 1, 9 + 2 j}[b], MMA m = 4 gi + j of the superblock, q4 = m / 2
+//                           (lane c's B registers b0 (h = 0) and b1 (h = 1) of MMAs 2 q4 and 2 q4 + 1 = 16 bytes)
+//   xsum4[tok][g]           4 * sum of q over scale group g (int32); zero for token slots beyond mc
+//   xexp[tok]               s_tok * row_scale / 4 (NaN when the row holds a non-finite value)
+template <int MT, typename XT, typename Sync>
+__device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, int* xsum4, float* xexp,
+                             float* xinv, Sync&& consumer_sync) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr bool IS_I8 = sizeof(XT) == 1;
+  // pass 1: row maxima. Every consumer thread takes 128-bit pieces of every row; the warps' partial maxima meet in
+  // xinv[m * DC_CWARPS + warp] (xinv has room for that: see the shared-memory plan in the kernel)
+  if (!IS_I8) {
+    for (int m = 0; m < mc; ++m) {
+      const XT* row = x + (m0 + m) * p.K;
+      float am = 0.f;
+      for (int i = threadIdx.x * 8; i < p.K; i += DC_CWARPS * 32 * 8) {
+        const float a = amax8(row + i);
+        am = (a > am || a != a) ? a : am;
+      }
+      for (int off = 16; off > 0; off >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, am, off);
+        am = (o > am || o != o) ? o : am;
+      }
+      if (lane == 0) xinv[m * DC_CWARPS + warp] = am;
+    }
+    if (!consumer_sync()) return false;
+  }
+  float my_inv = 0.f;  // of token slot `lane` (lanes below MT)
+  if (lane < MT) {
+    float inv = 0.f, ex = 0.f;
+    if (lane < mc) {
+      const float rs = p.row_scale ? p.row_scale[m0 + lane] : 1.f;
+      if (IS_I8) {
+        inv = 1.f;
+        ex = 0.25f * rs;
+      } else {
+        float amax = 0.f;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) acc[b][i] = 0.f;
+        for (int w = 0; w < DC_CWARPS; ++w) {
+          const float o = xinv[lane * DC_CWARPS + w];
+          amax = (o > amax || o != o) ? o : amax;
+        }
+        if (!(amax <= 3.0e38f)) {
+          ex = __int_as_float(0x7fc00000);  // a non-finite activation: the token's outputs are NaN
+        } else if (amax > 0.f) {
+          inv = 16256.f / amax;
+          ex = 0.25f * (amax / 16256.f) * rs;
+        }
+      }
+    }
+    my_inv = inv;
+    if (warp == 0) xexp[lane] = ex;
+  }
+  // pass 2: one warp per (token slot, 128-trit group): lane = position / 4 inside the group's 128 bytes
+  const int c = (lane >> 2) & 3, j = ((lane >> 4) & 1) * 2 + ((lane >> 1) & 1), h = lane & 1;
+  for (int u = warp; u < MT * p.G; u += DC_CWARPS) {
+    const int m = u / p.G, g = u - m * p.G;
+    const float inv = __shfl_sync(0xffffffffu, my_inv, m);
+    int sum = 0;
+    if (m < mc) {
+      const XT* row = x + (m0 + m) * p.K + (g * 128 + 16 * c + 64 * h + 2 * j);
+      const float2 f0 = load_pair(row), f1 = load_pair(row + 8);  // trits (2j, 2j + 1) and (8 + 2j, 9 + 2j) of the word
+      const float v[4] = {f0.x, f1.x, f0.y, f1.y};                   // byte order b = 0..3
+      uint32_t whi = 0, wlo = 0;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-              const int ch = half * 2 + cc;
-              const uint32_t a_lo = wl[ch], a_hi = wh[ch], a_lo2 = a_lo >> 10, a_hi2 = a_hi >> 10;
-              // this lane's 16 k of the chunk: k = 256 sb + 64 ch + 16 c .. + 15, as 8 fp16 pairs per token
-              const int koff = (sb * 256 + ch * 64 + c * 16) * 2;
-              uint4 q[NB][2];
-#pragma unroll
-              for (int b = 0; b < NB; ++b) {
-                // token columns that do not exist are zero registers: no shared-memory traffic for them
-                if (b * 8 + g8 < mc) {
-                  const uint8_t* xr = xs + (size_t)(b * 8 + g8) * p.xstride + koff;
-                  q[b][0] = *reinterpret_cast<const uint4*>(xr);
-                  q[b][1] = *reinterpret_cast<const uint4*>(xr + 16);
-                } else {
-                  q[b][0] = zero4;
-                  q[b][1] = zero4;
-                }
-              }
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                // pairs jj (in place) and jj + 4 (jj = 0 in place at field 4, else from the shifted word)
-                const uint32_t m_a = 0x00030003u << (2 * jj);
-                const uint32_t a0 = a_lo & m_a, a1 = a_hi & m_a;
-                uint32_t a2, a3;
-                if (jj == 0) {
-                  a2 = a_lo & 0x03000300u;
-                  a3 = a_hi & 0x03000300u;
-                } else {
-                  const uint32_t m_b = 0x00030003u << (2 * (jj - 1));
-                  a2 = a_lo2 & m_b;
-                  a3 = a_hi2 & m_b;
-                }
-#pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                  const uint32_t b0 = jj == 0 ? q[b][0].x : jj == 1 ? q[b][0].y : jj == 2 ? q[b][0].z : q[b][0].w;
-                  const uint32_t b1 = jj == 0 ? q[b][1].x : jj == 1 ? q[b][1].y : jj == 2 ? q[b][1].z : q[b][1].w;
-                  mma_f16(acc[b], a0, a1, a2, a3, b0, b1);
-                }
-              }
+      for (int b = 0; b < 4; ++b) {
+        int q;
+        if (IS_I8) {
+          q = (int)v[b];
+        } else {
+          q = (int)fminf(fmaxf(rintf(v[b] * inv), -16256.f), 16256.f);  // NaN -> 0; such a row's result is NaN through xexp
+        }
+        sum += q;
+        const int hi = IS_I8 ? 0 : (q + 64) >> 7;
+        const int lo = q - (hi << 7);
+        whi |= (uint32_t)(hi & 0xff) << (8 * b);
+        wlo |= (uint32_t)(lo & 0xff) << (8 * b);
+      }
+      // lane bits: (q4 & 1) c1 c0 (m & 1) h -> byte position (g & 1) * 128 + (q4 & 1) * 64 + c * 16 + (m & 1) * 8 + h * 4
+      const int pos = (g >> 1) * 256 + (g & 1) * 128 + lane * 4;
+      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m) * p.xstride + pos) = whi;
+      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m + 1) * p.xstride + pos) = wlo;
+    }
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) xsum4[m * p.G + g] = 4 * sum;
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
+// GS = scale groups that share an MMA's columns (4: one token row per pass, 2: two, 1: four per column block);
+// NB = column blocks (GS == 1 only): 4 NB token rows per pass.
+template <int GS, int NB, typename XT>
+__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? 6 : (NB == 2 ? 4 : 2))
+decode_kernel(const DecodeParams p) {
+  constexpr int MT = 4 * NB / GS;  // token rows per pass
+  constexpr int TPB = 4 / GS;      // token rows per column block
+  extern __shared__ __align__(128) uint8_t dsm[];
+  uint8_t* ring = dsm;                                           // DC_RING x DC_PART
+  uint8_t* zero = ring + DC_RING * DC_PART;                      // DC_ZERO
+  uint8_t* xs = zero + DC_ZERO;                                  // 2 MT staged rows
+  int* xsum4 = reinterpret_cast<int*>(xs + (size_t)2 * MT * p.xstride);  // [MT][G]
+  float* xexp = reinterpret_cast<float*>(xsum4 + MT * p.G);      // [MT]
+  float* xinv = xexp + MT;                                       // [MT][DC_CWARPS] partial row maxima
+  __shared__ uint64_t bar_full[DC_RING], bar_empty[DC_RING], bar_stage;
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < DC_RING; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);           // the producer's expect_tx arrive
+      mbar_init(smem_u32(&bar_empty[s]), DC_CWARPS);  // one arrive per consumer warp
+    }
+    mbar_init(smem_u32(&bar_stage), DC_CWARPS);       // the consumer warps' own barrier (bounded, unlike bar.sync)
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < DC_ZERO / 4; i += DC_THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
+  __syncthreads();
+
+  // contiguous, equally sized (+-1) range of items for this CTA
+  const long long items = (long long)p.E * p.NT * 2;
+  const long long i0 = items * blockIdx.x / gridDim.x, i1 = items * (blockIdx.x + 1) / gridDim.x;
+
+  if (warp == DC_CWARPS) {
+    // ------------------------------------------------------------------ producer: packed slabs -> ring
+    if (lane == 0) {
+      uint32_t slot = 0, ph = 0;
+      bool ok = true;
+      for (long long item = i0; ok && item < i1; ++item) {
+        const Item it = item_of(p, item);
+        const int passes = (int)((it.rb - it.ra + MT - 1) / MT);
+        const int64_t off0 = (((int64_t)it.e * p.NT + it.nt) * p.S) * 8192 + it.half * DC_PART;
+        for (int ps = 0; ok && ps < passes; ++ps)
+          for (int term = 0; ok && term < p.n_terms; ++term)
+            for (int sb = 0; sb < p.S; ++sb) {
+              if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) { ok = false; break; }
+              const uint32_t full = smem_u32(&bar_full[slot]);
+              mbar_arrive_expect_tx(full, DC_PART);
+              bulk_load(smem_u32(ring + slot * DC_PART), p.tiled[term] + off0 + (int64_t)sb * 8192, DC_PART, full);
+              if (++slot == DC_RING) { slot = 0; ph ^= 1u; }
             }
-            // group done: y += scale[row][grp] * (2^17 acc - sum_k x); C fragment = (row r0 | r0 + 8) x (token 2c | 2c + 1)
-            const float sl = grp < p.G ? __half2float(s_lo[grp]) : 0.f, sh = grp < p.G ? __half2float(s_hi[grp]) : 0.f;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int g8 = lane >> 2, c = lane & 3;
+    const int swz = (g8 >> 1) & 3;
+    const uint32_t a_off = (uint32_t)((warp * 16 + g8) * 64 + ((c ^ swz) << 4));  // this lane's unit of row g8; row g8 + 8: + 512
+    const uint32_t ring_a = smem_u32(ring), zero_a = smem_u32(zero), xs_a = smem_u32(xs);
+    // B column of this lane: pair g8 / 2, part g8 & 1; C columns of this lane: pair c
+    const int col_pair = g8 >> 1, col_part = g8 & 1;
+    const int tok_c = c / GS, slot_c = c % GS;  // (+ b * TPB) the token and the group slot of this lane's C columns
+    uint32_t slot = 0, ph = 0, stage_ph = 0;
+    bool ok = true;
+    int staged_e = -1;
+    int64_t staged_m0 = -1;
+    auto consumer_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_stage));
+      const bool r = mbar_wait(smem_u32(&bar_stage), stage_ph, abort_flag);
+      stage_ph ^= 1u;
+      __syncwarp();
+      return r;
+    };
+
+    for (long long item = i0; ok && item < i1; ++item) {
+      const Item it = item_of(p, item);
+      const int n_lo = it.nt * 128 + it.half * 64 + warp * 16 + g8, n_hi = n_lo + 8;
+      for (int64_t m0 = it.ra; ok && m0 < it.rb; m0 += MT) {
+        const int mc = (int)(it.rb - m0 < MT ? it.rb - m0 : MT);
+        if (staged_e != it.e || staged_m0 != m0) {
+          // every consumer is done with the previous rows; then stage; then everyone sees the new ones
+          ok = consumer_sync() && stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, xsum4, xexp, xinv, consumer_sync) &&
+               consumer_sync();
+          if (!ok) break;
+          staged_e = it.e;
+          staged_m0 = m0;
+        }
+        // B pointers: for block b and phase s (= group % GS) the lane reads its column's staged row when the column's
+        // pair belongs to that phase and its token exists, else the zeros
+        uint32_t bbase[NB][GS], bstep[NB][GS];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+          for (int s = 0; s < GS; ++s) {
+            const int tok = b * TPB + col_pair / GS;
+            const bool act = (col_pair % GS) == s && tok < mc;
+            bbase[b][s] = act ? xs_a + (uint32_t)(2 * tok + col_part) * (uint32_t)p.xstride + (uint32_t)c * 16u : zero_a;
+            bstep[b][s] = act ? 256u : 0u;
+          }
+        float y[NB][2];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) y[b][0] = y[b][1] = 0.f;
+
+        for (int term = 0; ok && term < p.n_terms; ++term) {
+          const __half* s_lo = p.scale[term] + ((int64_t)it.e * p.N + (n_lo < p.N ? n_lo : 0)) * p.G;
+          const __half* s_hi = p.scale[term] + ((int64_t)it.e * p.N + (n_hi < p.N ? n_hi : 0)) * p.G;
+          int accA[NB][4], accB[NB][4];
+#pragma unroll
+          for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) accA[b][i] = accB[b][i] = 0;
+          // scales of the lane's group of the next epilogue, requested a block of groups ahead
+          auto scale_at = [&](const __half* s, int grp) { return grp < p.G ? __half2float(s[grp]) : 0.f; };
+          float sl_n = scale_at(s_lo, slot_c), sh_n = scale_at(s_hi, slot_c);
+          // epilogue of the block of GS groups whose first group is g_first: this lane's group is g_first + slot_c
+          auto epilogue = [&](int g_first) {
+            const int g_mine = g_first + slot_c;
+            const float sl = sl_n, sh = sh_n;
+            sl_n = scale_at(s_lo, g_mine + GS);
+            sh_n = scale_at(s_hi, g_mine + GS);
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-              const float x0 = xsum[(b * 8 + 2 * c) * p.G + grp], x1 = xsum[(b * 8 + 2 * c + 1) * p.G + grp];
-              y[b][0] = fmaf(sl, fmaf(acc[b][0], 131072.f, -x0), y[b][0]);
-              y[b][1] = fmaf(sl, fmaf(acc[b][1], 131072.f, -x1), y[b][1]);
-              y[b][2] = fmaf(sh, fmaf(acc[b][2], 131072.f, -x0), y[b][2]);
-              y[b][3] = fmaf(sh, fmaf(acc[b][3], 131072.f, -x1), y[b][3]);
+              const int xs4 = g_mine < p.G ? xsum4[(b * TPB + tok_c) * p.G + g_mine] : 0;
+              // 4 * sum_k u_k q_k = 128 * (4 A_hi + B_hi) + (4 A_lo + B_lo); minus 4 * sum_k q_k
+              const int v_lo = ((((accA[b][0] << 2) + accB[b][0]) << 7) + ((accA[b][1] << 2) + accB[b][1])) - xs4;
+              const int v_hi = ((((accA[b][2] << 2) + accB[b][2]) << 7) + ((accA[b][3] << 2) + accB[b][3])) - xs4;
+              y[b][0] = fmaf(sl, (float)v_lo, y[b][0]);
+              y[b][1] = fmaf(sh, (float)v_hi, y[b][1]);
+            }
+          };
+
+          // superblocks two at a time, so that the phase of every group (group % GS) is a compile-time value
+          for (int sb0 = 0; ok && sb0 < p.S; sb0 += 2) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int sb = sb0 + u;
+              if (sb >= p.S || !ok) continue;
+              if (!mbar_wait(smem_u32(&bar_full[slot]), ph, abort_flag)) { ok = false; continue; }
+              const uint32_t sa = ring_a + slot * DC_PART + a_off;
+              const uint4 w_lo = lds128(sa), w_hi = lds128(sa + 512);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
+              if (++slot == DC_RING) { slot = 0; ph ^= 1u; }
+#pragma unroll
+              for (int gi = 0; gi < 2; ++gi) {
+                constexpr uint32_t M1 = 0x03030303u, M4 = 0x0c0c0c0cu;
+                const int phase = (u * 2 + gi) % GS;   // group % GS
+                const bool fresh = phase == 0;         // first group of an epilogue block: the accumulators restart
+                const uint32_t l0 = gi ? w_lo.z : w_lo.x, l1 = gi ? w_lo.w : w_lo.y, h0 = gi ? w_hi.z : w_hi.x, h1 = gi ? w_hi.w : w_hi.y;
+                const uint32_t l0s = l0 >> 4, l1s = l1 >> 4, h0s = h0 >> 4, h1s = h1 >> 4;
+                const uint32_t a[4][4] = {{l0 & M1, h0 & M1, l1 & M1, h1 & M1},
+                                          {l0 & M4, h0 & M4, l1 & M4, h1 & M4},
+                                          {l0s & M1, h0s & M1, l1s & M1, h1s & M1},
+                                          {l0s & M4, h0s & M4, l1s & M4, h1s & M4}};
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                  const uint32_t ba = bbase[b][phase] + (uint32_t)sb * bstep[b][phase] + (uint32_t)gi * 128u;
+                  const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
+                  if (fresh) {
+                    mma_u8s8<true>(accA[b], a[0][0], a[0][1], a[0][2], a[0][3], q0.x, q0.y);
+                    mma_u8s8<true>(accB[b], a[1][0], a[1][1], a[1][2], a[1][3], q0.z, q0.w);
+                  } else {
+                    mma_u8s8<false>(accA[b], a[0][0], a[0][1], a[0][2], a[0][3], q0.x, q0.y);
+                    mma_u8s8<false>(accB[b], a[1][0], a[1][1], a[1][2], a[1][3], q0.z, q0.w);
+                  }
+                  mma_u8s8<false>(accA[b], a[2][0], a[2][1], a[2][2], a[2][3], q1.x, q1.y);
+                  mma_u8s8<false>(accB[b], a[3][0], a[3][1], a[3][2], a[3][3], q1.z, q1.w);
+                }
+                if (phase == GS - 1) epilogue(sb * 2 + gi - (GS - 1));
+              }
             }
           }
+          // K of an odd number of superblocks with four groups per block: the last block holds two groups
+          if (GS == 4 && ok && (p.S & 1)) epilogue(p.G - 2);
         }
-      }
-      // store: rows n_lo / n_hi, tokens m0 + b * 8 + 2c (+1)
+        if (!ok) break;
+        // the quad's lanes hold the partial sums of their group slots
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
+        for (int b = 0; b < NB; ++b)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int tok = b * 8 + 2 * c + (i & 1);
-          const int n = i < 2 ? n_lo : n_hi;
-          if (tok < mc && n < p.N) {
-            const float v = y[b][i] * xexp[tok];
-            const int64_t o = (m0 + tok) * p.N + n;
-            if (p.out_dtype == DST_OUT_F32) {
-              float* out = static_cast<float*>(p.out);
-              out[o] = p.accumulate ? out[o] + v : v;
-            } else if (p.out_dtype == DST_OUT_BF16) {
-              static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-            } else {
-              static_cast<__half*>(p.out)[o] = __float2half_rn(v);
+          for (int i = 0; i < 2; ++i) {
+            if (GS >= 2) y[b][i] += __shfl_xor_sync(0xffffffffu, y[b][i], 1);
+            if (GS == 4) y[b][i] += __shfl_xor_sync(0xffffffffu, y[b][i], 2);
+          }
+        if (slot_c == 0) {
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            const int tok = b * TPB + tok_c;
+            if (tok < mc) {
+              const float f = xexp[tok];
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int n = i ? n_hi : n_lo;
+                if (n < p.N) {
+                  const float v = y[b][i] * f;
+                  const int64_t o = (m0 + tok) * p.N + n;
+                  if (p.out_dtype == DST_OUT_F32) {
+                    float* out = static_cast<float*>(p.out);
+                    out[o] = p.accumulate ? out[o] + v : v;
+                  } else if (p.out_dtype == DST_OUT_BF16) {
+                    static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+                  } else {
+                    static_cast<__half*>(p.out)[o] = __float2half_rn(v);
+                  }
+                }
+              }
             }
           }
         }
       }
     }
   }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // give bulk copies still in flight time to land before the CTA's shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_s) atomicExch(&g_decode_status, DST_ERR_TIMEOUT);
+}
+
+template <int GS, int NB, typename XT>
+int launch_one(const DecodeParams& p, int sms, cudaStream_t stream) {
+  constexpr int MT = 4 * NB / GS;
+  const size_t smem = (size_t)DC_RING * DC_PART + DC_ZERO + (size_t)2 * MT * p.xstride + (size_t)MT * p.G * 4 + (size_t)MT * 4 * (1 + DC_CWARPS);
+  if (smem > 220 * 1024) return DST_ERR_UNSUPPORTED;
+  auto kernel = decode_kernel<GS, NB, XT>;
+  DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  DST_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, DC_THREADS, smem));
+  if (per_sm < 1) return DST_ERR_UNSUPPORTED;
+  const long long items = (long long)p.E * p.NT * 2;
+  const long long want = (long long)sms * per_sm;
+  const int grid = (int)(items < want ? items : want);
+  kernel<<<grid, DC_THREADS, smem, stream>>>(p);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+template <typename XT>
+int launch_rows(const DecodeParams& p, int64_t rows_hint, int sms, cudaStream_t stream) {
+  if (rows_hint <= 1) return launch_one<4, 1, XT>(p, sms, stream);
+  if (rows_hint <= 2) return launch_one<2, 1, XT>(p, sms, stream);
+  if (rows_hint <= 4) return launch_one<1, 1, XT>(p, sms, stream);
+  if (rows_hint <= 8) return launch_one<1, 2, XT>(p, sms, stream);
+  const int rc = launch_one<1, 4, XT>(p, sms, stream);
+  return rc == DST_ERR_UNSUPPORTED ? launch_one<1, 2, XT>(p, sms, stream) : rc;  // 16 staged rows of a long K may not fit
 }
 
 }  // namespace
@@ -257,8 +520,9 @@ decode_kernel(const DecodeParams p) {
 bool decode_supports(const GemmArgs& a) {
   if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
   return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 256 == 0 &&
-         a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16) &&
-         (size_t)16 * (a.K * 2 + 16) + (size_t)16 * (a.G + 2) * 4 <= 200 * 1024 && a.T < (int64_t(1) << 31);
+         a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16 || a.act_dtype == DST_ACT_I8) &&
+         (size_t)DC_RING * DC_PART + DC_ZERO + (size_t)16 * (a.K + 64) + (size_t)8 * (a.G + 8) * 4 <= 220 * 1024 &&
+         a.T < (int64_t(1) << 31);
 }
 
 int launch_decode(const GemmArgs& a, cudaStream_t stream) {
@@ -268,6 +532,7 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   for (int i = 0; i < a.terms.n; ++i)
     if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 1) != 0)
       return DST_ERR_ALIGNMENT;
+  if ((reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return DST_ERR_ALIGNMENT;  // rows are read with 128-bit loads
   DecodeParams p;
   for (int i = 0; i < DST_MAX_TERMS; ++i) {
     p.tiled[i] = i < a.terms.n ? a.terms.packed[i] : nullptr;
@@ -275,7 +540,6 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   }
   p.n_terms = a.terms.n;
   p.x = a.x;
-  p.act_dtype = a.act_dtype;
   p.row_scale = a.row_scale;
   p.offsets = a.offsets;
   p.out = a.out;
@@ -288,28 +552,26 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   p.G = (int)a.G;
   p.NT = (int)cdiv64(a.N, 128);
   p.S = (int)tiled_superblocks(a.fmt, a.K);
-  p.xstride = (int)(a.K * 2 + 16);
-  // up to 8 rows per expert (known on the host, or guessed from the mean) -> one token block per pass
+  p.xstride = (int)(a.K + 64);
+  // rows per expert: known on the host, or guessed from the mean (an expert with more rows takes several passes)
   const int64_t rows_hint = a.max_rows >= 0 ? a.max_rows : cdiv64(a.T, a.E);
   int dev = 0, sms = 148;
   DST_CUDA_TRY(cudaGetDevice(&dev));
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const long long items = (long long)p.E * p.NT;
-  const int nb = rows_hint <= 8 ? 1 : 2;
-  const size_t smem = (size_t)nb * 8 * p.xstride + (size_t)nb * 8 * (p.G + 2) * 4;
-  // as many CTAs per SM as the staged token rows allow (up to 3: 24 warps keep enough loads in flight)
-  int per_sm = (int)((220 * 1024) / (smem + 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
-  const long long want = (long long)sms * per_sm;
-  const int grid = (int)(items < want ? items : want);
-  if (nb == 1) {
-    DST_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    decode_kernel<1><<<grid, DC_THREADS, smem, stream>>>(p);
-  } else {
-    DST_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    decode_kernel<2><<<grid, DC_THREADS, smem, stream>>>(p);
+  if (a.act_dtype == DST_ACT_BF16) return launch_rows<__nv_bfloat16>(p, rows_hint, sms, stream);
+  if (a.act_dtype == DST_ACT_F16) return launch_rows<__half>(p, rows_hint, sms, stream);
+  return launch_rows<int8_t>(p, rows_hint, sms, stream);
+}
+
+// Reads and clears the decode kernel's status word (DST_OK or DST_ERR_TIMEOUT in *status).
+int decode_take_status(int* status) {
+  int st = 0;
+  DST_CUDA_TRY(cudaMemcpyFromSymbol(&st, g_decode_status, sizeof(int)));
+  if (st != 0) {
+    const int zero = 0;
+    DST_CUDA_TRY(cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)));
   }
-  DST_CUDA_TRY(cudaGetLastError());
+  *status = st;
   return DST_OK;
 }
 

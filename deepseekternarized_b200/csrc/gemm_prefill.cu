@@ -964,9 +964,11 @@ extern "C" int dst_check_device_status(dst_stream_t stream) {
   if (st != 0) {
     const int zero = 0;
     DST_CUDA_TRY(cudaMemcpyToSymbol(dst::g_device_status, &zero, sizeof(int)));
-    return DST_ERR_TIMEOUT;
   }
-  return DST_OK;
+  int st_decode = 0;  // the decode kernel keeps a status word of its own
+  const int rc = dst::decode_take_status(&st_decode);
+  if (rc != DST_OK) return rc;
+  return (st != 0 || st_decode != 0) ? DST_ERR_TIMEOUT : DST_OK;
 }
 
 // ------------------------------------------------------------------------------------------ no-allocation entry

@@ -7,62 +7,91 @@ namespace dst {
 namespace {
 
 // ------------------------------------------------------------------------------------------ router
-// One warp per token. Scores are the fp32 softmax of the E logits; the k largest are picked by k
-// rounds of warp arg-max (equal scores: lower expert id wins), then renormalised.
+// One warp per token. score = f(logit / gate_temp) with f = softmax over the E logits, sigmoid, or
+// sqrt(softplus) (boilerplate/engine/model.py:389-399); the k experts are picked by k rounds of warp arg-max over
+// score + bias (equal keys: lower expert id wins), the weights are the UNBIASED scores of the picked experts,
+// optionally renormalised, times route_scale (model.py:400-405).
+// A NaN key ranks above every number, as in torch.topk, and every round picks among the experts not picked yet,
+// so the k ids of a token are always distinct and inside [0, E) whatever the logits hold (all-NaN and all -inf
+// rows included: their weights are NaN, their ids 0..k-1).
 constexpr int ROUTE_MAX_PER_LANE = 32;  // E <= 1024
 
-__global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E, int top_k, int renorm, float route_scale,
-                             float* __restrict__ weights, int32_t* __restrict__ ids) {
+// a ranks above b: NaN above everything, NaNs equal among themselves
+__device__ __forceinline__ bool route_above(float a, float b) {
+  const bool an = a != a, bn = b != b;
+  return an ? !bn : (!bn && a > b);
+}
+
+__global__ void route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E, int top_k,
+                             int score_func, float inv_temp, int renorm, float route_scale, float* __restrict__ weights,
+                             int32_t* __restrict__ ids) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const float* row = logits + t * E;
-  float v[ROUTE_MAX_PER_LANE];
+  float v[ROUTE_MAX_PER_LANE];  // unbiased scores
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
     const int e = j * 32 + lane;
-    v[j] = e < E ? row[e] : -INFINITY;
+    v[j] = e < E ? row[e] * inv_temp : -INFINITY;
     mx = fmaxf(mx, v[j]);
   }
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  float sum = 0.f;
+  if (score_func == DST_SCORE_SOFTMAX) {
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
-    const int e = j * 32 + lane;
-    v[j] = e < E ? expf(v[j] - mx) : -1.f;  // -1 marks "not a candidate"
-    if (e < E) sum += v[j];
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+      const int e = j * 32 + lane;
+      v[j] = expf(v[j] - mx);
+      if (e < E) sum += v[j];
+    }
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) v[j] *= inv;
+  } else if (score_func == DST_SCORE_SIGMOID) {
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) v[j] = 1.f / (1.f + expf(-v[j]));
+  } else {  // sqrt(softplus), softplus(x) = x above 20 as torch computes it
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) v[j] = sqrtf(v[j] > 20.f ? v[j] : log1pf(expf(v[j])));
   }
-  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-  const float inv = 1.f / sum;
+  uint32_t taken = 0;  // bit j: expert j * 32 + lane has been picked
   float wsel[8];
   int isel[8];
   float wsum = 0.f;
   for (int r = 0; r < top_k; ++r) {
-    float best = -1.f;
-    int bi = 0x7fffffff;
+    float best = 0.f, best_w = 0.f;
+    int bi = 0x7fffffff;  // no candidate in this lane yet
 #pragma unroll
     for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
       const int e = j * 32 + lane;
-      if (v[j] > best) {  // ascending e within a lane: first maximum is the lowest id
-        best = v[j];
-        bi = e;
+      if (e < E && !((taken >> j) & 1u)) {
+        const float key = bias ? v[j] + bias[e] : v[j];
+        if (bi == 0x7fffffff || route_above(key, best)) {  // ascending e within a lane: the first maximum is the lowest id
+          best = key;
+          best_w = v[j];
+          bi = e;
+        }
       }
     }
     for (int off = 16; off > 0; off >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const float ow = __shfl_xor_sync(0xffffffffu, best_w, off);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      if (ob > best || (ob == best && oi < bi)) {
+      const bool take = oi != 0x7fffffff && (bi == 0x7fffffff || route_above(ob, best) || (!route_above(best, ob) && oi < bi));
+      if (take) {
         best = ob;
+        best_w = ow;
         bi = oi;
       }
     }
-#pragma unroll
-    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
-      if (j * 32 + lane == bi) v[j] = -1.f;
-    wsel[r] = best * inv;  // the softmax score
+    // top_k <= E, so some lane always had a candidate: 0 <= bi < E
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    wsel[r] = best_w;
     isel[r] = bi;
-    wsum += wsel[r];
+    wsum += best_w;
   }
   if (lane == 0) {
     const float d = (renorm && top_k > 1) ? 1.f / (wsum + 1e-20f) : 1.f;
@@ -75,7 +104,8 @@ __global__ void route_kernel(const float* __restrict__ logits, int64_t T, int E,
 
 // ------------------------------------------------------------------------------------ routing sort
 // Stable counting sort in three steps over chunks of SORT_CHUNK consecutive ids, one warp per chunk:
-//   1. per-chunk histogram               hist[c][e]
+//   1. per-chunk histogram               hist[c][e]; also presets order[] to 0, so the tail that dropped ids leave
+//                                         unwritten holds a valid row index instead of whatever was in memory
 //   2. one block: offsets[e] and the start of every (chunk, expert) run, in place in hist
 //   3. per chunk, in input order: warp match on the expert id gives each entry its rank among equal
 //      ids of the same 32-entry step; a per-expert cursor in shared memory carries across steps.
@@ -83,7 +113,7 @@ constexpr int SORT_CHUNK = 1024;
 
 template <typename IdT>
 __global__ void sort_hist_kernel(const IdT* __restrict__ ids, int64_t n, int E, int32_t* __restrict__ hist,
-                                 int32_t* __restrict__ bad_count) {
+                                 int32_t* __restrict__ bad_count, int64_t* __restrict__ order) {
   extern __shared__ int32_t sh[];
   for (int e = threadIdx.x; e < E; e += 32) sh[e] = 0;
   __syncwarp();
@@ -95,6 +125,7 @@ __global__ void sort_hist_kernel(const IdT* __restrict__ ids, int64_t n, int E, 
       const int64_t e = (int64_t)ids[i];
       if (e >= 0 && e < E) atomicAdd(&sh[e], 1);
       else ++bad;
+      order[i] = 0;
     }
   }
   __syncwarp();
@@ -162,12 +193,16 @@ __global__ void sort_place_kernel(const IdT* __restrict__ ids, int64_t n, int E,
 }
 
 // ------------------------------------------------------------------------------------------ gather
+// Every kernel that follows `order` clamps the entry to [0, n): an order array that was not produced by the routing
+// sort (or one whose tail belongs to dropped ids) can then make a row wrong, but cannot make an access leave the buffers.
+__device__ __forceinline__ int64_t clamp_slot(int64_t f, int64_t n) { return f < 0 ? 0 : (f >= n ? n - 1 : f); }
+
 // dst[p, :] = src[order[p] / top_k, :], 16-byte vectors where the row length allows.
 __global__ void gather_rows_kernel(const uint16_t* __restrict__ src, const int64_t* __restrict__ order, int64_t n_rows,
                                    int64_t K, int top_k, uint16_t* __restrict__ dst) {
   const int64_t p = blockIdx.x;
   if (p >= n_rows) return;
-  const int64_t t = order[p] / top_k;
+  const int64_t t = clamp_slot(order[p], n_rows) / top_k;
   const uint16_t* s = src + t * K;
   uint16_t* d = dst + p * K;
   if ((K & 7) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
@@ -186,7 +221,7 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, const float*
                               __nv_bfloat16* __restrict__ h) {
   const int64_t p = blockIdx.x;
   if (p >= n_rows) return;
-  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const float w = route_weights ? route_weights[order ? clamp_slot(order[p], n_rows) : p] : 1.f;
   const __nv_bfloat16* g = gu + p * 2 * inter;
   const __nv_bfloat16* u = g + inter;
   for (int64_t i = threadIdx.x; i < inter; i += blockDim.x) {
@@ -266,7 +301,7 @@ gather_rows_norm_vec_kernel(const __nv_bfloat16* __restrict__ src, const int64_t
                             __half* __restrict__ dst, float* __restrict__ factor) {
   __shared__ float red[32];
   const int64_t p = blockIdx.x;
-  const int64_t t = order ? order[p] / top_k : p;
+  const int64_t t = order ? clamp_slot(order[p], (int64_t)gridDim.x) / top_k : p;
   const uint4* s = reinterpret_cast<const uint4*>(src + t * K);
   const int chunks = (int)(K >> 3);
   float v[J][8];
@@ -297,7 +332,7 @@ swiglu_norm_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __rest
                        int64_t inter, float limit, __half* __restrict__ h, float* __restrict__ factor) {
   __shared__ float red[32];
   const int64_t p = blockIdx.x;
-  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const float w = route_weights ? route_weights[order ? clamp_slot(order[p], (int64_t)gridDim.x) : p] : 1.f;
   const uint4* g = reinterpret_cast<const uint4*>(gu + p * 2 * inter);
   const uint4* u = reinterpret_cast<const uint4*>(gu + p * 2 * inter + inter);
   const int chunks = (int)(inter >> 3);
@@ -341,7 +376,7 @@ __global__ void gather_rows_norm_kernel(const __nv_bfloat16* __restrict__ src, c
                                         int top_k, __half* __restrict__ dst, float* __restrict__ factor) {
   __shared__ float red[32];
   const int64_t p = blockIdx.x;
-  const int64_t t = order ? order[p] / top_k : p;
+  const int64_t t = order ? clamp_slot(order[p], (int64_t)gridDim.x) / top_k : p;
   const __nv_bfloat16* s = src + t * K;
   float amax = 0.f;
   for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(s[k])));
@@ -357,7 +392,7 @@ __global__ void swiglu_norm_kernel(const __nv_bfloat16* __restrict__ gu, const f
                                    float* __restrict__ factor) {
   __shared__ float red[32];
   const int64_t p = blockIdx.x;
-  const float w = route_weights ? route_weights[order ? order[p] : p] : 1.f;
+  const float w = route_weights ? route_weights[order ? clamp_slot(order[p], (int64_t)gridDim.x) : p] : 1.f;
   const __nv_bfloat16* g = gu + p * 2 * inter;
   const __nv_bfloat16* u = g + inter;
   float amax = 0.f;
@@ -385,6 +420,8 @@ __global__ void swiglu_norm_kernel(const __nv_bfloat16* __restrict__ gu, const f
 }
 
 // ----------------------------------------------------------------------------------------- combine
+// inv[] is preset to -1 by the entry points; a (token, slot) whose expert id was dropped by the routing sort keeps
+// -1 and contributes nothing.
 __global__ void invert_order_kernel(const int64_t* __restrict__ order, int64_t n, int64_t* __restrict__ inv) {
   const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (p < n) {
@@ -393,78 +430,68 @@ __global__ void invert_order_kernel(const int64_t* __restrict__ order, int64_t n
   }
 }
 
-// One block per token: its top_k rows of `down`, visited in increasing expert id, summed in fp32.
+// A token's (position, expert id) pairs in increasing expert id (the ids of one token are distinct); positions that
+// are negative (dropped ids) or beyond the n_pos rows of `down` are marked -1.
+__device__ __forceinline__ void token_slots(const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int64_t t, int top_k,
+                                            int64_t n_pos, int64_t* pos, int* eid) {
+  for (int s = 0; s < top_k; ++s) {
+    const int64_t q = inv[t * top_k + s];
+    pos[s] = (q >= 0 && q < n_pos) ? q : -1;
+    eid[s] = ids[t * top_k + s];
+  }
+  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id
+    const int e = eid[i];
+    const int64_t q = pos[i];
+    int j = i - 1;
+    while (j >= 0 && eid[j] > e) {
+      eid[j + 1] = eid[j];
+      pos[j + 1] = pos[j];
+      --j;
+    }
+    eid[j + 1] = e;
+    pos[j + 1] = q;
+  }
+}
+
+// One block per token: its top_k rows of `down`, visited in increasing expert id, summed in fp32; then the optional
+// row of `add` (the shared expert's bf16 output, boilerplate/engine/model.py:421) in fp32, then the cast.
 __global__ void combine_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv,
-                               const int32_t* __restrict__ ids, int top_k, int64_t hidden,
+                               const int32_t* __restrict__ ids, int top_k, int64_t hidden, const __nv_bfloat16* __restrict__ add,
                                __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
   int64_t pos[8];
   int eid[8];
-  for (int s = 0; s < top_k; ++s) {
-    pos[s] = inv[t * top_k + s];
-    eid[s] = ids[t * top_k + s];
-  }
-  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
-    const int e = eid[i];
-    const int64_t p = pos[i];
-    int j = i - 1;
-    while (j >= 0 && eid[j] > e) {
-      eid[j + 1] = eid[j];
-      pos[j + 1] = pos[j];
-      --j;
-    }
-    eid[j + 1] = e;
-    pos[j + 1] = p;
-  }
-  for (int64_t c = threadIdx.x * 2; c < hidden; c += blockDim.x * 2) {
-    float a0 = 0.f, a1 = 0.f;
-    if (c + 1 < hidden && (hidden & 1) == 0) {
-      for (int s = 0; s < top_k; ++s) {
-        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(down + pos[s] * hidden + c);
-        a0 += __bfloat162float(v.x);
-        a1 += __bfloat162float(v.y);
-      }
-      *reinterpret_cast<__nv_bfloat162*>(y + t * hidden + c) = __floats2bfloat162_rn(a0, a1);
-    } else {
-      for (int cc = 0; cc < 2 && c + cc < hidden; ++cc) {
-        float acc = 0.f;
-        for (int s = 0; s < top_k; ++s) acc += __bfloat162float(down[pos[s] * hidden + c + cc]);
-        y[t * hidden + c + cc] = __float2bfloat16_rn(acc);
-      }
-    }
+  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos, eid);
+  for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < top_k; ++s)
+      if (pos[s] >= 0) acc += __bfloat162float(down[pos[s] * hidden + c]);
+    if (add) acc += __bfloat162float(add[t * hidden + c]);
+    y[t * hidden + c] = __float2bfloat16_rn(acc);
   }
 }
-
 
 // combine_kernel for hidden % 8 == 0: 128-bit loads and stores.
 __global__ void __launch_bounds__(256)
 combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int top_k,
-                   int64_t hidden, __nv_bfloat16* __restrict__ y) {
+                   int64_t hidden, const __nv_bfloat16* __restrict__ add, __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
   int64_t pos[8];
   int eid[8];
-  for (int s = 0; s < top_k; ++s) {
-    pos[s] = inv[t * top_k + s];
-    eid[s] = ids[t * top_k + s];
-  }
-  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
-    const int e = eid[i];
-    const int64_t p = pos[i];
-    int j = i - 1;
-    while (j >= 0 && eid[j] > e) {
-      eid[j + 1] = eid[j];
-      pos[j + 1] = pos[j];
-      --j;
-    }
-    eid[j + 1] = e;
-    pos[j + 1] = p;
-  }
+  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos, eid);
   const int chunks = (int)(hidden >> 3);
   for (int c = threadIdx.x; c < chunks; c += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < top_k; ++s) {
+      if (pos[s] < 0) continue;
       float f[8];
       bf16x8_to_float(reinterpret_cast<const uint4*>(down + pos[s] * hidden)[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    if (add) {
+      float f[8];
+      bf16x8_to_float(reinterpret_cast<const uint4*>(add + t * hidden)[c], f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
@@ -510,8 +537,10 @@ __global__ void combine_weighted_kernel(const __nv_bfloat16* __restrict__ down, 
   int64_t pos[8];
   int eid[8];
   float wv[8];
+  const int64_t n_pos = (int64_t)gridDim.x * top_k;
   for (int s = 0; s < top_k; ++s) {
-    pos[s] = inv[t * top_k + s];
+    const int64_t q = inv[t * top_k + s];
+    pos[s] = (q >= 0 && q < n_pos) ? q : -1;  // -1: the slot's expert id was dropped by the routing sort
     eid[s] = ids[t * top_k + s];
     wv[s] = __bfloat162float(__float2bfloat16_rn(weights[t * top_k + s]));
   }
@@ -533,6 +562,7 @@ __global__ void combine_weighted_kernel(const __nv_bfloat16* __restrict__ down, 
   for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < top_k; ++s) {
+      if (pos[s] < 0) continue;
       const float r = __bfloat162float(__float2bfloat16_rn(__bfloat162float(down[pos[s] * hidden + c]) * wv[s]));
       acc = __bfloat162float(__float2bfloat16_rn(acc + r));
     }
@@ -545,25 +575,28 @@ __global__ void combine_weighted_kernel(const __nv_bfloat16* __restrict__ down, 
 
 using namespace dst;
 
-extern "C" int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
-                                         float* weights, int32_t* ids, dst_stream_t stream);
-
-extern "C" int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
-                                      float* weights, int32_t* ids, dst_stream_t stream) {
-  return dst_route_softmax_topk_ex(logits, T, E, top_k, 1, route_scale, weights, ids, stream);
-}
-
-extern "C" int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
-                                         float* weights, int32_t* ids, dst_stream_t stream) {
-  if (T < 0 || E <= 0 || top_k <= 0) return DST_ERR_BAD_ARG;
+extern "C" int dst_route_topk(const float* logits, const float* bias, int64_t T, int64_t E, int top_k, int score_func, float gate_temp,
+                              int renorm, float route_scale, float* weights, int32_t* ids, dst_stream_t stream) {
+  if (T < 0 || E <= 0 || top_k <= 0 || score_func < DST_SCORE_SOFTMAX || score_func > DST_SCORE_SQRTSOFTPLUS || !(gate_temp != 0.f))
+    return DST_ERR_BAD_ARG;
   if (E > 32 * ROUTE_MAX_PER_LANE || top_k > 8 || top_k > E) return DST_ERR_UNSUPPORTED;
   if (T == 0) return DST_OK;
   if (!logits || !weights || !ids) return DST_ERR_BAD_ARG;
   const int warps = 4;
   route_kernel<<<(unsigned)cdiv64(T, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, T, (int)E, top_k, renorm, route_scale, weights, ids);
+      logits, bias, T, (int)E, top_k, score_func, 1.f / gate_temp, renorm, route_scale, weights, ids);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
+}
+
+extern "C" int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
+                                         float* weights, int32_t* ids, dst_stream_t stream) {
+  return dst_route_topk(logits, nullptr, T, E, top_k, DST_SCORE_SOFTMAX, 1.f, renorm, route_scale, weights, ids, stream);
+}
+
+extern "C" int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
+                                      float* weights, int32_t* ids, dst_stream_t stream) {
+  return dst_route_topk(logits, nullptr, T, E, top_k, DST_SCORE_SOFTMAX, 1.f, 1, route_scale, weights, ids, stream);
 }
 
 extern "C" size_t dst_sort_workspace_bytes(int64_t n, int64_t E) {
@@ -587,9 +620,9 @@ extern "C" int dst_sort_by_expert(const void* ids, int ids_are_i32, int64_t n, i
   int32_t* hist = static_cast<int32_t*>(workspace);
   const size_t sh32 = (size_t)E * sizeof(int32_t);
   if (ids_are_i32)
-    sort_hist_kernel<int32_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int32_t*>(ids), n, (int)E, hist, bad_count);
+    sort_hist_kernel<int32_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int32_t*>(ids), n, (int)E, hist, bad_count, order);
   else
-    sort_hist_kernel<int64_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int64_t*>(ids), n, (int)E, hist, bad_count);
+    sort_hist_kernel<int64_t><<<(unsigned)chunks, 32, sh32, st>>>(static_cast<const int64_t*>(ids), n, (int)E, hist, bad_count, order);
   DST_CUDA_TRY(cudaGetLastError());
   sort_scan_kernel<<<1, 512, (size_t)E * sizeof(int64_t), st>>>(hist, chunks, (int)E, offsets);
   DST_CUDA_TRY(cudaGetLastError());
@@ -672,24 +705,32 @@ extern "C" int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, 
   return DST_OK;
 }
 
-extern "C" int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
-                           int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream) {
+extern "C" int dst_combine_add(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
+                               int64_t hidden, int64_t* inv, const void* add_bf16, void* y_bf16, dst_stream_t stream) {
   if (T < 0 || top_k <= 0 || top_k > 8 || hidden <= 0) return DST_ERR_BAD_ARG;
   if (T == 0) return DST_OK;
   if (!down_bf16 || !order || !ids || !inv || !y_bf16) return DST_ERR_BAD_ARG;
   if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
   auto st = static_cast<cudaStream_t>(stream);
   const int64_t n = T * top_k;
+  DST_CUDA_TRY(cudaMemsetAsync(inv, 0xff, (size_t)n * sizeof(int64_t), st));  // -1: no row (see invert_order_kernel)
   invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
   DST_CUDA_TRY(cudaGetLastError());
-  if (hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(down_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(y_bf16) & 15) == 0)
-    combine_vec_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
+  auto add = static_cast<const __nv_bfloat16*>(add_bf16);
+  if (hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(down_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(y_bf16) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(add_bf16) & 15) == 0)
+    combine_vec_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden, add,
                                                    static_cast<__nv_bfloat16*>(y_bf16));
   else
-    combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden,
+    combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden, add,
                                                static_cast<__nv_bfloat16*>(y_bf16));
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
+}
+
+extern "C" int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
+                           int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream) {
+  return dst_combine_add(down_bf16, order, ids, T, top_k, hidden, inv, nullptr, y_bf16, stream);
 }
 
 extern "C" int dst_swiglu_std(const void* gu_bf16, int64_t n_rows, int64_t inter, void* h_bf16, dst_stream_t stream) {
@@ -723,6 +764,7 @@ extern "C" int dst_combine_weighted(const void* down_bf16, const int64_t* order,
   if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
   auto st = static_cast<cudaStream_t>(stream);
   const int64_t n = T * top_k;
+  DST_CUDA_TRY(cudaMemsetAsync(inv, 0xff, (size_t)n * sizeof(int64_t), st));  // -1: no row
   invert_order_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, n, inv);
   DST_CUDA_TRY(cudaGetLastError());
   combine_weighted_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, weights, top_k, hidden,

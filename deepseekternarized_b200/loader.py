@@ -1,7 +1,9 @@
 """Manifest-driven loader: routed-expert weights of a Boilerplate export -> the stacked device layout.
 
 A Boilerplate-format directory (``docs/architecture/format.md`` of the reference, section "manifest.json")
-holds ``manifest.json`` and safetensors shards. A Mode C/D weight ``X`` is stored per term ``i`` as
+holds ``manifest.json`` and safetensors shards. A Mode C weight (k stacked terms) or Mode D weight (one QAT-trained
+term; the exporter writes ``"mode": rule.mode`` for both, ``boilerplate/format/export.py:202-234``, and the engine reads
+both through the same branch, ``boilerplate/engine/model.py:364``) ``X`` is stored per term ``i`` as
 ``X.tq{i}.packed`` uint8 ``[N, ceil(K / per_byte)]`` and ``X.tq{i}.scale`` fp16/bf16 ``[N, ceil(K / group)]``
 (``format.md:87-92``); its manifest entry names the packing, the number of terms, the group, the scale type
 and, per stored tensor, the shard file and a SHA-256 of its bytes (``format.md:108-134``). The reference reads
@@ -41,8 +43,9 @@ def _entry(manifest: dict, base: str) -> dict:
     meta = manifest["tensors"].get(base)
     if meta is None:
         raise ManifestError(f"{base}: not in the manifest")
-    if meta.get("mode") != "C":
-        raise ManifestError(f"{base}: mode {meta.get('mode')!r}, the ternary backend takes Mode C (stacked ternary) weights")
+    if meta.get("mode") not in ("C", "D"):
+        raise ManifestError(f"{base}: mode {meta.get('mode')!r}, the ternary backend takes Mode C (stacked ternary) and "
+                            "Mode D (single ternary term) weights")
     if meta.get("packing") not in _PER_BYTE:
         raise ManifestError(f"{base}: unknown packing {meta.get('packing')!r}")
     return meta
@@ -82,7 +85,8 @@ def load_expert_weights(root, experts_prefix: str, n_experts: int, device=None, 
     ``boilerplate/engine/model.py:365-387``; pass ``names=("gate_proj", "down_proj", "up_proj")`` for the standard
     engine's naming, ``engine/standard.py:130-133``). ``first_expert`` / ``n_experts`` select a rank's shard for
     expert parallelism. ``verify`` checks every tensor's SHA-256 against the manifest. With ``prepare`` (and a CUDA
-    ``device``) the packed stacks are re-laid-out once into the tiled device layout.
+    ``device``) the packed stacks are re-laid-out once into the tiled device layout (fp16 scales; bf16 scales stay
+    canonical and run on the generic kernel). The returned object carries the manifest's ``act`` entry as ``.act``.
     """
     root = Path(root)
     mpath = root / "manifest.json"
@@ -98,7 +102,8 @@ def load_expert_weights(root, experts_prefix: str, n_experts: int, device=None, 
         gate, gm = got[g_name]
         down, dm = got[d_name]
         up, um = got[u_name]
-        key = (gm["packing"], int(gm["group"]), int(gm["terms"]), tuple(gm["shape"]), tuple(dm["shape"]), gm.get("scale_dtype"))
+        key = (gm["packing"], int(gm["group"]), int(gm["terms"]), tuple(gm["shape"]), tuple(dm["shape"]), gm.get("scale_dtype"),
+               gm.get("act"))
         for m in (dm, um):
             if (m["packing"], int(m["group"]), int(m["terms"])) != key[:3]:
                 raise ManifestError(f"{experts_prefix}.{e}: projections differ in packing, group or number of terms")
@@ -116,9 +121,10 @@ def load_expert_weights(root, experts_prefix: str, n_experts: int, device=None, 
             stacks[i][3].append(down[i][1])
     if ref is None:
         raise ManifestError("no experts requested")
-    fmt, group, _, (inter, hidden), _, _ = ref
+    fmt, group, _, (inter, hidden), _, _, act = ref
     dev = torch.device(device) if device is not None else torch.device("cpu")
     w = ExpertWeights([torch.stack(s[0]).to(dev) for s in stacks], [torch.stack(s[1]).to(dev) for s in stacks],
                       [torch.stack(s[2]).to(dev) for s in stacks], [torch.stack(s[3]).to(dev) for s in stacks],
                       int(hidden), int(inter), group, fmt)
+    w.act = act  # the manifest's activation mode of these weights ("int8" or "bf16", boilerplate/format/policy.py:73), for the caller
     return w.prepare() if prepare and dev.type == "cuda" else w

@@ -1,15 +1,20 @@
 """The MoE routed-expert layer on B200: single GPU and expert-parallel over NCCL.
 
-Semantics are the reference's V4 MoE layer (``boilerplate/engine/model.py:376-422``) with
-softmax scores, renormalised top-k, ``route_scale`` and optional SwiGLU clamp, no shared expert:
+Semantics are the reference's V4 MoE layer (``boilerplate/engine/model.py:376-422``): the router with its three
+score functions, gate bias, temperature, optional renormalisation and ``route_scale``; the SwiGLU clamp; the
+shared expert:
 
     weights, ids = route(x)                                   # model.py:389-405
     for experts in increasing id over their tokens:           # model.py:415-420
         h = bf16(weight * silu(w1(x)) * w3(x))                # w1/w3 outputs rounded to bf16, model.py:376-386
         y[token] += w2(h)                                     # bf16 output, fp32 accumulation
+    y += shared_expert(x)                                     # model.py:421
     y = bf16(y)
 
-where the reference loops over experts in Python (three ``TernaryLinear`` calls each), this layer
+``MoELayer.forward`` takes the router's logits; ``MoELayer.forward_routed`` takes ``(weights, ids)`` an engine has
+already computed, which makes the layer a replacement for the loop of ``V4Model.moe`` / ``StandardDecoder._moe``.
+
+Where the reference loops over experts in Python (three ``TernaryLinear`` calls each), this layer
 sorts the (token, slot) pairs by expert once and runs two grouped ternary GEMMs over all experts
 (gate and up stacked into one [2I, hidden] weight per expert).
 
@@ -86,15 +91,25 @@ class B200Ops:
     def _lib():
         return kb._require("auto")
 
-    def route(self, logits: torch.Tensor, top_k: int, route_scale: float, renorm: bool = True):
+    def route(self, logits: torch.Tensor, top_k: int, route_scale: float, renorm: bool = True, score_func: str = "softmax",
+              bias: torch.Tensor | None = None, gate_temp: float = 1.0):
+        """boilerplate/engine/model.py:389-405 from the gate's logits: scores = f(logits / gate_temp), selection on
+        scores + bias, weights from the unbiased scores."""
         lib = self._lib()
+        if score_func not in _lib.SCORE_FUNCS:
+            raise ValueError(f"score_func must be one of {sorted(_lib.SCORE_FUNCS)}, got {score_func!r}")
         logits = logits.float().contiguous()
         T, E = logits.shape
+        if bias is not None:
+            bias = bias.to(device=logits.device, dtype=torch.float32).contiguous()
+            if bias.numel() != E:
+                raise ValueError("the gate bias holds one value per expert")
         w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
         ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
         with torch.cuda.device(logits.device):
-            _lib.check(lib.dst_route_softmax_topk_ex(logits.data_ptr(), T, E, top_k, 1 if renorm else 0, ctypes.c_float(route_scale),
-                                                     w.data_ptr(), ids.data_ptr(), kb._stream(logits)))
+            _lib.check(lib.dst_route_topk(logits.data_ptr(), bias.data_ptr() if bias is not None else None, T, E, top_k,
+                                          _lib.SCORE_FUNCS[score_func], ctypes.c_float(gate_temp), 1 if renorm else 0,
+                                          ctypes.c_float(route_scale), w.data_ptr(), ids.data_ptr(), kb._stream(logits)))
         return w, ids
 
     def sort(self, ids: torch.Tensor, n_experts: int):
@@ -104,16 +119,20 @@ class B200Ops:
         return (self.fused_norm and self.algo in ("auto", "prefill") and isinstance(weights[0], kb.TiledWeights)
                 and rows > 16 * weights[0].E)
 
-    def gather(self, x: torch.Tensor, order: torch.Tensor, top_k: int, for_weights=None):
+    def gather(self, x: torch.Tensor, order: torch.Tensor | None, top_k: int, for_weights=None):
+        """Rows ``x[order // top_k]`` (``order`` None: the rows as they are)."""
         lib = self._lib()
         x = x.contiguous()
-        if for_weights is not None and x.dtype == torch.bfloat16 and self._norm_ok(for_weights, order.numel()):
-            out = torch.empty(order.numel(), x.size(1), dtype=torch.float16, device=x.device)
-            fac = torch.empty(order.numel(), dtype=torch.float32, device=x.device)
+        n = order.numel() if order is not None else x.size(0)
+        if for_weights is not None and x.dtype == torch.bfloat16 and self._norm_ok(for_weights, n):
+            out = torch.empty(n, x.size(1), dtype=torch.float16, device=x.device)
+            fac = torch.empty(n, dtype=torch.float32, device=x.device)
             with torch.cuda.device(x.device):
-                _lib.check(lib.dst_gather_rows_norm(x.data_ptr(), order.data_ptr(), order.numel(), x.size(1), top_k, out.data_ptr(),
-                                                    fac.data_ptr(), kb._stream(x)))
+                _lib.check(lib.dst_gather_rows_norm(x.data_ptr(), order.data_ptr() if order is not None else None, n, x.size(1), top_k,
+                                                    out.data_ptr(), fac.data_ptr(), kb._stream(x)))
             return kb.NormRows(out, fac)
+        if order is None:
+            return x
         out = torch.empty(order.numel(), x.size(1), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):
             _lib.check(lib.dst_gather_rows(x.data_ptr(), order.data_ptr(), order.numel(), x.size(1), top_k, out.data_ptr(),
@@ -170,15 +189,21 @@ class B200Ops:
                                                 inv.data_ptr(), y.data_ptr(), kb._stream(down)))
         return y
 
-    def combine(self, down: torch.Tensor, order: torch.Tensor, ids: torch.Tensor, T: int, top_k: int) -> torch.Tensor:
+    def combine(self, down: torch.Tensor, order: torch.Tensor, ids: torch.Tensor, T: int, top_k: int,
+                add: torch.Tensor | None = None) -> torch.Tensor:
+        """Per token: its experts' rows in increasing expert id, fp32 sum, then ``add`` (the shared expert's bf16 rows), bf16."""
         lib = self._lib()
         hidden = down.size(1)
         inv = torch.empty(T * top_k, dtype=torch.int64, device=down.device)
         y = torch.empty(T, hidden, dtype=torch.bfloat16, device=down.device)
         ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        if add is not None:
+            add = add.contiguous()
+            if tuple(add.shape) != (T, hidden) or add.dtype != torch.bfloat16:
+                raise RuntimeError("the added rows must be bf16 [tokens, hidden]")
         with torch.cuda.device(down.device):
-            _lib.check(lib.dst_combine(down.data_ptr(), order.data_ptr(), ids32.data_ptr(), T, top_k, hidden, inv.data_ptr(),
-                                       y.data_ptr(), kb._stream(down)))
+            _lib.check(lib.dst_combine_add(down.data_ptr(), order.data_ptr(), ids32.data_ptr(), T, top_k, hidden, inv.data_ptr(),
+                                           add.data_ptr() if add is not None else None, y.data_ptr(), kb._stream(down)))
         return y
 
 
@@ -186,21 +211,44 @@ class MoELayer:
     """Single-device routed-expert layer over ``ExpertWeights``.
 
     ``flavour="v4"`` follows boilerplate/engine/model.py:372-422 (routing weight before w2, fp32 accumulation over
-    a token's experts); ``flavour="standard"`` follows boilerplate/engine/standard.py:154-176 (OLMoE-style: every
-    intermediate in bf16, weight applied to the expert output, bf16 accumulation, ``norm_topk_prob`` optional).
+    a token's experts, shared expert added at the end); ``flavour="standard"`` follows
+    boilerplate/engine/standard.py:154-176 (OLMoE-style: every intermediate in bf16, weight applied to the expert
+    output, bf16 accumulation, ``norm_topk_prob`` optional).
+
+    Router options of the V4 flavour (model.py:389-405): ``score_func`` "softmax" | "sigmoid" | "sqrtsoftplus",
+    ``gate_bias`` [E] added for the selection only, ``gate_temp`` dividing the logits, ``norm_topk_prob``,
+    ``route_scale``. ``shared``: the shared expert as ``ExpertWeights`` holding one expert (model.py:421), or None.
     """
 
     def __init__(self, weights: ExpertWeights, top_k: int, route_scale: float = 1.0, swiglu_limit: float = 0.0, ops=None,
-                 flavour: str = "v4", norm_topk_prob: bool = True):
+                 flavour: str = "v4", norm_topk_prob: bool = True, score_func: str = "softmax", gate_bias=None,
+                 gate_temp: float = 1.0, shared: ExpertWeights | None = None):
         if flavour not in ("v4", "standard"):
             raise ValueError(f"flavour must be 'v4' or 'standard', got {flavour!r}")
+        if score_func not in _lib.SCORE_FUNCS:
+            raise ValueError(f"score_func must be one of {sorted(_lib.SCORE_FUNCS)}, got {score_func!r}")
+        if flavour == "standard" and (score_func != "softmax" or gate_bias is not None or gate_temp != 1.0 or shared is not None):
+            raise ValueError("the standard flavour routes by plain softmax and has no shared expert (engine/standard.py:156-176)")
+        if shared is not None and (shared.n_experts != 1 or shared.hidden != weights.hidden):
+            raise ValueError("the shared expert is one expert over the same hidden size")
         self.w, self.top_k, self.route_scale, self.swiglu_limit = weights, top_k, route_scale, swiglu_limit
         self.flavour, self.norm_topk_prob = flavour, norm_topk_prob
+        self.score_func, self.gate_bias, self.gate_temp, self.shared = score_func, gate_bias, gate_temp, shared
         self.ops = ops if ops is not None else B200Ops()
 
-    def _forward_standard(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+    def route(self, logits: torch.Tensor):
+        """(weights [T, k] f32, ids [T, k]) from the gate's logits, per this layer's router options."""
+        if self.flavour == "standard":
+            return self.ops.route(logits, self.top_k, 1.0, renorm=self.norm_topk_prob)
+        if self.score_func == "softmax" and self.gate_bias is None and self.gate_temp == 1.0:
+            if self.norm_topk_prob:
+                return self.ops.route(logits, self.top_k, self.route_scale)  # the three-argument form every ops object has
+            return self.ops.route(logits, self.top_k, self.route_scale, renorm=False)
+        return self.ops.route(logits, self.top_k, self.route_scale, renorm=self.norm_topk_prob, score_func=self.score_func,
+                              bias=self.gate_bias, gate_temp=self.gate_temp)
+
+    def _forward_standard(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         w, T = self.w, x.size(0)
-        weights, ids = self.ops.route(logits, self.top_k, 1.0, renorm=self.norm_topk_prob)
         order, offsets = self.ops.sort(ids, w.n_experts)
         xs = self.gather_for_experts(x, order, self.top_k)
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
@@ -208,9 +256,10 @@ class MoELayer:
         down = self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
         return self.ops.combine_weighted(down, order, ids, weights, T, self.top_k)
 
-    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order, out=None) -> torch.Tensor:
-        """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows (into ``out`` if given)."""
-        w = self.w
+    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order, out=None, weights=None) -> torch.Tensor:
+        """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows (into ``out`` if given).
+        ``weights``: the experts to run (default: the routed ones); ``offsets`` None = one expert over all rows."""
+        w = self.w if weights is None else weights
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
         if getattr(self.ops, "fused_norm", False):
             h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit, for_weights=w.w2_packed)
@@ -220,22 +269,42 @@ class MoELayer:
             return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
         return self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt, out=out)
 
-    def gather_for_experts(self, x: torch.Tensor, order: torch.Tensor, top_k: int):
+    def gather_for_experts(self, x: torch.Tensor, order: torch.Tensor, top_k: int, weights=None):
         """Rows in expert-sorted order, in the format the first expert GEMM reads fastest."""
+        w = self.w if weights is None else weights
         if getattr(self.ops, "fused_norm", False):
-            return self.ops.gather(x, order, top_k, for_weights=self.w.w13_packed)
+            return self.ops.gather(x, order, top_k, for_weights=w.w13_packed)
         return self.ops.gather(x, order, top_k)
 
-    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
-        """x [T, hidden] bf16, router logits [T, E] f32 -> y [T, hidden] bf16."""
+    def shared_forward(self, x: torch.Tensor):
+        """``swiglu(L.shared, x)`` of boilerplate/engine/model.py:421 as bf16 rows [T, hidden] (None without a shared
+        expert): one expert over every token, no routing weight, the same clamp."""
+        if self.shared is None:
+            return None
+        xs = self.gather_for_experts(x, None, 1, weights=self.shared)
+        return self.experts_forward(xs, None, None, None, weights=self.shared)
+
+    def forward_routed(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """x [T, hidden] bf16 with routing weights [T, k] f32 and expert ids [T, k] (int32 or int64) that the caller
+        computed (``V4Model.route`` / the top-k of ``StandardDecoder._moe``) -> y [T, hidden] bf16. An id outside
+        [0, E) drops that (token, slot)."""
+        if tuple(weights.shape) != tuple(ids.shape) or weights.size(0) != x.size(0) or weights.size(-1) != self.top_k:
+            raise ValueError("weights and ids are [tokens, top_k]")
         if self.flavour == "standard":
-            return self._forward_standard(x, logits)
+            return self._forward_standard(x, weights, ids)
         T = x.size(0)
-        weights, ids = self.ops.route(logits, self.top_k, self.route_scale)
         order, offsets = self.ops.sort(ids, self.w.n_experts)
         xs = self.gather_for_experts(x, order, self.top_k)
-        down = self.experts_forward(xs, offsets, weights.reshape(-1), order)
-        return self.ops.combine(down, order, ids, T, self.top_k)
+        down = self.experts_forward(xs, offsets, weights.reshape(-1).float().contiguous(), order)
+        if self.shared is None:
+            return self.ops.combine(down, order, ids, T, self.top_k)
+        return self.ops.combine(down, order, ids, T, self.top_k, add=self.shared_forward(x))
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """x [T, hidden] bf16, router logits [T, E] f32 (``F.linear(x.float(), gate_w)``, before the temperature)
+        -> y [T, hidden] bf16."""
+        weights, ids = self.route(logits)
+        return self.forward_routed(x, weights, ids)
 
     __call__ = forward
 
@@ -291,10 +360,13 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights: ExpertWeights, n_experts_total: int, top_k: int, group=None, route_scale: float = 1.0,
-                 swiglu_limit: float = 0.0, ops=None, transport: str = "auto"):
+                 swiglu_limit: float = 0.0, ops=None, transport: str = "auto", norm_topk_prob: bool = True,
+                 score_func: str = "softmax", gate_bias=None, gate_temp: float = 1.0, shared: ExpertWeights | None = None):
         """``transport``: "nccl" = all_to_all_single of rows both ways (any backend, also gloo on CPU);
         "peer" = the rows are written into / read from the owners' buffers by this library's kernels over NVLink
-        (CUDA, one node, torch symmetric memory, B200Ops); "auto" = "peer" where it can be set up, else "nccl"."""
+        (CUDA, one node, torch symmetric memory, B200Ops); "auto" = "peer" where it can be set up, else "nccl".
+        Router options and ``shared`` as in ``MoELayer`` (``gate_bias`` over the GLOBAL experts; the shared expert is
+        replicated: every rank applies it to its own tokens)."""
         import torch.distributed as dist
 
         self.dist = dist
@@ -305,7 +377,8 @@ class ExpertParallelMoE:
         self.El = expert_owner_split(n_experts_total, self.world)
         if weights.n_experts != self.El:
             raise ValueError(f"rank holds {weights.n_experts} experts, expected {self.El}")
-        self.local = MoELayer(weights, top_k, route_scale, swiglu_limit, ops)
+        self.local = MoELayer(weights, top_k, route_scale, swiglu_limit, ops, norm_topk_prob=norm_topk_prob, score_func=score_func,
+                              gate_bias=gate_bias, gate_temp=gate_temp, shared=shared)
         self.ops = self.local.ops
         self.top_k = top_k
         self.last_dispatch_rows = 0
@@ -322,8 +395,11 @@ class ExpertParallelMoE:
             return False
         if self._peer is not None:
             return True
-        ok = (x.is_cuda and isinstance(self.ops, B200Ops) and self.ops.fused_norm and self.world <= _lib.MAX_PEERS
-              and x.size(1) % 8 == 0 and x.size(1) <= 8192 and self.dist.get_backend(self.pg) == "nccl")
+        # the peer kernels hand the tcgen05 kernel its fp16 row format: tiled weights it covers are part of the condition
+        ok = (x.is_cuda and isinstance(self.ops, B200Ops) and self.ops.fused_norm and self.ops.algo in ("auto", "prefill")
+              and self.world <= _lib.MAX_PEERS and x.size(1) % 8 == 0 and x.size(1) <= 8192
+              and self.dist.get_backend(self.pg) == "nccl" and isinstance(self.local.w.w13_packed[0], kb.TiledWeights)
+              and isinstance(self.local.w.w2_packed[0], kb.TiledWeights))
         bufs = None
         if ok:
             try:
@@ -347,15 +423,17 @@ class ExpertParallelMoE:
         self._peer = False
         return False
 
-    def _forward_peer(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+    def _forward_peer(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         dist, W, El = self.dist, self.world, self.El
         lib = B200Ops._lib()
         T, hidden = x.size(0), x.size(1)
         if T * self.top_k * W > self._peer[0].cap:
-            raise RuntimeError("more tokens per step than the peer buffers were sized for")
+            # a local decision: the buffers were sized (collectively, at the first step) for the largest token count
+            # any rank showed then, and a rank that later brings more must not enter the step's collectives
+            raise RuntimeError("more tokens per step than the peer buffers were sized for: keep every step's token count "
+                               "at or below the first step's largest")
         buf = self._peer[self._step & 1]  # two sets: a peer may still read last step's outputs while this step pushes
         self._step += 1
-        weights, ids = self.ops.route(logits, self.top_k, self.local.route_scale)
         order, offsets = self.ops.sort(ids, self.E)
         counts = offsets.diff().to(torch.int64).contiguous()
         counts_all = torch.empty(W, self.E, dtype=torch.int64, device=x.device)
@@ -374,22 +452,28 @@ class ExpertParallelMoE:
         if R > 0:
             xs2 = kb.NormRows(buf.rows[:R], buf.fac[:R])
             self.local.experts_forward(xs2, offsets2, buf.wts[:R], None, out=buf.down[:R])
+        shared = self.local.shared_forward(x)  # this rank's tokens through the (replicated) shared expert
         dist.all_reduce(self._sync, group=self.pg)  # every rank's expert outputs are written
         inv = torch.empty(T * self.top_k, dtype=torch.int64, device=x.device)
         y = torch.empty(T, hidden, dtype=torch.bfloat16, device=x.device)
         ids32 = ids.reshape(-1).to(torch.int32).contiguous()
         with torch.cuda.device(x.device):
-            _lib.check(lib.dst_ep_combine_pull(buf.ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(),
-                                               dst_start.data_ptr(), T, El, self.top_k, hidden, inv.data_ptr(), y.data_ptr(), W,
-                                               kb._stream(x)))
+            _lib.check(lib.dst_ep_combine_pull_add(buf.ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(),
+                                                   dst_start.data_ptr(), T, El, self.top_k, hidden, inv.data_ptr(),
+                                                   shared.data_ptr() if shared is not None else None, y.data_ptr(), W, kb._stream(x)))
         return y
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """x [T, hidden] bf16 and the gate's logits over the GLOBAL experts [T, E] -> y [T, hidden] bf16."""
+        weights, ids = self.local.route(logits)
+        return self.forward_routed(x, weights, ids)
+
+    def forward_routed(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """The step from routing weights [T, k] and GLOBAL expert ids [T, k] the caller computed."""
         if x.dtype == torch.bfloat16 and self._peer_setup(x):
-            return self._forward_peer(x, logits)
+            return self._forward_peer(x, weights.float().contiguous(), ids)
         dist, W, El = self.dist, self.world, self.El
         T = x.size(0)
-        weights, ids = self.ops.route(logits, self.top_k, self.local.route_scale)
         order, offsets = self.ops.sort(ids, self.E)  # sorted by global expert = by owner rank, then local expert
         xs = self.ops.gather(x, order, self.top_k)
         row_w = weights.reshape(-1)[order].contiguous()
@@ -422,7 +506,9 @@ class ExpertParallelMoE:
 
         down = torch.empty(xs.size(0), back.size(1), dtype=back.dtype, device=x.device)
         dist.all_to_all_single(down, back, send_l, recv_l, group=self.pg)
-        return self.ops.combine(down, order, ids, T, self.top_k)
+        if self.local.shared is None:
+            return self.ops.combine(down, order, ids, T, self.top_k)
+        return self.ops.combine(down, order, ids, T, self.top_k, add=self.local.shared_forward(x))
 
     __call__ = forward
 

@@ -132,8 +132,8 @@ int dst_quant_act_int8(const void* x, int x_is_f32, int64_t M, int64_t K, int8_t
  *                NULL. The prefill kernel keeps the fp16 copy of the activations and the per-row
  *                factors there; it is free again when the launched work has finished.
  *
- * Fast-kernel coverage: tiled weights, group == 128, K % 128 == 0, fp16 scales, bf16 or f16
- * activations. GENERIC reads canonical weights only.
+ * Fast-kernel coverage: tiled weights, group == 128, K % 128 == 0 (TQ2 decode: K % 256 == 0), fp16 scales, bf16,
+ * f16 or int8 activations. GENERIC reads canonical weights only.
  * Bounds: E <= DST_MAX_EXPERTS, K <= 2^24, N <= 2^24, T <= 2^31 - 1.
  *
  * Replaces the native entry ternary_grouped_gemm (boilerplate/kernels/csrc/ternary_cuda.cpp:7-10,
@@ -168,6 +168,19 @@ int dst_sort_by_expert(const void* ids, int ids_are_i32, int64_t n, int64_t E, i
  */
 int dst_route_softmax_topk(const float* logits, int64_t T, int64_t E, int top_k, float route_scale,
                            float* weights, int32_t* ids, dst_stream_t stream);
+/*
+ * The general router of boilerplate/engine/model.py:389-405:
+ *   score   = f(logit / gate_temp), f = softmax over the E logits | sigmoid | sqrt(softplus)   (score_func)
+ *   ids     = the top_k experts by score + bias[e] (bias [E] f32 or NULL; ties: lower expert id first; a NaN ranks
+ *             above every number as in torch.topk)
+ *   weights = the UNBIASED scores of the picked experts, divided by (their sum + 1e-20) when renorm != 0 and
+ *             top_k > 1, times route_scale
+ * The top_k ids of a token are always distinct and inside [0, E), whatever the logits hold (NaN, +-inf).
+ * E <= 1024, top_k <= 8, gate_temp != 0.
+ */
+enum { DST_SCORE_SOFTMAX = 0, DST_SCORE_SIGMOID = 1, DST_SCORE_SQRTSOFTPLUS = 2 };
+int dst_route_topk(const float* logits, const float* bias, int64_t T, int64_t E, int top_k, int score_func, float gate_temp,
+                   int renorm, float route_scale, float* weights, int32_t* ids, dst_stream_t stream);
 /* The same with the renormalisation optional (renorm = 0: the softmax scores of the selected experts as they are):
  * the `norm_topk_prob` switch of boilerplate/engine/standard.py:159-165. */
 int dst_route_softmax_topk_ex(const float* logits, int64_t T, int64_t E, int top_k, int renorm, float route_scale,
@@ -208,6 +221,11 @@ int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64
  */
 int dst_combine(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
                 int64_t hidden, int64_t* inv, void* y_bf16, dst_stream_t stream);
+/* The same with one more bf16 row per token added in fp32 after the experts' rows and before the cast: the shared
+ * expert's output, `y += self.swiglu(L.shared, x)` of boilerplate/engine/model.py:421. add_bf16 [T, hidden] or NULL.
+ * A (token, slot) whose expert id the routing sort dropped (outside [0, E)) contributes nothing. */
+int dst_combine_add(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,
+                    int64_t hidden, int64_t* inv, const void* add_bf16, void* y_bf16, dst_stream_t stream);
 
 /*
  * The standard (OLMoE-style) MoE flavour, boilerplate/engine/standard.py:149-176, which keeps every intermediate in
@@ -252,6 +270,11 @@ int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* of
 int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
                         const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
                         void* y_bf16, int world, dst_stream_t stream);
+/* dst_ep_combine_pull with the token's row of add_bf16 [T, hidden] (this rank's shared-expert output, or NULL) added
+ * in fp32 after the experts' rows, as dst_combine_add does. */
+int dst_ep_combine_pull_add(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
+                            const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
+                            const void* add_bf16, void* y_bf16, int world, dst_stream_t stream);
 
 /*
  * The grouped GEMM for callers that must not allocate device memory. (This entry has no counterpart
@@ -287,7 +310,7 @@ int dst_ternary_grouped_gemm_noalloc(void* out, int out_dtype, int accumulate, c
                                      const void* const* packed_tiled, const void* const* scales, int n_terms,
                                      int64_t E, int64_t T, int64_t N, int64_t K, int fmt, dst_stream_t stream);
 
-/* Reads (and clears) the device-side status word that bounded waits in the tcgen05 kernel write when
+/* Reads (and clears) the device-side status words that bounded waits in the tcgen05 and decode kernels write when
  * they give up. Synchronises `stream`. Returns DST_OK or DST_ERR_TIMEOUT. */
 int dst_check_device_status(dst_stream_t stream);
 

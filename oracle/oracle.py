@@ -256,14 +256,28 @@ def route_softmax_topk(x, gate_w, top_k: int, route_scale: float = 1.0):
     return route_from_logits(logits, top_k, route_scale)
 
 
-def route_from_logits(logits, top_k: int, route_scale: float = 1.0):
-    logits = _c(logits, np.float32)
-    z = logits - logits.max(-1, keepdims=True)
-    e = np.exp(z, dtype=np.float32)
-    scores = (e / e.sum(-1, keepdims=True, dtype=np.float32)).astype(np.float32)
-    idx = np.argsort(-scores, axis=-1, kind="stable")[:, :top_k]
+def route_from_logits(logits, top_k: int, route_scale: float = 1.0, score_func: str = "softmax", bias=None,
+                      gate_temp: float = 1.0, norm_topk_prob: bool = True):
+    """boilerplate/engine/model.py:391-405 from ``logits = F.linear(x.float(), gate_w)``: divide by the temperature,
+    score function, top-k of (scores + bias) (descending; on equal values the lower expert id first), weights from
+    the unbiased scores, optional renormalisation by (sum + 1e-20), times route_scale."""
+    z = (_c(logits, np.float32) / np.float32(gate_temp)).astype(np.float32)
+    if score_func == "softmax":
+        z = z - z.max(-1, keepdims=True)
+        e = np.exp(z, dtype=np.float32)
+        scores = (e / e.sum(-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    elif score_func == "sigmoid":
+        scores = (np.float32(1.0) / (np.float32(1.0) + np.exp(-z, dtype=np.float32))).astype(np.float32)
+    elif score_func == "sqrtsoftplus":
+        sp = np.where(z > 20, z, np.log1p(np.exp(np.minimum(z, 20), dtype=np.float32), dtype=np.float32))
+        scores = np.sqrt(sp, dtype=np.float32)
+    else:
+        raise ValueError(f"unknown score function {score_func!r}")
+    biased = scores if bias is None else (scores + _c(bias, np.float32)).astype(np.float32)
+    idx = np.argsort(-biased, axis=-1, kind="stable")[:, :top_k]
     w = np.take_along_axis(scores, idx, -1)
-    w = w / (w.sum(-1, keepdims=True, dtype=np.float32) + np.float32(1e-20))
+    if norm_topk_prob and top_k > 1:
+        w = w / (w.sum(-1, keepdims=True, dtype=np.float32) + np.float32(1e-20))
     return (w * np.float32(route_scale)).astype(np.float32), idx.astype(np.int64)
 
 
@@ -286,9 +300,10 @@ def swiglu_expert(x, w1, w2, w3, weights, K_hidden, K_inter, group, fmt, swiglu_
     return ternary_linear(bf16_round(h), w2, K_inter, group, fmt)
 
 
-def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_limit=0.0):
-    """boilerplate/engine/model.py:407-422 without the shared expert: experts in increasing id, each
-    over its tokens in token order, fp32 accumulation ``y[idx] += w2(...)``, final cast to bf16.
+def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_limit=0.0, shared=None):
+    """boilerplate/engine/model.py:407-422: experts in increasing id, each over its tokens in token order, fp32
+    accumulation ``y[idx] += w2(...)``, then ``y += swiglu(shared, x)`` (``shared`` = (w1, w2, w3) terms or None),
+    final cast to bf16.
 
     ``experts[e] = (w1_terms, w2_terms, w3_terms)``; ``weights``/``indices`` [T, k] from routing.
     """
@@ -300,6 +315,8 @@ def moe_layer(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_li
             continue
         w1, w2, w3 = experts[e]
         y[idx] += swiglu_expert(x[idx], w1, w2, w3, weights[idx, top, None], hidden, inter, group, fmt, swiglu_limit)
+    if shared is not None:
+        y += swiglu_expert(x, shared[0], shared[1], shared[2], None, hidden, inter, group, fmt, swiglu_limit)
     return bf16_round(y)
 
 
@@ -347,7 +364,7 @@ def moe_layer_standard(x, logits, experts, top_k, hidden, inter, group, fmt, nor
     return y, w, idx.astype(np.int64)
 
 
-def moe_layer_f64(x, weights, indices, experts, hidden, inter, group, fmt):
+def moe_layer_f64(x, weights, indices, experts, hidden, inter, group, fmt, swiglu_limit=0.0, shared=None):
     """The same layer in fp64 with no intermediate rounding (dequantized weights, boilerplate/ternary/ops.py:51-58):
     the yardstick for how much of a layer-level difference is bf16 rounding noise."""
     x = np.asarray(x, np.float64)
@@ -358,8 +375,16 @@ def moe_layer_f64(x, weights, indices, experts, hidden, inter, group, fmt):
             continue
         w1, w2, w3 = (dequantized(t, K, group, fmt) for t, K in zip(experts[e], (hidden, inter, hidden)))
         g, u = x[idx] @ w1.T, x[idx] @ w3.T
+        if swiglu_limit > 0:
+            u, g = np.clip(u, -swiglu_limit, swiglu_limit), np.minimum(g, swiglu_limit)
         h = np.asarray(weights, np.float64)[idx, top, None] * (g / (1.0 + np.exp(-g))) * u
         y[idx] += h @ w2.T
+    if shared is not None:
+        w1, w2, w3 = (dequantized(t, K, group, fmt) for t, K in zip(shared, (hidden, inter, hidden)))
+        g, u = x @ w1.T, x @ w3.T
+        if swiglu_limit > 0:
+            u, g = np.clip(u, -swiglu_limit, swiglu_limit), np.minimum(g, swiglu_limit)
+        y += ((g / (1.0 + np.exp(-g))) * u) @ w2.T
     return y
 
 

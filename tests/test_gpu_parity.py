@@ -148,7 +148,8 @@ def test_config1_decode_sweep_tq1_equals_tq2_on_same_trits(kb, fmt, M, N):
     for f in ("tq1", "tq2"):
         y[f] = kb.ternary_gemm_bf16(xt, [torch.from_numpy(O.pack(t, f)).to(DEV)], [st], K, 128, f).cpu().numpy()
     check_gemm(y[fmt], x, [(O.pack(t, fmt), s)], K, 128, fmt)
-    assert O.rel_fro(y["tq1"], y["tq2"]) < 1e-5  # same trits, same arithmetic: formats agree far inside the tolerance
+    # same trits through two kernels (TQ2 decode: 15-bit integer activations; the others: fp16): both far inside the tolerance
+    assert O.rel_fro(y["tq1"], y["tq2"]) < 2e-4
 
 
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])

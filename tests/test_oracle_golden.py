@@ -148,3 +148,37 @@ def test_table_row_lookup_matches_reference(golden, fmt):
     vals = O.gather_dequant_rows(g[f"{fmt}_ids"], terms, K, group, fmt)
     assert vals.shape == (*g[f"{fmt}_ids"].shape, K)
     assert np.array_equal(O.bf16_bits(vals).reshape(-1, K), g[f"{fmt}_vals_bits"])
+
+
+def variant_case(g, name):
+    """One case of the moe_layer_variants fixture (tests/golden/make_golden.py, section 5d) as plain values."""
+    T, hidden, inter, E, topk, group, k_terms, code, norm, with_shared = (int(v) for v in g[f"{name}_meta"])
+    gate_temp, route_scale, limit = (float(v) for v in g[f"{name}_params"])
+    fmt = FMT[code]
+
+    def terms(tag, wn):
+        return [(g[f"{name}_{tag}_{wn}_packed{i}"], g[f"{name}_{tag}_{wn}_scale{i}"]) for i in range(k_terms)]
+
+    experts = [tuple(terms(f"e{e}", wn) for wn in ("w1", "w2", "w3")) for e in range(E)]
+    shared = tuple(terms("shared", wn) for wn in ("w1", "w2", "w3")) if with_shared else None
+    bias = g[f"{name}_gate_b"] if f"{name}_gate_b" in g.files else None
+    return dict(T=T, hidden=hidden, inter=inter, E=E, topk=topk, group=group, k_terms=k_terms, fmt=fmt, norm=bool(norm),
+                gate_temp=gate_temp, route_scale=route_scale, limit=limit, score_func=str(g[f"{name}_score_func"]), bias=bias,
+                experts=experts, shared=shared, x=O.from_bf16_bits(g[f"{name}_x_bits"]), logits=g[f"{name}_logits"],
+                weights=g[f"{name}_route_weights"], indices=g[f"{name}_route_indices"], y_bits=g[f"{name}_y_bits"])
+
+
+@pytest.mark.parametrize("name", ["sigmoid", "sqrtsoftplus", "softmax_limit"])
+def test_moe_layer_variants_match_reference(golden, name):
+    """boilerplate/engine/model.py:376-422 with the options the plain fixture leaves off: sigmoid and sqrt-softplus
+    scores, a gate bias (selection only), a temperature, no renormalisation, route_scale, the SwiGLU clamp and the
+    shared expert, each produced by the reference's own V4Model.route / swiglu / moe."""
+    c = variant_case(golden("moe_layer_variants"), name)
+    w, idx = O.route_from_logits(c["logits"], c["topk"], c["route_scale"], c["score_func"], c["bias"], c["gate_temp"], c["norm"])
+    assert np.array_equal(idx, c["indices"])
+    assert np.allclose(w, c["weights"], rtol=1e-5, atol=1e-7)
+    y = O.moe_layer(c["x"], c["weights"], c["indices"], c["experts"], c["hidden"], c["inter"], c["group"], c["fmt"],
+                    swiglu_limit=c["limit"], shared=c["shared"])
+    want = O.from_bf16_bits(c["y_bits"])
+    assert O.rel_fro(y, want) < 2e-3
+    assert np.mean(O.bf16_bits(y) != c["y_bits"]) < 0.02
