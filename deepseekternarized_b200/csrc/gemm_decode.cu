@@ -3,8 +3,8 @@
 //     out[m, n] = row_scale[m] * sum_i sum_g scale_i[e, n, g] * sum_{k in g} x[m, k] * trit_i[e, n, k]
 //
 // Every packed byte crosses HBM once: one thread per CTA streams the 64-row halves of the tiled layout's 8 KB slabs
-// (layout_kernels.cu) into a shared-memory ring with cp.async.bulk + mbarrier, four consumer warps read them from
-// there with 128-bit loads. The multiply-adds are exact integer arithmetic on mma.sync.m16n8k32 (u8 x s8 -> s32)
+// (layout_kernels.cu), two at a time, into a shared-memory ring with cp.async.bulk + mbarrier; four consumer warps
+// read them from there with 128-bit loads. The multiply-adds are exact integer arithmetic on mma.sync.m16n8k32 (u8 x s8 -> s32)
 // fed straight from registers:
 //
 //   A fragment  a weight row's packed word ANDed with a byte-wise 2-bit field mask IS the operand: four u8 digits
@@ -31,7 +31,7 @@
 // Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all warps leave
 // and the kernel records DST_ERR_TIMEOUT in the status word dst_check_device_status reads.
 //
-// Coverage: TQ2 tiled weights, group 128, K % 256 == 0, fp16 scales, bf16 / fp16 / int8 activations, any row
+// Coverage: TQ2 tiled weights, group 128, K % 512 == 0 (a ring slot is two 256-trit superblocks), fp16 scales, bf16 / fp16 / int8 activations, any row
 // count per expert (rows are processed up to 16 at a time; beyond that the weights are streamed again).
 #include "dst_common.cuh"
 
@@ -41,7 +41,9 @@ namespace {
 constexpr int DC_CWARPS = 4;                     // consumer warps, 16 weight rows each
 constexpr int DC_THREADS = (DC_CWARPS + 1) * 32;  // + the producer warp
 constexpr int DC_PART = DC_CWARPS * 16 * 64;      // bytes of one item's share of a slab: 64 rows x 64 B
-constexpr int DC_RING = 6;                        // slots of the slab ring
+constexpr int DC_SLOT_DATA = 2 * DC_PART;         // a ring slot holds the item's share of TWO superblocks (four scale groups)
+constexpr int DC_SLOT = DC_SLOT_DATA + 16;        // ... followed by its own "full" and "empty" mbarriers (one address register serves all)
+constexpr int DC_RING = 4;                        // slots of the slab ring
 constexpr int DC_ZERO = 512;                      // bytes of zeros the lanes without a column read
 constexpr long long DC_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
@@ -71,17 +73,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One try_wait: the thread may be suspended by the hardware for up to the hinted time (nanoseconds) while the phase
+// is incomplete, so a waiting warp takes few issue slots from the warps that have work.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
   return done != 0;
 }
-// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed.
+// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed. BACKOFF sleeps between polls (the
+// producer, which runs slabs ahead of the consumers and has no reason to poll fast).
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
+    if (BACKOFF) __nanosleep(256);
     if (mbar_test(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
@@ -263,19 +270,22 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
 // ------------------------------------------------------------------------------------------ the kernel
 // GS = scale groups that share an MMA's columns (4: one token row per pass, 2: two, 1: four per column block);
 // NB = column blocks (GS == 1 only): 4 NB token rows per pass.
+#ifndef DC_MINB
+#define DC_MINB 4
+#endif
 template <int GS, int NB, typename XT>
-__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? 6 : (NB == 2 ? 4 : 2))
+__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? DC_MINB : (NB == 2 ? 4 : 2))
 decode_kernel(const DecodeParams p) {
   constexpr int MT = 4 * NB / GS;  // token rows per pass
   constexpr int TPB = 4 / GS;      // token rows per column block
   extern __shared__ __align__(128) uint8_t dsm[];
-  uint8_t* ring = dsm;                                           // DC_RING x DC_PART
-  uint8_t* zero = ring + DC_RING * DC_PART;                      // DC_ZERO
+  uint8_t* ring = dsm;                                           // DC_RING x DC_SLOT: [two parts][full barrier][empty barrier]
+  uint8_t* zero = ring + DC_RING * DC_SLOT;                      // DC_ZERO
   uint8_t* xs = zero + DC_ZERO;                                  // 2 MT staged rows
   int* xsum4 = reinterpret_cast<int*>(xs + (size_t)2 * MT * p.xstride);  // [MT][G]
   float* xexp = reinterpret_cast<float*>(xsum4 + MT * p.G);      // [MT]
   float* xinv = xexp + MT;                                       // [MT][DC_CWARPS] partial row maxima
-  __shared__ uint64_t bar_full[DC_RING], bar_empty[DC_RING], bar_stage;
+  __shared__ uint64_t bar_stage;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -283,8 +293,8 @@ decode_kernel(const DecodeParams p) {
   if (threadIdx.x == 0) {
     abort_s = 0;
     for (int s = 0; s < DC_RING; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);           // the producer's expect_tx arrive
-      mbar_init(smem_u32(&bar_empty[s]), DC_CWARPS);  // one arrive per consumer warp
+      mbar_init(smem_u32(ring + s * DC_SLOT + DC_SLOT_DATA), 1);                   // full: the producer's expect_tx arrive
+      mbar_init(smem_u32(ring + s * DC_SLOT + DC_SLOT_DATA + 8), DC_CWARPS * 32);  // empty: one arrive per consumer thread
     }
     mbar_init(smem_u32(&bar_stage), DC_CWARPS);       // the consumer warps' own barrier (bounded, unlike bar.sync)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -299,7 +309,8 @@ decode_kernel(const DecodeParams p) {
   if (warp == DC_CWARPS) {
     // ------------------------------------------------------------------ producer: packed slabs -> ring
     if (lane == 0) {
-      uint32_t slot = 0, ph = 0;
+      const uint32_t ring_a = smem_u32(ring), ring_end = ring_a + DC_RING * DC_SLOT;
+      uint32_t sbase = ring_a, ph = 0;
       bool ok = true;
       for (long long item = i0; ok && item < i1; ++item) {
         const Item it = item_of(p, item);
@@ -307,12 +318,15 @@ decode_kernel(const DecodeParams p) {
         const int64_t off0 = (((int64_t)it.e * p.NT + it.nt) * p.S) * 8192 + it.half * DC_PART;
         for (int ps = 0; ok && ps < passes; ++ps)
           for (int term = 0; ok && term < p.n_terms; ++term)
-            for (int sb = 0; sb < p.S; ++sb) {
-              if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) { ok = false; break; }
-              const uint32_t full = smem_u32(&bar_full[slot]);
-              mbar_arrive_expect_tx(full, DC_PART);
-              bulk_load(smem_u32(ring + slot * DC_PART), p.tiled[term] + off0 + (int64_t)sb * 8192, DC_PART, full);
-              if (++slot == DC_RING) { slot = 0; ph ^= 1u; }
+            for (int sb = 0; sb < p.S; sb += 2) {
+              if (!mbar_wait<true>(sbase + DC_SLOT_DATA + 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+              const uint32_t full = sbase + DC_SLOT_DATA;
+              mbar_arrive_expect_tx(full, DC_SLOT_DATA);
+              const uint8_t* src = p.tiled[term] + off0 + (int64_t)sb * 8192;
+              bulk_load(sbase, src, DC_PART, full);
+              bulk_load(sbase + DC_PART, src + 8192, DC_PART, full);
+              sbase += DC_SLOT;
+              if (sbase == ring_end) { sbase = ring_a; ph ^= 1u; }
             }
       }
     }
@@ -325,8 +339,8 @@ decode_kernel(const DecodeParams p) {
     // B column of this lane: pair g8 / 2, part g8 & 1; C columns of this lane: pair c
     const int col_pair = g8 >> 1, col_part = g8 & 1;
     const int tok_c = c / GS, slot_c = c % GS;  // (+ b * TPB) the token and the group slot of this lane's C columns
-    uint32_t slot = 0, ph = 0, stage_ph = 0;
-    bool ok = true;
+    const uint32_t ring_end = ring_a + DC_RING * DC_SLOT;
+    uint32_t sbase = ring_a, ph = 0, stage_ph = 0;  // the current ring slot and the parity of its "full" phase
     int staged_e = -1;
     int64_t staged_m0 = -1;
     auto consumer_sync = [&]() -> bool {
@@ -338,16 +352,16 @@ decode_kernel(const DecodeParams p) {
       return r;
     };
 
-    for (long long item = i0; ok && item < i1; ++item) {
+    for (long long item = i0; item < i1; ++item) {
       const Item it = item_of(p, item);
       const int n_lo = it.nt * 128 + it.half * 64 + warp * 16 + g8, n_hi = n_lo + 8;
-      for (int64_t m0 = it.ra; ok && m0 < it.rb; m0 += MT) {
+      for (int64_t m0 = it.ra; m0 < it.rb; m0 += MT) {
         const int mc = (int)(it.rb - m0 < MT ? it.rb - m0 : MT);
         if (staged_e != it.e || staged_m0 != m0) {
           // every consumer is done with the previous rows; then stage; then everyone sees the new ones
-          ok = consumer_sync() && stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, xsum4, xexp, xinv, consumer_sync) &&
-               consumer_sync();
-          if (!ok) break;
+          if (!(consumer_sync() && stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, xsum4, xexp, xinv, consumer_sync) &&
+                consumer_sync()))
+            goto aborted;
           staged_e = it.e;
           staged_m0 = m0;
         }
@@ -367,7 +381,7 @@ decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int b = 0; b < NB; ++b) y[b][0] = y[b][1] = 0.f;
 
-        for (int term = 0; ok && term < p.n_terms; ++term) {
+        for (int term = 0; term < p.n_terms; ++term) {
           const __half* s_lo = p.scale[term] + ((int64_t)it.e * p.N + (n_lo < p.N ? n_lo : 0)) * p.G;
           const __half* s_hi = p.scale[term] + ((int64_t)it.e * p.N + (n_hi < p.N ? n_hi : 0)) * p.G;
           int accA[NB][4], accB[NB][4];
@@ -395,18 +409,19 @@ decode_kernel(const DecodeParams p) {
             }
           };
 
-          // superblocks two at a time, so that the phase of every group (group % GS) is a compile-time value
-          for (int sb0 = 0; ok && sb0 < p.S; sb0 += 2) {
+          // two superblocks (one ring slot, four scale groups) per iteration: the phase of every group (group % GS) is a
+          // compile-time value, and the barrier traffic and slot arithmetic are paid once per 2 KB of this warp's rows
+          for (int sb0 = 0; sb0 < p.S; sb0 += 2) {
+            if (!mbar_wait(sbase + DC_SLOT_DATA, ph, abort_flag)) goto aborted;
+            const uint32_t sa = sbase + a_off;
+            const uint4 w_lo2[2] = {lds128(sa), lds128(sa + DC_PART)}, w_hi2[2] = {lds128(sa + 512), lds128(sa + DC_PART + 512)};
+            mbar_arrive(sbase + DC_SLOT_DATA + 8);  // every lane arrives for itself: its four loads above are done
+            sbase += DC_SLOT;
+            if (sbase == ring_end) { sbase = ring_a; ph ^= 1u; }
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const int sb = sb0 + u;
-              if (sb >= p.S || !ok) continue;
-              if (!mbar_wait(smem_u32(&bar_full[slot]), ph, abort_flag)) { ok = false; continue; }
-              const uint32_t sa = ring_a + slot * DC_PART + a_off;
-              const uint4 w_lo = lds128(sa), w_hi = lds128(sa + 512);
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
-              if (++slot == DC_RING) { slot = 0; ph ^= 1u; }
+              const uint4 w_lo = w_lo2[u], w_hi = w_hi2[u];
 #pragma unroll
               for (int gi = 0; gi < 2; ++gi) {
                 constexpr uint32_t M1 = 0x03030303u, M4 = 0x0c0c0c0cu;
@@ -414,32 +429,25 @@ decode_kernel(const DecodeParams p) {
                 const bool fresh = phase == 0;         // first group of an epilogue block: the accumulators restart
                 const uint32_t l0 = gi ? w_lo.z : w_lo.x, l1 = gi ? w_lo.w : w_lo.y, h0 = gi ? w_hi.z : w_hi.x, h1 = gi ? w_hi.w : w_hi.y;
                 const uint32_t l0s = l0 >> 4, l1s = l1 >> 4, h0s = h0 >> 4, h1s = h1 >> 4;
-                const uint32_t a[4][4] = {{l0 & M1, h0 & M1, l1 & M1, h1 & M1},
-                                          {l0 & M4, h0 & M4, l1 & M4, h1 & M4},
-                                          {l0s & M1, h0s & M1, l1s & M1, h1s & M1},
-                                          {l0s & M4, h0s & M4, l1s & M4, h1s & M4}};
 #pragma unroll
                 for (int b = 0; b < NB; ++b) {
                   const uint32_t ba = bbase[b][phase] + (uint32_t)sb * bstep[b][phase] + (uint32_t)gi * 128u;
                   const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
                   if (fresh) {
-                    mma_u8s8<true>(accA[b], a[0][0], a[0][1], a[0][2], a[0][3], q0.x, q0.y);
-                    mma_u8s8<true>(accB[b], a[1][0], a[1][1], a[1][2], a[1][3], q0.z, q0.w);
+                    mma_u8s8<true>(accA[b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
+                    mma_u8s8<true>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
                   } else {
-                    mma_u8s8<false>(accA[b], a[0][0], a[0][1], a[0][2], a[0][3], q0.x, q0.y);
-                    mma_u8s8<false>(accB[b], a[1][0], a[1][1], a[1][2], a[1][3], q0.z, q0.w);
+                    mma_u8s8<false>(accA[b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
+                    mma_u8s8<false>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
                   }
-                  mma_u8s8<false>(accA[b], a[2][0], a[2][1], a[2][2], a[2][3], q1.x, q1.y);
-                  mma_u8s8<false>(accB[b], a[3][0], a[3][1], a[3][2], a[3][3], q1.z, q1.w);
+                  mma_u8s8<false>(accA[b], l0s & M1, h0s & M1, l1s & M1, h1s & M1, q1.x, q1.y);
+                  mma_u8s8<false>(accB[b], l0s & M4, h0s & M4, l1s & M4, h1s & M4, q1.z, q1.w);
                 }
                 if (phase == GS - 1) epilogue(sb * 2 + gi - (GS - 1));
               }
             }
           }
-          // K of an odd number of superblocks with four groups per block: the last block holds two groups
-          if (GS == 4 && ok && (p.S & 1)) epilogue(p.G - 2);
         }
-        if (!ok) break;
         // the quad's lanes hold the partial sums of their group slots
 #pragma unroll
         for (int b = 0; b < NB; ++b)
@@ -475,6 +483,7 @@ decode_kernel(const DecodeParams p) {
         }
       }
     }
+  aborted:;  // a bounded wait gave up (the abort flag is up): leave without touching anything else
   }
 
   // ------------------------------------------------------------------ teardown
@@ -490,7 +499,7 @@ decode_kernel(const DecodeParams p) {
 template <int GS, int NB, typename XT>
 int launch_one(const DecodeParams& p, int sms, cudaStream_t stream) {
   constexpr int MT = 4 * NB / GS;
-  const size_t smem = (size_t)DC_RING * DC_PART + DC_ZERO + (size_t)2 * MT * p.xstride + (size_t)MT * p.G * 4 + (size_t)MT * 4 * (1 + DC_CWARPS);
+  const size_t smem = (size_t)DC_RING * DC_SLOT + DC_ZERO + (size_t)2 * MT * p.xstride + (size_t)MT * p.G * 4 + (size_t)MT * 4 * (1 + DC_CWARPS);
   if (smem > 220 * 1024) return DST_ERR_UNSUPPORTED;
   auto kernel = decode_kernel<GS, NB, XT>;
   DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -519,9 +528,9 @@ int launch_rows(const DecodeParams& p, int64_t rows_hint, int sms, cudaStream_t 
 
 bool decode_supports(const GemmArgs& a) {
   if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
-  return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 256 == 0 &&
+  return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 512 == 0 &&
          a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16 || a.act_dtype == DST_ACT_I8) &&
-         (size_t)DC_RING * DC_PART + DC_ZERO + (size_t)16 * (a.K + 64) + (size_t)8 * (a.G + 8) * 4 <= 220 * 1024 &&
+         (size_t)DC_RING * DC_SLOT + DC_ZERO + (size_t)16 * (a.K + 64) + (size_t)8 * (a.G + 8) * 4 <= 220 * 1024 &&
          a.T < (int64_t(1) << 31);
 }
 

@@ -22,9 +22,9 @@ DEV = "cuda"
 
 def fast_algos(K, group, scale_dtype=np.float16, fmt="tq1"):
     """Kernels that must accept a shape: the tcgen05 kernel and the TQ1 decode GEMV cover group 128, K % 128 == 0,
-    fp16 scales; the TQ2 decode GEMV additionally needs K % 256 == 0."""
+    fp16 scales; the TQ2 decode GEMV additionally needs K % 512 == 0."""
     ok = group == 128 and K % 128 == 0 and scale_dtype == np.float16
-    return ["generic", "auto"] + (["prefill"] if ok else []) + (["decode"] if ok and (fmt == "tq1" or K % 256 == 0) else [])
+    return ["generic", "auto"] + (["prefill"] if ok else []) + (["decode"] if ok and (fmt == "tq1" or K % 512 == 0) else [])
 
 
 @pytest.fixture(scope="module")
