@@ -23,6 +23,16 @@ namespace {
 struct PeerPtrs {
   void* p[DST_MAX_PEERS];
 };
+// Entry d of a by-value parameter table. Indexing the array with a run-time value would make the compiler copy the
+// whole table into every thread's local memory (measured: 384 bytes of stack per thread made the push kernel 7x
+// slower than its single-GPU counterpart); a chain of selects over compile-time indices reads the constant bank.
+__device__ __forceinline__ void* peer_ptr(const PeerPtrs& t, int d) {
+  void* r = t.p[0];
+#pragma unroll
+  for (int i = 1; i < DST_MAX_PEERS; ++i)
+    if (d == i) r = t.p[i];
+  return r;
+}
 
 __device__ __forceinline__ void bf16x8_to_float(const uint4& q, float* f) {
   const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -44,22 +54,36 @@ __device__ __forceinline__ int expert_of_row(const int64_t* __restrict__ offsets
   return lo;
 }
 
+// One thread per sorted row: the rank that owns its expert and its row in that rank's receive buffer, packed as
+// (rank << 48) | row; -1 for rows past the last expert's range (ids the routing sort dropped). Doing the search here,
+// once, in parallel, keeps a chain of dependent loads out of every block of the push kernel.
+__global__ void ep_row_dest_kernel(const int64_t* __restrict__ offsets, const int64_t* __restrict__ dst_start, int64_t n_rows, int E, int El,
+                                   int64_t* __restrict__ dest) {
+  const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (p >= n_rows) return;
+  if (p >= offsets[E]) {
+    dest[p] = -1;
+    return;
+  }
+  const int g = expert_of_row(offsets, E, p);
+  dest[p] = ((int64_t)(g / El) << 48) | (dst_start[g] + (p - offsets[g]));
+}
+
 template <int J>  // 16-byte chunks per thread: rows of K <= 2048 J elements
 __global__ void __launch_bounds__(256)
-ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ order, const int64_t* __restrict__ offsets,
-               const float* __restrict__ route_weights, const int64_t* __restrict__ dst_start, int E, int El, int top_k, int64_t K,
-               PeerPtrs rows, PeerPtrs fac, PeerPtrs wts) {
+ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ order, const int64_t* __restrict__ dest,
+               const float* __restrict__ route_weights, const int64_t* __restrict__ first_row, int top_k, int64_t K, PeerPtrs rows,
+               PeerPtrs fac, PeerPtrs wts) {
   __shared__ float red[32];
-  __shared__ int64_t s_dst[2];
-  const int64_t p = blockIdx.x;
-  if (p >= offsets[E]) return;  // rows past the last expert's range belong to ids the routing sort dropped
+  // Blocks walk the sorted rows starting at *first_row (the rows of the rank after this one) and wrap around: the
+  // rows are sorted by destination rank, and with every rank starting at rank 0's rows all of them would store into
+  // the same GPU at the same time (measured at 8 ranks: 300 GB/s per sender instead of the link's 770).
+  int64_t p = (int64_t)blockIdx.x + (first_row ? *first_row : 0);
+  if (p >= (int64_t)gridDim.x) p -= (int64_t)gridDim.x;
+  const int64_t dst = dest[p];
+  if (dst < 0) return;  // a row of an id the routing sort dropped
   int64_t slot = order[p];
   slot = slot < 0 ? 0 : (slot >= (int64_t)gridDim.x ? (int64_t)gridDim.x - 1 : slot);  // never leaves the token rows
-  if (threadIdx.x == 0) {
-    const int g = expert_of_row(offsets, E, p);
-    s_dst[0] = g / El;
-    s_dst[1] = dst_start[g] + (p - offsets[g]);
-  }
   const uint4* s = reinterpret_cast<const uint4*>(x + (slot / top_k) * K);
   const int chunks = (int)(K >> 3);
   float v[J][8];
@@ -73,7 +97,7 @@ ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ 
       for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
     }
   }
-  // block maximum (also publishes s_dst)
+  // block maximum
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
@@ -86,9 +110,9 @@ ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ 
     ex -= 8;  // amax * 2^-ex in [128, 256)
   }
   const float down = ldexpf(1.f, -ex);
-  const int d = (int)s_dst[0];
-  const int64_t dr = s_dst[1];
-  uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(rows.p[d]) + dr * K);
+  const int d = (int)(dst >> 48);
+  const int64_t dr = dst & ((int64_t(1) << 48) - 1);
+  uint4* out = reinterpret_cast<uint4*>(static_cast<__half*>(peer_ptr(rows, d)) + dr * K);
 #pragma unroll
   for (int j = 0; j < J; ++j) {
     const int c = threadIdx.x + j * 256;
@@ -103,8 +127,8 @@ ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ 
     }
   }
   if (threadIdx.x == 0) {
-    static_cast<float*>(fac.p[d])[dr] = ldexpf(1.f, ex);
-    static_cast<float*>(wts.p[d])[dr] = route_weights[slot];
+    static_cast<float*>(peer_ptr(fac, d))[dr] = ldexpf(1.f, ex);
+    static_cast<float*>(peer_ptr(wts, d))[dr] = route_weights[slot];
   }
 }
 
@@ -124,27 +148,32 @@ ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t*
                   const int64_t* __restrict__ dst_start, int E, int El, int top_k, int64_t hidden, const __nv_bfloat16* __restrict__ add,
                   __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
-  const __nv_bfloat16* src[8];
-  int eid[8];
-  for (int s = 0; s < top_k; ++s) {
-    const int g = ids[t * top_k + s];
-    const int64_t p = inv[t * top_k + s];
-    eid[s] = g;
-    const bool ok = g >= 0 && g < E && p >= 0;
-    src[s] = ok ? static_cast<const __nv_bfloat16*>(down.p[g / El]) + (dst_start[g] + (p - offsets[g])) * hidden : nullptr;
-  }
-  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
-    const int e = eid[i];
-    const __nv_bfloat16* q = src[i];
-    int j = i - 1;
-    while (j >= 0 && eid[j] > e) {
-      eid[j + 1] = eid[j];
-      src[j + 1] = src[j];
-      --j;
+  __shared__ const __nv_bfloat16* src[8];
+  if (threadIdx.x == 0) {  // one thread sorts: arrays indexed at run time live in local memory
+    const __nv_bfloat16* sp[8];
+    int eid[8];
+    for (int s = 0; s < top_k; ++s) {
+      const int g = ids[t * top_k + s];
+      const int64_t p = inv[t * top_k + s];
+      eid[s] = g;
+      const bool ok = g >= 0 && g < E && p >= 0;
+      sp[s] = ok ? static_cast<const __nv_bfloat16*>(peer_ptr(down, g / El)) + (dst_start[g] + (p - offsets[g])) * hidden : nullptr;
     }
-    eid[j + 1] = e;
-    src[j + 1] = q;
+    for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
+      const int e = eid[i];
+      const __nv_bfloat16* q = sp[i];
+      int j = i - 1;
+      while (j >= 0 && eid[j] > e) {
+        eid[j + 1] = eid[j];
+        sp[j + 1] = sp[j];
+        --j;
+      }
+      eid[j + 1] = e;
+      sp[j + 1] = q;
+    }
+    for (int s = 0; s < top_k; ++s) src[s] = sp[s];
   }
+  __syncthreads();
   const int chunks = (int)(hidden >> 3);
   for (int c = threadIdx.x; c < chunks; c += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -171,6 +200,33 @@ ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t*
   }
 }
 
+// Placement of this rank's routed rows in their owners' buffers, from every rank's routing-sort offsets over the
+// global experts (offsets_all [W][E + 1], the all-gathered `offsets` arrays). One block; thread g handles expert g:
+//   dst_start[g]      = rows of the owner's earlier experts from all ranks + rows of expert g from lower ranks
+//   offsets_local[i]  = row offsets of THIS rank's own experts in its receive buffer (the grouped GEMM's offsets)
+__global__ void ep_placement_kernel(const int64_t* __restrict__ offsets_all, int W, int E, int El, int rank,
+                                    int64_t* __restrict__ dst_start, int64_t* __restrict__ offsets_local) {
+  extern __shared__ int64_t tot[];  // [E] rows of expert g from all ranks
+  for (int g = threadIdx.x; g < E; g += blockDim.x) {
+    int64_t t = 0;
+    for (int r = 0; r < W; ++r) t += offsets_all[(int64_t)r * (E + 1) + g + 1] - offsets_all[(int64_t)r * (E + 1) + g];
+    tot[g] = t;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < E; g += blockDim.x) {
+    const int first = (g / El) * El;
+    int64_t base = 0;
+    for (int j = first; j < g; ++j) base += tot[j];
+    int64_t before = 0;
+    for (int r = 0; r < rank; ++r) before += offsets_all[(int64_t)r * (E + 1) + g + 1] - offsets_all[(int64_t)r * (E + 1) + g];
+    dst_start[g] = base + before;
+    if (g / El == rank) {
+      offsets_local[g - first] = base;
+      if (g == first + El - 1) offsets_local[El] = base + tot[g];
+    }
+  }
+}
+
 bool fill_peers(PeerPtrs& out, const void* const* ptrs, int world) {
   for (int i = 0; i < DST_MAX_PEERS; ++i) out.p[i] = nullptr;
   for (int i = 0; i < world; ++i) {
@@ -185,15 +241,27 @@ bool fill_peers(PeerPtrs& out, const void* const* ptrs, int world) {
 
 using namespace dst;
 
+extern "C" int dst_ep_placement(const int64_t* offsets_all, int world, int64_t E, int64_t experts_per_rank, int rank, int64_t* dst_start,
+                                int64_t* offsets_local, dst_stream_t stream) {
+  if (world < 1 || world > DST_MAX_PEERS || E <= 0 || experts_per_rank <= 0 || rank < 0 || rank >= world) return DST_ERR_BAD_ARG;
+  if (E > 4096 || experts_per_rank * world != E) return DST_ERR_BAD_SHAPE;  // the per-expert totals live in shared memory
+  if (!offsets_all || !dst_start || !offsets_local) return DST_ERR_BAD_ARG;
+  ep_placement_kernel<<<1, 512, (size_t)E * sizeof(int64_t), static_cast<cudaStream_t>(stream)>>>(
+      offsets_all, world, (int)E, (int)experts_per_rank, rank, dst_start, offsets_local);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
 extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
                                 const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
                                 const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
-                                int world, dst_stream_t stream) {
-  if (n_rows < 0 || E <= 0 || experts_per_rank <= 0 || top_k <= 0 || K <= 0 || world < 1 || world > DST_MAX_PEERS) return DST_ERR_BAD_ARG;
+                                int world, int rank, int64_t* row_dest, dst_stream_t stream) {
+  if (n_rows < 0 || E <= 0 || experts_per_rank <= 0 || top_k <= 0 || K <= 0 || world < 1 || world > DST_MAX_PEERS || rank < 0 || rank >= world)
+    return DST_ERR_BAD_ARG;
   if (E > DST_MAX_EXPERTS || experts_per_rank * world < E) return DST_ERR_BAD_SHAPE;
   if (K % 8 != 0 || K > 8192) return DST_ERR_UNSUPPORTED;
   if (n_rows == 0) return DST_OK;
-  if (!x_bf16 || !order || !offsets || !route_weights || !dst_start || !peer_rows_f16 || !peer_row_factor || !peer_row_weight)
+  if (!x_bf16 || !order || !offsets || !route_weights || !dst_start || !peer_rows_f16 || !peer_row_factor || !peer_row_weight || !row_dest)
     return DST_ERR_BAD_ARG;
   if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
@@ -202,12 +270,17 @@ extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const 
     return DST_ERR_ALIGNMENT;
   auto st = static_cast<cudaStream_t>(stream);
   auto xp = static_cast<const __nv_bfloat16*>(x_bf16);
+  ep_row_dest_kernel<<<(unsigned)cdiv64(n_rows, 256), 256, 0, st>>>(offsets, dst_start, n_rows, (int)E, (int)experts_per_rank, row_dest);
+  DST_CUDA_TRY(cudaGetLastError());
+  // start at the rows of the next rank's first expert (offsets[that expert] <= n_rows; beyond the experts: row 0)
+  const int64_t next_first = (int64_t)((rank + 1) % world) * experts_per_rank;
+  const int64_t* first_row = next_first < E ? offsets + next_first : nullptr;
   if (K <= 2048)
-    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
   else if (K <= 4096)
-    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
   else
-    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, offsets, route_weights, dst_start, (int)E, (int)experts_per_rank, top_k, K, rows, fac, wts);
+    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

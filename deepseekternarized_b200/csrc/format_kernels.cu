@@ -51,9 +51,9 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ packed, int64_t N, int
   }
 }
 
-// One block per token row: absmax, then q = clamp(rint(x / s)).
-template <typename XT>
-__global__ void quant_act_kernel(const XT* __restrict__ x, int64_t K, int8_t* __restrict__ q,
+// One block per token row: absmax, then q = clamp(rint(x / s)), stored as int8 or as the same integers in fp16.
+template <typename XT, typename QT>
+__global__ void quant_act_kernel(const XT* __restrict__ x, int64_t K, QT* __restrict__ q,
                                  float* __restrict__ s) {
   __shared__ float red[32];
   const int64_t m = blockIdx.x;
@@ -74,7 +74,7 @@ __global__ void quant_act_kernel(const XT* __restrict__ x, int64_t K, int8_t* __
   for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
     float r = rintf(__fdiv_rn((float)row[k], sc));  // round half to even, as torch.round
     r = fminf(fmaxf(r, -127.f), 127.f);
-    q[m * K + k] = (int8_t)r;
+    q[m * K + k] = (QT)r;  // int8, or the same integer as fp16 (exact: |r| <= 127)
   }
 }
 
@@ -170,9 +170,25 @@ extern "C" int dst_quant_act_int8(const void* x, int x_is_f32, int64_t M, int64_
   if (M > 0x7fffffff) return DST_ERR_BAD_SHAPE;
   auto st = static_cast<cudaStream_t>(stream);
   if (x_is_f32)
-    dst::quant_act_kernel<float><<<(unsigned)M, 256, 0, st>>>(static_cast<const float*>(x), K, q, s);
+    dst::quant_act_kernel<float, int8_t><<<(unsigned)M, 256, 0, st>>>(static_cast<const float*>(x), K, q, s);
   else
-    dst::quant_act_kernel<__nv_bfloat16><<<(unsigned)M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, q, s);
+    dst::quant_act_kernel<__nv_bfloat16, int8_t><<<(unsigned)M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, q, s);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_quant_act_int8_f16(const void* x, int x_is_f32, int64_t M, int64_t K, void* q_f16, float* s,
+                                      dst_stream_t stream) {
+  if (K <= 0 || M < 0) return DST_ERR_BAD_ARG;
+  if (M == 0) return DST_OK;
+  if (!x || !q_f16 || !s) return DST_ERR_BAD_ARG;
+  if (M > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (x_is_f32)
+    dst::quant_act_kernel<float, __half><<<(unsigned)M, 256, 0, st>>>(static_cast<const float*>(x), K, static_cast<__half*>(q_f16), s);
+  else
+    dst::quant_act_kernel<__nv_bfloat16, __half><<<(unsigned)M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K,
+                                                                             static_cast<__half*>(q_f16), s);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

@@ -43,7 +43,13 @@ constexpr int DC_THREADS = (DC_CWARPS + 1) * 32;  // + the producer warp
 constexpr int DC_PART = DC_CWARPS * 16 * 64;      // bytes of one item's share of a slab: 64 rows x 64 B
 constexpr int DC_SLOT_DATA = 2 * DC_PART;         // a ring slot holds the item's share of TWO superblocks (four scale groups)
 constexpr int DC_SLOT = DC_SLOT_DATA + 16;        // ... followed by its own "full" and "empty" mbarriers (one address register serves all)
-constexpr int DC_RING = 4;                        // slots of the slab ring
+#ifndef DC_RING_SLOTS
+#define DC_RING_SLOTS 4
+#endif
+constexpr int DC_RING = DC_RING_SLOTS;            // slots of the slab ring
+#ifndef DC_PRODUCER_SLEEP
+#define DC_PRODUCER_SLEEP true
+#endif
 constexpr int DC_ZERO = 512;                      // bytes of zeros the lanes without a column read
 constexpr long long DC_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
@@ -103,19 +109,21 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// 128-bit shared-memory load from a shared-window address. Not volatile: the compiler may move it among the
+// arithmetic around it; the mbarrier waits and arrives carry memory clobbers, which it does not cross.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
 // d = a * b + c, u8 x s8 -> s32; ZERO: c = 0
 template <bool ZERO>
 __device__ __forceinline__ void mma_u8s8(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   if (ZERO)
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
   else
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
@@ -319,7 +327,7 @@ decode_kernel(const DecodeParams p) {
         for (int ps = 0; ok && ps < passes; ++ps)
           for (int term = 0; ok && term < p.n_terms; ++term)
             for (int sb = 0; sb < p.S; sb += 2) {
-              if (!mbar_wait<true>(sbase + DC_SLOT_DATA + 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+              if (!mbar_wait<DC_PRODUCER_SLEEP>(sbase + DC_SLOT_DATA + 8, ph ^ 1u, abort_flag)) { ok = false; break; }
               const uint32_t full = sbase + DC_SLOT_DATA;
               mbar_arrive_expect_tx(full, DC_SLOT_DATA);
               const uint8_t* src = p.tiled[term] + off0 + (int64_t)sb * 8192;

@@ -326,49 +326,58 @@ gather_rows_norm_vec_kernel(const __nv_bfloat16* __restrict__ src, const int64_t
   if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
 }
 
+// Rows p = blockIdx.x, blockIdx.x + gridDim.x, ... below the row count; the count is n_rows, or the smaller of n_rows and
+// *n_rows_dev when the caller only knows it on the device (expert-parallel steps: rows received from the other ranks).
 template <int J>
 __global__ void __launch_bounds__(256)
 swiglu_norm_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route_weights, const int64_t* __restrict__ order,
-                       int64_t inter, float limit, __half* __restrict__ h, float* __restrict__ factor) {
+                       int64_t n_rows, const int64_t* __restrict__ n_rows_dev, int64_t inter, float limit, __half* __restrict__ h,
+                       float* __restrict__ factor) {
   __shared__ float red[32];
-  const int64_t p = blockIdx.x;
-  const float w = route_weights ? route_weights[order ? clamp_slot(order[p], (int64_t)gridDim.x) : p] : 1.f;
-  const uint4* g = reinterpret_cast<const uint4*>(gu + p * 2 * inter);
-  const uint4* u = reinterpret_cast<const uint4*>(gu + p * 2 * inter + inter);
+  int64_t n = n_rows;
+  if (n_rows_dev) {
+    const int64_t m = *n_rows_dev;
+    n = m < 0 ? 0 : (m < n ? m : n);
+  }
   const int chunks = (int)(inter >> 3);
-  float v[J][8];
-  float amax = 0.f;
+  for (int64_t p = blockIdx.x; p < n; p += gridDim.x) {
+    const float w = route_weights ? route_weights[order ? clamp_slot(order[p], n_rows) : p] : 1.f;
+    const uint4* g = reinterpret_cast<const uint4*>(gu + p * 2 * inter);
+    const uint4* u = reinterpret_cast<const uint4*>(gu + p * 2 * inter + inter);
+    float v[J][8];
+    float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = threadIdx.x + j * 256;
-    if (c < chunks) {
-      float gate[8], up[8];
-      bf16x8_to_float(g[c], gate);
-      bf16x8_to_float(u[c], up);
+    for (int j = 0; j < J; ++j) {
+      const int c = threadIdx.x + j * 256;
+      if (c < chunks) {
+        float gate[8], up[8];
+        bf16x8_to_float(g[c], gate);
+        bf16x8_to_float(u[c], up);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float ga = gate[i], uu = up[i];
-        if (limit > 0.f) {
-          uu = fminf(fmaxf(uu, -limit), limit);
-          ga = fminf(ga, limit);
+        for (int i = 0; i < 8; ++i) {
+          float ga = gate[i], uu = up[i];
+          if (limit > 0.f) {
+            uu = fminf(fmaxf(uu, -limit), limit);
+            ga = fminf(ga, limit);
+          }
+          float x = (ga / (1.f + expf(-ga))) * uu;
+          if (route_weights) x = w * x;
+          x = __bfloat162float(__float2bfloat16_rn(x));  // the reference's rounding point
+          v[j][i] = x;
+          amax = fmaxf(amax, fabsf(x));
         }
-        float x = (ga / (1.f + expf(-ga))) * uu;
-        if (route_weights) x = w * x;
-        x = __bfloat162float(__float2bfloat16_rn(x));  // the reference's rounding point
-        v[j][i] = x;
-        amax = fmaxf(amax, fabsf(x));
       }
     }
-  }
-  const int ex = norm_exponent(block_max(amax, red));
-  const float down = ldexpf(1.f, -ex);
-  uint4* d = reinterpret_cast<uint4*>(h + p * inter);
+    const int ex = norm_exponent(block_max(amax, red));
+    const float down = ldexpf(1.f, -ex);
+    uint4* d = reinterpret_cast<uint4*>(h + p * inter);
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = threadIdx.x + j * 256;
-    if (c < chunks) d[c] = float8_to_f16(v[j], down);
+    for (int j = 0; j < J; ++j) {
+      const int c = threadIdx.x + j * 256;
+      if (c < chunks) d[c] = float8_to_f16(v[j], down);
+    }
+    if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
   }
-  if (threadIdx.x == 0) factor[p] = ldexpf(1.f, ex);
 }
 
 // dst[p, :] = fp16(src[order[p] / top_k, :] * 2^-e_p), factor[p] = 2^e_p; one block per row, K <= 8 * 1024 per thread loop
@@ -430,27 +439,34 @@ __global__ void invert_order_kernel(const int64_t* __restrict__ order, int64_t n
   }
 }
 
-// A token's (position, expert id) pairs in increasing expert id (the ids of one token are distinct); positions that
-// are negative (dropped ids) or beyond the n_pos rows of `down` are marked -1.
+// A token's positions in `down` in increasing expert id (the ids of one token are distinct) -> pos[0 .. top_k) in
+// shared memory; positions that are negative (dropped ids) or beyond the n_pos rows of `down` are marked -1. One
+// thread sorts (its arrays are indexed at run time, so they live in local memory: one thread's worth, not a block's).
 __device__ __forceinline__ void token_slots(const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int64_t t, int top_k,
-                                            int64_t n_pos, int64_t* pos, int* eid) {
-  for (int s = 0; s < top_k; ++s) {
-    const int64_t q = inv[t * top_k + s];
-    pos[s] = (q >= 0 && q < n_pos) ? q : -1;
-    eid[s] = ids[t * top_k + s];
-  }
-  for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id
-    const int e = eid[i];
-    const int64_t q = pos[i];
-    int j = i - 1;
-    while (j >= 0 && eid[j] > e) {
-      eid[j + 1] = eid[j];
-      pos[j + 1] = pos[j];
-      --j;
+                                            int64_t n_pos, int64_t* pos_shared) {
+  if (threadIdx.x == 0) {
+    int64_t pos[8];
+    int eid[8];
+    for (int s = 0; s < top_k; ++s) {
+      const int64_t q = inv[t * top_k + s];
+      pos[s] = (q >= 0 && q < n_pos) ? q : -1;
+      eid[s] = ids[t * top_k + s];
     }
-    eid[j + 1] = e;
-    pos[j + 1] = q;
+    for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id
+      const int e = eid[i];
+      const int64_t q = pos[i];
+      int j = i - 1;
+      while (j >= 0 && eid[j] > e) {
+        eid[j + 1] = eid[j];
+        pos[j + 1] = pos[j];
+        --j;
+      }
+      eid[j + 1] = e;
+      pos[j + 1] = q;
+    }
+    for (int s = 0; s < top_k; ++s) pos_shared[s] = pos[s];
   }
+  __syncthreads();
 }
 
 // One block per token: its top_k rows of `down`, visited in increasing expert id, summed in fp32; then the optional
@@ -459,9 +475,8 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ down, const int
                                const int32_t* __restrict__ ids, int top_k, int64_t hidden, const __nv_bfloat16* __restrict__ add,
                                __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
-  int64_t pos[8];
-  int eid[8];
-  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos, eid);
+  __shared__ int64_t pos[8];
+  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos);
   for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < top_k; ++s)
@@ -476,9 +491,8 @@ __global__ void __launch_bounds__(256)
 combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int top_k,
                    int64_t hidden, const __nv_bfloat16* __restrict__ add, __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
-  int64_t pos[8];
-  int eid[8];
-  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos, eid);
+  __shared__ int64_t pos[8];
+  token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos);
   const int chunks = (int)(hidden >> 3);
   for (int c = threadIdx.x; c < chunks; c += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -682,6 +696,25 @@ extern "C" int dst_gather_rows_norm(const void* src_bf16, const int64_t* order, 
   return DST_OK;
 }
 
+namespace {
+// grid of the row-looping SwiGLU kernel: a block per row up to a few waves, then the blocks walk the rows
+unsigned swiglu_grid(int64_t n_rows, bool count_on_device) {
+  const int64_t cap = count_on_device ? 148 * 8 : 148 * 64;
+  return (unsigned)(n_rows < cap ? n_rows : cap);
+}
+int swiglu_norm_launch(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows, const int64_t* n_rows_dev,
+                       int64_t inter, float limit, void* h_f16, float* row_factor, cudaStream_t st) {
+  auto a = static_cast<const __nv_bfloat16*>(gu_bf16);
+  auto d = static_cast<__half*>(h_f16);
+  const unsigned grid = swiglu_grid(n_rows, n_rows_dev != nullptr);
+  if (inter <= 2048) swiglu_norm_vec_kernel<1><<<grid, 256, 0, st>>>(a, route_weights, order, n_rows, n_rows_dev, inter, limit, d, row_factor);
+  else if (inter <= 4096) swiglu_norm_vec_kernel<2><<<grid, 256, 0, st>>>(a, route_weights, order, n_rows, n_rows_dev, inter, limit, d, row_factor);
+  else swiglu_norm_vec_kernel<4><<<grid, 256, 0, st>>>(a, route_weights, order, n_rows, n_rows_dev, inter, limit, d, row_factor);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+}  // namespace
+
 extern "C" int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
                                int64_t inter, float limit, void* h_f16, float* row_factor, dst_stream_t stream) {
   if (n_rows < 0 || inter <= 0) return DST_ERR_BAD_ARG;
@@ -689,20 +722,24 @@ extern "C" int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, 
   if (!gu_bf16 || !h_f16 || !row_factor) return DST_ERR_BAD_ARG;
   if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
   const bool vec = inter % 8 == 0 && inter <= 8192 && (reinterpret_cast<uintptr_t>(gu_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(h_f16) & 15) == 0;
-  if (vec) {
-    auto st = static_cast<cudaStream_t>(stream);
-    auto a = static_cast<const __nv_bfloat16*>(gu_bf16);
-    auto d = static_cast<__half*>(h_f16);
-    if (inter <= 2048) swiglu_norm_vec_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
-    else if (inter <= 4096) swiglu_norm_vec_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
-    else swiglu_norm_vec_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(a, route_weights, order, inter, limit, d, row_factor);
-    DST_CUDA_TRY(cudaGetLastError());
-    return DST_OK;
-  }
+  if (vec) return swiglu_norm_launch(gu_bf16, route_weights, order, n_rows, nullptr, inter, limit, h_f16, row_factor, static_cast<cudaStream_t>(stream));
   swiglu_norm_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gu_bf16), route_weights, order, inter, limit, static_cast<__half*>(h_f16), row_factor);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
+}
+
+extern "C" int dst_swiglu_norm_dev(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows_max,
+                                   const int64_t* n_rows_dev, int64_t inter, float limit, void* h_f16, float* row_factor,
+                                   dst_stream_t stream) {
+  if (n_rows_max < 0 || inter <= 0) return DST_ERR_BAD_ARG;
+  if (n_rows_max == 0) return DST_OK;
+  if (!gu_bf16 || !h_f16 || !row_factor || !n_rows_dev) return DST_ERR_BAD_ARG;
+  if (n_rows_max > 0x7fffffff) return DST_ERR_BAD_SHAPE;
+  if (inter % 8 != 0 || inter > 8192) return DST_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(gu_bf16) & 15) != 0 || (reinterpret_cast<uintptr_t>(h_f16) & 15) != 0) return DST_ERR_ALIGNMENT;
+  return swiglu_norm_launch(gu_bf16, route_weights, order, n_rows_max, n_rows_dev, inter, limit, h_f16, row_factor,
+                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dst_combine_add(const void* down_bf16, const int64_t* order, const int32_t* ids, int64_t T, int top_k,

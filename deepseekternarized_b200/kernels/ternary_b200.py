@@ -68,10 +68,14 @@ def _require(backend: str):
 class TiledWeights:
     """Packed ternary weights of E experts in the tiled device layout (see ``include/dst_b200.h``):
     a byte permutation of the canonical ``[E, N, packed_cols]`` tensor built once by ``tile_weights``;
-    ``untile`` restores the canonical bytes bit for bit."""
+    ``untile`` restores the canonical bytes bit for bit.
 
-    def __init__(self, data: torch.Tensor, E: int, N: int, K: int, fmt: str):
-        self.data, self.E, self.N, self.K, self.fmt = data, E, N, K, fmt
+    ``decode``: for TQ1 weights, optionally the SAME trits once more as tiled TQ2 (2 bits per trit instead of 1.6:
+    +25 % device bytes for that copy). The TQ2 decode GEMV unpacks four trits with one AND, the TQ1 one needs a table
+    read and ~4.5 integer instructions per byte, so few-row calls are served from this copy when it exists."""
+
+    def __init__(self, data: torch.Tensor, E: int, N: int, K: int, fmt: str, decode: "TiledWeights | None" = None):
+        self.data, self.E, self.N, self.K, self.fmt, self.decode = data, E, N, K, fmt, decode
 
     @property
     def device(self):
@@ -105,10 +109,11 @@ class NormRows:
         return self.data.device
 
 
-def tile_weights(packed: torch.Tensor, fmt: str, K: int) -> TiledWeights:
+def tile_weights(packed: torch.Tensor, fmt: str, K: int, decode_copy: bool = False) -> TiledWeights:
     """Canonical packed weights ``[E, N, packed_cols]`` (or ``[N, packed_cols]``) -> ``TiledWeights``: the one-time
     device re-layout the fast kernels read (the reference copies weights to the device at the same
-    point, ``boilerplate/ternary/ops.py:41-45``)."""
+    point, ``boilerplate/ternary/ops.py:41-45``). ``decode_copy`` (TQ1 with K % 512 == 0 only): also keep the trits
+    as tiled TQ2 for the decode GEMV (see ``TiledWeights.decode``)."""
     code = _fmt_code(fmt)
     lib = _require("auto")
     if packed.dim() == 2:
@@ -121,7 +126,30 @@ def tile_weights(packed: torch.Tensor, fmt: str, K: int) -> TiledWeights:
     data = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=packed.device)
     with torch.cuda.device(packed.device):
         _lib.check(lib.dst_tile_weights(packed.data_ptr(), E, N, K, code, data.data_ptr(), _stream(packed)))
-    return TiledWeights(data, E, N, K, fmt)
+    dec = None
+    if decode_copy and fmt == "tq1" and K % 512 == 0:
+        dec = TiledWeights(_reencode_tq2_tiled(lib, packed, K), E, N, K, "tq2")
+    return TiledWeights(data, E, N, K, fmt, dec)
+
+
+def _reencode_tq2_tiled(lib, packed_tq1: torch.Tensor, K: int) -> torch.Tensor:
+    """Canonical TQ1 ``[E, N, ceil(K/5)]`` -> the tiled TQ2 buffer of the same trits (unpack, pack as TQ2, tile), a few
+    experts at a time so the int8 trits in between stay small."""
+    E, N, _ = packed_tq1.shape
+    dev = packed_tq1.device
+    out = torch.empty(max(int(lib.dst_tiled_bytes(_lib.FMT_TQ2, E, N, K)), 16), dtype=torch.uint8, device=dev)
+    per_expert = int(lib.dst_tiled_bytes(_lib.FMT_TQ2, 1, N, K))
+    step = max(1, (256 << 20) // max(N * K, 1))
+    with torch.cuda.device(dev):
+        st = _stream(packed_tq1)
+        for e0 in range(0, E, step):
+            n = min(step, E - e0)
+            trits = torch.empty(n * N, K, dtype=torch.int8, device=dev)
+            tq2 = torch.empty(n * N, K // 4, dtype=torch.uint8, device=dev)
+            _lib.check(lib.dst_unpack(packed_tq1[e0:e0 + n].data_ptr(), n * N, K, _lib.FMT_TQ1, trits.data_ptr(), st))
+            _lib.check(lib.dst_pack(trits.data_ptr(), n * N, K, _lib.FMT_TQ2, tq2.data_ptr(), st))
+            _lib.check(lib.dst_tile_weights(tq2.data_ptr(), n, N, K, _lib.FMT_TQ2, out[e0 * per_expert:].data_ptr(), st))
+    return out
 
 
 def fast_path_covers(K: int, group: int, scale_dtype, act_dtype=torch.bfloat16) -> bool:
@@ -172,6 +200,10 @@ def _grouped(lib, x, row_scale, offsets, packed_terms, scale_terms, K, group, fm
     if tiled:
         if any(p.K != K or p.fmt != fmt for p in packed_terms):
             raise RuntimeError("inconsistent ternary GEMM shapes")
+        # few rows per expert and a 2-bit copy of the TQ1 trits on the device: the decode GEMV reads that copy
+        if fmt == "tq1" and algo in ("auto", "decode") and act_code != _lib.ACT_F16_NORM and all(p.decode is not None for p in packed_terms) \
+                and x.size(0) <= 16 * packed_terms[0].E:
+            packed_terms, fmt, code, algo = [p.decode for p in packed_terms], "tq2", _lib.FMT_TQ2, "decode"
     elif algo != "generic" and fast_path_covers(K, group, scale_terms[0].dtype, x.dtype) and all(
             p.is_cuda and p.dtype == torch.uint8 and p.dim() == 3 for p in packed_terms) and (
             algo != "auto" or 2 * x.size(0) * packed_terms[0].size(1) * K >= (1 << 28)):

@@ -63,13 +63,15 @@ class ExpertWeights:
     def n_experts(self) -> int:
         return self.w13_packed[0].size(0)
 
-    def prepare(self, drop_canonical: bool = True) -> "ExpertWeights":
+    def prepare(self, drop_canonical: bool = True, decode_copy: bool = False) -> "ExpertWeights":
         """Re-layout the packed weights once into the tiled device layout the fast kernels read
-        (the reference copies weights to the device at this point, ``boilerplate/ternary/ops.py:41-45``)."""
+        (the reference copies weights to the device at this point, ``boilerplate/ternary/ops.py:41-45``).
+        ``decode_copy``: TQ1 weights also keep a tiled TQ2 copy of their trits for decode-sized steps
+        (``kernels.ternary_b200.TiledWeights.decode``)."""
         if not isinstance(self.w13_packed[0], kb.TiledWeights) and kb.fast_path_covers(self.hidden, self.group, self.w13_scale[0].dtype) \
                 and kb.fast_path_covers(self.inter, self.group, self.w2_scale[0].dtype):
-            w13 = [kb.tile_weights(p, self.fmt, self.hidden) for p in self.w13_packed]
-            w2 = [kb.tile_weights(p, self.fmt, self.inter) for p in self.w2_packed]
+            w13 = [kb.tile_weights(p, self.fmt, self.hidden, decode_copy) for p in self.w13_packed]
+            w2 = [kb.tile_weights(p, self.fmt, self.inter, decode_copy) for p in self.w2_packed]
             if not drop_canonical:
                 self.canonical = (self.w13_packed, self.w2_packed)
             self.w13_packed, self.w2_packed = w13, w2
@@ -144,8 +146,17 @@ class B200Ops:
                                             algo=self.algo, out=out, validate_offsets=False)
 
     def swiglu(self, gu: torch.Tensor, row_weights: torch.Tensor | None, order: torch.Tensor | None, inter: int,
-               limit: float, for_weights=None):
+               limit: float, for_weights=None, n_rows_dev: torch.Tensor | None = None):
+        """``n_rows_dev``: a device int64 holding how many of gu's rows exist (the rest is buffer capacity)."""
         lib = self._lib()
+        if n_rows_dev is not None:
+            h = torch.empty(gu.size(0), inter, dtype=torch.float16, device=gu.device)
+            fac = torch.empty(gu.size(0), dtype=torch.float32, device=gu.device)
+            with torch.cuda.device(gu.device):
+                _lib.check(lib.dst_swiglu_norm_dev(gu.data_ptr(), row_weights.data_ptr() if row_weights is not None else None,
+                                                   order.data_ptr() if order is not None else None, gu.size(0), n_rows_dev.data_ptr(), inter,
+                                                   ctypes.c_float(limit), h.data_ptr(), fac.data_ptr(), kb._stream(gu)))
+            return kb.NormRows(h, fac)
         if for_weights is not None and self._norm_ok(for_weights, gu.size(0)):
             h = torch.empty(gu.size(0), inter, dtype=torch.float16, device=gu.device)
             fac = torch.empty(gu.size(0), dtype=torch.float32, device=gu.device)
@@ -256,12 +267,17 @@ class MoELayer:
         down = self.ops.gemm(h, offsets, w.w2_packed, w.w2_scale, w.inter, w.group, w.fmt)
         return self.ops.combine_weighted(down, order, ids, weights, T, self.top_k)
 
-    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order, out=None, weights=None) -> torch.Tensor:
+    def experts_forward(self, xs: torch.Tensor, offsets: torch.Tensor, row_weights, order, out=None, weights=None,
+                        n_rows_dev=None) -> torch.Tensor:
         """Rows sorted by expert -> w2(bf16(weight * silu(w1 x) * w3 x)) as bf16 rows (into ``out`` if given).
-        ``weights``: the experts to run (default: the routed ones); ``offsets`` None = one expert over all rows."""
+        ``weights``: the experts to run (default: the routed ones); ``offsets`` None = one expert over all rows;
+        ``n_rows_dev``: device int64 with the number of rows that exist when ``xs`` is a buffer of larger capacity
+        (the grouped GEMMs follow ``offsets``, whose last entry is that number)."""
         w = self.w if weights is None else weights
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
-        if getattr(self.ops, "fused_norm", False):
+        if n_rows_dev is not None:
+            h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit, n_rows_dev=n_rows_dev)
+        elif getattr(self.ops, "fused_norm", False):
             h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit, for_weights=w.w2_packed)
         else:
             h = self.ops.swiglu(gu, row_weights, order, w.inter, self.swiglu_limit)
@@ -434,26 +450,37 @@ class ExpertParallelMoE:
                                "at or below the first step's largest")
         buf = self._peer[self._step & 1]  # two sets: a peer may still read last step's outputs while this step pushes
         self._step += 1
+        ev = self._phase_events()
         order, offsets = self.ops.sort(ids, self.E)
-        counts = offsets.diff().to(torch.int64).contiguous()
-        counts_all = torch.empty(W, self.E, dtype=torch.int64, device=x.device)
-        dist.all_gather_into_tensor(counts_all, counts, group=self.pg)
-        dst_start, offsets2 = ep_placement(counts_all, self.rank, El)
-        R = int(offsets2[-1].item())  # the one host sync of the step
-        self.last_dispatch_rows = R
+        ev("route+sort")
+        # every rank's offsets over the global experts -> where my rows go, and my own experts' row offsets: no host step
+        offs_all = torch.empty(W, self.E + 1, dtype=torch.int64, device=x.device)
+        dist.all_gather_into_tensor(offs_all, offsets, group=self.pg)
+        dst_start = torch.empty(self.E, dtype=torch.int64, device=x.device)
+        offsets2 = torch.empty(El + 1, dtype=torch.int64, device=x.device)
+        row_dest = torch.empty(order.numel(), dtype=torch.int64, device=x.device)
         x = x.contiguous()
         wflat = weights.reshape(-1).contiguous()
         with torch.cuda.device(x.device):
+            _lib.check(lib.dst_ep_placement(offs_all.data_ptr(), W, self.E, El, self.rank, dst_start.data_ptr(), offsets2.data_ptr(),
+                                            kb._stream(x)))
+            ev("offsets all-gather+placement")
             _lib.check(lib.dst_ep_push_rows(x.data_ptr(), order.data_ptr(), offsets.data_ptr(), wflat.data_ptr(), dst_start.data_ptr(),
                                             order.numel(), self.E, El, self.top_k, hidden, buf.ptrs["rows"], buf.ptrs["fac"],
-                                            buf.ptrs["wts"], W, kb._stream(x)))
-        getattr(self.ops, "count", lambda n: None)(3)  # kernels launched here rather than through ops (push, invert, combine)
+                                            buf.ptrs["wts"], W, self.rank, row_dest.data_ptr(), kb._stream(x)))
+        getattr(self.ops, "count", lambda n: None)(5)  # kernels launched here rather than through ops (placement, row destinations, push, invert, combine)
+        ev("push")
         dist.all_reduce(self._sync, group=self.pg)  # every rank's rows have landed
-        if R > 0:
-            xs2 = kb.NormRows(buf.rows[:R], buf.fac[:R])
-            self.local.experts_forward(xs2, offsets2, buf.wts[:R], None, out=buf.down[:R])
+        ev("barrier")
+        # the received rows: the buffers' whole capacity goes to the kernels, the row count stays on the device
+        # (offsets2[-1]); the grouped GEMMs follow offsets2, the SwiGLU kernel reads the count
+        self.last_dispatch_rows = offsets2[-1:]
+        xs2 = kb.NormRows(buf.rows, buf.fac)
+        self.local.experts_forward(xs2, offsets2, buf.wts, None, out=buf.down, n_rows_dev=offsets2[-1:])
         shared = self.local.shared_forward(x)  # this rank's tokens through the (replicated) shared expert
+        ev("expert GEMMs+SwiGLU")
         dist.all_reduce(self._sync, group=self.pg)  # every rank's expert outputs are written
+        ev("barrier 2")
         inv = torch.empty(T * self.top_k, dtype=torch.int64, device=x.device)
         y = torch.empty(T, hidden, dtype=torch.bfloat16, device=x.device)
         ids32 = ids.reshape(-1).to(torch.int32).contiguous()
@@ -461,7 +488,36 @@ class ExpertParallelMoE:
             _lib.check(lib.dst_ep_combine_pull_add(buf.ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(),
                                                    dst_start.data_ptr(), T, El, self.top_k, hidden, inv.data_ptr(),
                                                    shared.data_ptr() if shared is not None else None, y.data_ptr(), W, kb._stream(x)))
+        ev("combine-pull")
         return y
+
+    def _phase_events(self):
+        """With ``profile_phases`` on, returns a function that records a CUDA event after each named phase of a step
+        (``phase_log``: one [(name, event)] list per step, the first entry being the step's start)."""
+        if not getattr(self, "profile_phases", False):
+            return lambda name: None
+        log = [("start", torch.cuda.Event(enable_timing=True))]
+        log[0][1].record()
+        if not hasattr(self, "phase_log"):
+            self.phase_log = []
+        self.phase_log.append(log)
+
+        def mark(name):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            log.append((name, e))
+
+        return mark
+
+    def phases_ms(self) -> dict:
+        """Median milliseconds per phase over the logged steps (call after a synchronize); empties the log."""
+        steps = getattr(self, "phase_log", [])
+        out: dict = {}
+        for log in steps:
+            for (_, a), (name, b) in zip(log[:-1], log[1:]):
+                out.setdefault(name, []).append(a.elapsed_time(b))
+        self.phase_log = []
+        return {k: float(sorted(v)[len(v) // 2]) for k, v in out.items()}
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """x [T, hidden] bf16 and the gate's logits over the GLOBAL experts [T, E] -> y [T, hidden] bf16."""

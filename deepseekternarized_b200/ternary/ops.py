@@ -4,8 +4,9 @@ reference's ``boilerplate/ternary/ops.py`` (``quant_act_int8``, ``PackedTerm``, 
 The engines hold one ``TernaryLinear`` per weight (reference ``engine/model.py:361-370``,
 ``engine/standard.py:37-42``) and call it with activations of any leading shape. Here every call
 is one CUDA launch that sums all stacked terms; ``act="bf16"`` feeds bf16 activations with fp16
-group scales and fp32 accumulation, ``act="int8"`` quantises per token first (one more kernel) and
-follows the reference's int8 contract. There is no CPU or dequantised fallback.
+group scales and fp32 accumulation, ``act="int8"`` quantises per token first (one more kernel, which
+for many rows writes the tensor-core kernel's input format directly) and follows the reference's int8
+contract. Both modes keep their weights in the tiled device layout. There is no CPU or dequantised fallback.
 """
 
 from __future__ import annotations
@@ -19,8 +20,9 @@ from ..kernels import ternary_b200 as kb
 from .pack import unpack
 
 
-def quant_act_int8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """Per-token absmax int8: x ~= q * s, q in [-127, 127] (reference ``ops.py:20-25``), one kernel."""
+def quant_act_int8(x: torch.Tensor, as_f16: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token absmax int8: x ~= q * s, q in [-127, 127] (reference ``ops.py:20-25``), one kernel.
+    ``as_f16``: q comes back as fp16 holding the same integers, the row format the tcgen05 GEMM reads directly."""
     lib = kb._require("auto")
     if not x.is_cuda:
         raise RuntimeError("B200 ternary kernel unavailable for CPU tensors")
@@ -29,11 +31,11 @@ def quant_act_int8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     if x2.dtype not in (torch.float32, torch.bfloat16):
         x2 = x2.float()
     x2 = x2.contiguous()
-    q = torch.empty(x2.shape, dtype=torch.int8, device=x.device)
+    q = torch.empty(x2.shape, dtype=torch.float16 if as_f16 else torch.int8, device=x.device)
     s = torch.empty(x2.size(0), dtype=torch.float32, device=x.device)
+    fn = lib.dst_quant_act_int8_f16 if as_f16 else lib.dst_quant_act_int8
     with torch.cuda.device(x.device):
-        _lib.check(lib.dst_quant_act_int8(x2.data_ptr(), int(x2.dtype == torch.float32), x2.size(0), x2.size(1),
-                                          q.data_ptr(), s.data_ptr(), kb._stream(x2)))
+        _lib.check(fn(x2.data_ptr(), int(x2.dtype == torch.float32), x2.size(0), x2.size(1), q.data_ptr(), s.data_ptr(), kb._stream(x2)))
     return q.view(*lead, -1), s.view(lead)
 
 
@@ -56,7 +58,7 @@ class TernaryLinear:
     """
 
     def __init__(self, terms: list[PackedTerm], K: int, fmt: str, group: int, act: str = "int8", backend: str = "auto",
-                 algo: str = "auto"):
+                 algo: str = "auto", decode_copy: bool = False):
         kb._fmt_code(fmt)
         if act not in ("int8", "bf16"):
             raise ValueError(f"unknown activation mode {act!r}")
@@ -64,11 +66,12 @@ class TernaryLinear:
             raise RuntimeError(f"backend {backend!r} is unavailable in this package (no CPU path)")
         self.terms, self.K, self.fmt, self.group, self.act = terms, K, fmt, group, act
         self.backend, self.algo = backend, algo
+        self.decode_copy = decode_copy  # TQ1: keep a tiled TQ2 copy of the trits on the device for few-row calls
         self._dev = None
 
     def _on(self, device):
         """([packed], [scale [1,N,G]]) on ``device``, copied once and kept. Shapes the fast kernels cover
-        (group 128, K % 128 == 0, fp16 scales, bf16 activations) are kept in the tiled device layout,
+        (group 128, K % 128 == 0, fp16 scales; both activation modes) are kept in the tiled device layout,
         everything else as the canonical ``[1, N, Kp]`` bytes."""
         if self._dev is None or self._dev[0] != device:
             packed = [t.packed.to(device).contiguous()[None] for t in self.terms]
@@ -80,8 +83,8 @@ class TernaryLinear:
                 scales.append(s.contiguous()[None])
             if len({s.dtype for s in scales}) > 1:
                 scales = [s.float() for s in scales]
-            if self.act == "bf16" and self.algo != "generic" and kb.fast_path_covers(self.K, self.group, scales[0].dtype):
-                packed = [kb.tile_weights(p, self.fmt, self.K) for p in packed]
+            if self.algo != "generic" and kb.fast_path_covers(self.K, self.group, scales[0].dtype):
+                packed = [kb.tile_weights(p, self.fmt, self.K, self.decode_copy) for p in packed]
             self._dev = (device, packed, scales)
         return self._dev[1], self._dev[2]
 
@@ -107,10 +110,17 @@ class TernaryLinear:
         x2 = x.reshape(-1, self.K)
         packed, scales = self._on(x2.device)
         if self.act == "int8":
-            q, s = quant_act_int8(x2)
             lib = kb._require(self.backend)
             out = torch.empty(x2.size(0), self.out_features, dtype=torch.float32, device=x2.device)
-            kb._grouped(lib, q, s, None, packed, scales, self.K, self.group, self.fmt, out, False, self.algo)
+            tiled = isinstance(packed[0], kb.TiledWeights)
+            if tiled and self.algo in ("auto", "prefill") and x2.size(0) > 16:
+                # many rows: quantise straight into the tcgen05 kernel's row format (2 launches per linear)
+                qh, s = quant_act_int8(x2, as_f16=True)
+                kb.grouped_ternary_gemm_bf16(kb.NormRows(qh, s), None, packed, scales, self.K, self.group, self.fmt, out=out,
+                                             backend=self.backend)
+            else:
+                q, s = quant_act_int8(x2)
+                kb._grouped(lib, q, s, None, packed, scales, self.K, self.group, self.fmt, out, False, self.algo)
         else:
             xa = x2 if x2.dtype in (torch.bfloat16, torch.float16) else x2.bfloat16()
             od = out_dtype if out_dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32

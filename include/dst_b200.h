@@ -103,6 +103,11 @@ int dst_untile_weights(const uint8_t* tiled, int64_t E, int64_t N, int64_t K, in
  * Replaces boilerplate/ternary/ops.py:20-25 (quant_act_int8). */
 int dst_quant_act_int8(const void* x, int x_is_f32, int64_t M, int64_t K, int8_t* q, float* s,
                        dst_stream_t stream);
+/* The same quantisation with q stored as fp16 (every |q| <= 127 is exact in fp16): (q_f16, s) is then a
+ * DST_ACT_F16_NORM activation (rows + per-row factors), so an act = "int8" linear over many rows is this kernel and the
+ * tcgen05 GEMM, with no conversion pass in between. Same rounding as dst_quant_act_int8, value for value. */
+int dst_quant_act_int8_f16(const void* x, int x_is_f32, int64_t M, int64_t K, void* q_f16, float* s,
+                           dst_stream_t stream);
 
 /*
  * The ternary grouped GEMM.
@@ -212,6 +217,11 @@ int dst_gather_rows_norm(const void* src_bf16, const int64_t* order, int64_t n_r
                          void* dst_f16, float* row_factor, dst_stream_t stream);
 int dst_swiglu_norm(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows,
                     int64_t inter, float limit, void* h_f16, float* row_factor, dst_stream_t stream);
+/* dst_swiglu_norm over the first min(n_rows_max, *n_rows_dev) rows, the count read on the device: an expert-parallel
+ * rank learns how many rows the others sent it without a host round trip. inter % 8 == 0, inter <= 8192. */
+int dst_swiglu_norm_dev(const void* gu_bf16, const float* route_weights, const int64_t* order, int64_t n_rows_max,
+                        const int64_t* n_rows_dev, int64_t inter, float limit, void* h_f16, float* row_factor,
+                        dst_stream_t stream);
 
 /*
  * Combine: y[t, :] = bf16( sum over the token's top_k slots, in increasing expert id, of
@@ -259,14 +269,22 @@ int dst_gather_dequant_rows(const void* const* packed, const void* const* scales
  * expert outputs [cap, hidden] bf16. `offsets` [E + 1] is this rank's routing-sort offsets over the GLOBAL experts,
  * dst_start [E] the first row, in the owning rank's receive buffer, of this rank's rows of each expert.
  * dst_ep_push_rows: for every sorted row p, the token row order[p] / top_k as fp16 scaled by a power of two
- * (DST_ACT_F16_NORM) -> the owner's buffers (rows, factor, routing weight route_weights[order[p]]).
+ * (DST_ACT_F16_NORM) -> the owner's buffers (rows, factor, routing weight route_weights[order[p]]). row_dest is an
+ * int64 [n_rows] scratch the call fills (each row's owner and row there, found once by a small kernel of its own);
+ * `rank` is this rank's index: it starts with the rows of the rank after it, so the ranks do not all store into the
+ * same GPU at the same time.
  * dst_ep_combine_pull: y[t] = bf16( sum over the token's slots, in increasing expert id, of the owner's output row ).
  * Neither waits on another GPU; the caller orders the steps (a stream-ordered collective between them).
  */
+/* Where this rank's routed rows go: offsets_all [world][E + 1] holds every rank's routing-sort offsets over the global
+ * experts (an all-gather of `offsets`); writes dst_start [E] and offsets_local [experts_per_rank + 1] (the row offsets
+ * of this rank's own experts in its receive buffer = the grouped GEMM's offsets). One small kernel, no host step. */
+int dst_ep_placement(const int64_t* offsets_all, int world, int64_t E, int64_t experts_per_rank, int rank, int64_t* dst_start,
+                     int64_t* offsets_local, dst_stream_t stream);
 int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
                      const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
                      const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
-                     int world, dst_stream_t stream);
+                     int world, int rank, int64_t* row_dest, dst_stream_t stream);
 int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
                         const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
                         void* y_bf16, int world, dst_stream_t stream);

@@ -541,7 +541,8 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
         w, ids, order, offsets = routed[r]
         xr = x[r * tl:(r + 1) * tl].contiguous()
         _lib.check(lib.dst_ep_push_rows(xr.data_ptr(), order.data_ptr(), offsets.data_ptr(), w.data_ptr(), place[r][0].data_ptr(),
-                                        order.numel(), E, El, topk, hidden, ptrs["rows"], ptrs["fac"], ptrs["wts"], W, stream))
+                                        order.numel(), E, El, topk, hidden, ptrs["rows"], ptrs["fac"], ptrs["wts"], W, r,
+                                        torch.empty(order.numel(), dtype=torch.int64, device=DEV).data_ptr(), stream))
     for r in range(W):  # experts of rank r on the rows it received
         offsets2 = place[r][1]
         R = int(offsets2[-1])
@@ -561,3 +562,80 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
     w_all = ExpertWeights(*stack_experts(experts, 1, DEV), hidden, inter, group, fmt).prepare()
     want = torch.cat([MoELayer(w_all, topk)(x[r * tl:(r + 1) * tl].contiguous(), logits[r * tl:(r + 1) * tl].contiguous()) for r in range(W)])
     assert torch.equal(torch.cat(ys), want)
+
+
+# ------------------------------------------------------------------------------------------ act = "int8" as a resident path
+@pytest.mark.parametrize("fmt", ["tq1", "tq2"])
+def test_int8_linear_keeps_tiled_weights_and_matches_the_reference_contract(kb, fmt, monkeypatch):
+    """TernaryLinear(act="int8"), the mode every shipped policy selects (configs/policy/*.yaml of the reference): the
+    weights are tiled once, a few rows go to the decode GEMV as int8 (integer group sums, as ternary_gemm_ref has them,
+    boilerplate/kernels/ternary_cuda.py:52-64), many rows are quantised straight into the tcgen05 kernel's row format."""
+    from deepseekternarized_b200.ternary import ops
+
+    N, K, group = 320, 1024, 128
+    rng = np.random.default_rng(77)
+    terms = make_terms(rng, N, K, group, fmt, 2)
+    calls = []
+    real_tile = kb.tile_weights
+    monkeypatch.setattr(kb, "tile_weights", lambda *a, **k: (calls.append(1), real_tile(*a, **k))[1])
+    lin = ops.TernaryLinear([ops.PackedTerm(torch.from_numpy(p), torch.from_numpy(s)) for p, s in terms], K, fmt, group, act="int8",
+                            decode_copy=True)
+    for M in (3, 300, 3):
+        x = rng.standard_normal((M, K)).astype(np.float32) * 2
+        q, xs = O.quant_act_int8(x)
+        want = sum(O.gemm_ref_i8(q, xs, p, s.astype(np.float32), K, group, fmt) for p, s in terms)
+        got = lin(torch.from_numpy(x).to(DEV), out_dtype=torch.float32).cpu().numpy()
+        np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-3)
+        # decode rows: exact integer group sums. Many rows: the tcgen05 kernel merges the two stacked terms into one
+        # fp16 weight (s1 t1 + s2 t2, one rounding of 2^-12 relative) before the exact products
+        assert O.rel_fro(got, want) < (1e-5 if M <= 16 else 5e-4)
+    assert len(calls) == 2  # one re-layout per term, at the first call only
+    qh, s16 = ops.quant_act_int8(torch.from_numpy(x).to(DEV), as_f16=True)
+    qi, s8 = ops.quant_act_int8(torch.from_numpy(x).to(DEV))
+    assert qh.dtype == torch.float16 and torch.equal(qh.to(torch.int8), qi) and torch.equal(s16, s8)
+    assert np.array_equal(qi.cpu().numpy(), q) and np.array_equal(s8.cpu().numpy(), xs)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 19])
+def test_tq1_weights_with_a_two_bit_decode_copy(kb, M):
+    """TQ1 weights that also keep their trits as tiled TQ2 on the device: few-row calls read that copy (same trits, the
+    TQ2 decode kernel), many-row calls the TQ1 tiles; both inside the tolerance, and the copy equals packing the
+    trits as TQ2 in the first place."""
+    E, N, K = 3, 200, 1024
+    rng = np.random.default_rng(M)
+    t = O.synth_trits(rng, (E, N, K))
+    s = O.synth_scales(rng, (E, N, K // 128))
+    p1 = np.stack([O.pack(t[e], "tq1") for e in range(E)])
+    p2 = np.stack([O.pack(t[e], "tq2") for e in range(E)])
+    w1 = kb.tile_weights(torch.from_numpy(p1).to(DEV), "tq1", K, decode_copy=True)
+    w2 = kb.tile_weights(torch.from_numpy(p2).to(DEV), "tq2", K)
+    assert w1.decode is not None and torch.equal(w1.decode.data, w2.data)
+    counts = np.array([M, 0, max(1, M // 2)])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = O.synth_acts(rng, (int(offsets[-1]), K))
+    sd = torch.from_numpy(s).to(DEV)
+    y1 = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, [w1], [sd], K, 128, "tq1").cpu().numpy()
+    y2 = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, [w2], [sd], K, 128, "tq2", algo="decode").cpu().numpy()
+    if offsets[-1] <= 16 * E:
+        assert np.array_equal(y1, y2)  # the very same kernel on the very same bytes
+    for e in range(E):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            check_gemm(y1[a:b], x[a:b], [(p1[e], s[e])], K, 128, "tq1")
+            np.testing.assert_allclose(y1[a:b], O.gemm_f32(x[a:b], p1[e], s[e].astype(np.float32), K, 128, "tq1"), rtol=1e-4, atol=1e-3)
+
+
+def test_decode_kernel_int8_activations_are_exact_integer_sums(kb):
+    """int8 activations through the decode GEMV: the group sums are exact integers (int8 tensor-core MMAs), so the result
+    equals the reference-of-record up to the order of the fp32 additions over groups."""
+    E, N, K, group = 5, 136, 1536, 128
+    rng = np.random.default_rng(41)
+    terms = make_terms(rng, N, K, group, "tq2", 1, lead=(E,))
+    counts = np.array([1, 4, 0, 16, 9])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    q, xs = O.quant_act_int8(rng.standard_normal((int(offsets[-1]), K)).astype(np.float32) * 3)
+    want = O.grouped_gemm_i8(q, xs, offsets, terms[0][0], terms[0][1].astype(np.float32), K, group, "tq2")
+    tiled = kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), "tq2", K)
+    got = kb.grouped_ternary_gemm(torch.from_numpy(q).to(DEV), torch.from_numpy(xs).to(DEV), offsets, tiled,
+                                  torch.from_numpy(terms[0][1]).to(DEV), K, group, "tq2", algo="decode").cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-6)
