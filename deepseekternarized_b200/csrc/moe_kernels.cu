@@ -104,8 +104,9 @@ __global__ void route_kernel(const float* __restrict__ logits, const float* __re
 
 // ------------------------------------------------------------------------------------ routing sort
 // Stable counting sort in three steps over chunks of SORT_CHUNK consecutive ids, one warp per chunk:
-//   1. per-chunk histogram               hist[c][e]; also presets order[] to 0, so the tail that dropped ids leave
-//                                         unwritten holds a valid row index instead of whatever was in memory
+//   1. per-chunk histogram               hist[c][e]; also presets order[] to -1, so the tail that dropped ids leave
+//                                         unwritten is recognisable (every reader clamps or skips it) instead of
+//                                         holding whatever was in memory
 //   2. one block: offsets[e] and the start of every (chunk, expert) run, in place in hist
 //   3. per chunk, in input order: warp match on the expert id gives each entry its rank among equal
 //      ids of the same 32-entry step; a per-expert cursor in shared memory carries across steps.
@@ -125,7 +126,7 @@ __global__ void sort_hist_kernel(const IdT* __restrict__ ids, int64_t n, int E, 
       const int64_t e = (int64_t)ids[i];
       if (e >= 0 && e < E) atomicAdd(&sh[e], 1);
       else ++bad;
-      order[i] = 0;
+      order[i] = -1;
     }
   }
   __syncwarp();

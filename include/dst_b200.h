@@ -158,7 +158,7 @@ size_t dst_gemm_workspace_bytes(int algo, int act_dtype, int64_t T, int64_t K);
 /*
  * Routing sort: flattened expert ids [n] (int64 or int32) -> the stable order that sorts them by
  * expert and offsets[E+1] (int64). Ids outside [0, E) are counted in *bad_count (device int32, may
- * be NULL) and dropped. Runs three small kernels; `workspace` must hold dst_sort_workspace_bytes(n, E).
+ * be NULL) and dropped: order[offsets[E] .. n) is then -1. Runs three small kernels; `workspace` must hold dst_sort_workspace_bytes(n, E).
  * Replaces boilerplate/kernels/ternary_cuda.py:114-118 (sort_by_expert).
  */
 size_t dst_sort_workspace_bytes(int64_t n, int64_t E);
