@@ -58,7 +58,8 @@ bool decode_supports(const GemmArgs& a);
 int launch_decode_tq1(const GemmArgs& a, cudaStream_t stream);  // TQ1 decode kernel (gemm_decode_tq1.cu); reached through launch_decode
 bool decode_tq1_supports(const GemmArgs& a);
 bool prefill_supports(const GemmArgs& a);
-int decode_take_status(int* status);  // reads and clears the decode kernel's status word (0 or DST_ERR_TIMEOUT)
+int decode_take_status(int* status);
+int ep_take_status(int* status);      // the same for the expert-parallel barrier kernel  // reads and clears the decode kernel's status word (0 or DST_ERR_TIMEOUT)
 
 // ---------------------------------------------------------------------------------------------
 // Trit decoding. TQ1 digit i of byte v: ((v / 3^i) % 3) - 1 for v < 243, else 0

@@ -227,6 +227,29 @@ __global__ void ep_placement_kernel(const int64_t* __restrict__ offsets_all, int
   }
 }
 
+// Barrier among the ranks of a node over peer memory: thread r stores `seq` into slot `rank` of rank r's flag array,
+// then waits until slot r of this rank's own array has reached `seq`. Everything this rank's stream did before the
+// launch (its pushes into the peers' buffers) has completed before the kernel starts, and the fence orders it before
+// the flag. The wait is bounded (~2 s of clock cycles): on expiry the kernel records DST_ERR_TIMEOUT in the status word
+// and returns, so a rank that never arrives cannot hang the others' GPUs.
+__device__ int g_ep_status = 0;
+__global__ void ep_barrier_kernel(PeerPtrs flags, int world, int rank, long long seq) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  volatile long long* theirs = static_cast<volatile long long*>(peer_ptr(flags, r));
+  theirs[rank] = seq;
+  volatile long long* mine = static_cast<volatile long long*>(peer_ptr(flags, rank));
+  const long long t0 = clock64();
+  while (mine[r] < seq) {
+    if (clock64() - t0 > 4000000000LL) {
+      atomicExch(&g_ep_status, DST_ERR_TIMEOUT);
+      break;
+    }
+  }
+  __threadfence_system();
+}
+
 bool fill_peers(PeerPtrs& out, const void* const* ptrs, int world) {
   for (int i = 0; i < DST_MAX_PEERS; ++i) out.p[i] = nullptr;
   for (int i = 0; i < world; ++i) {
@@ -240,6 +263,28 @@ bool fill_peers(PeerPtrs& out, const void* const* ptrs, int world) {
 }  // namespace dst
 
 using namespace dst;
+
+extern "C" int dst_ep_barrier(const void* const* peer_flags, int world, int rank, int64_t seq, dst_stream_t stream) {
+  if (world < 1 || world > DST_MAX_PEERS || rank < 0 || rank >= world || seq <= 0 || !peer_flags) return DST_ERR_BAD_ARG;
+  PeerPtrs flags;
+  if (!fill_peers(flags, peer_flags, world)) return DST_ERR_ALIGNMENT;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, rank, (long long)seq);
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+namespace dst {
+int ep_take_status(int* status) {
+  int st = 0;
+  DST_CUDA_TRY(cudaMemcpyFromSymbol(&st, g_ep_status, sizeof(int)));
+  if (st != 0) {
+    const int zero = 0;
+    DST_CUDA_TRY(cudaMemcpyToSymbol(g_ep_status, &zero, sizeof(int)));
+  }
+  *status = st;
+  return DST_OK;
+}
+}  // namespace dst
 
 extern "C" int dst_ep_placement(const int64_t* offsets_all, int world, int64_t E, int64_t experts_per_rank, int rank, int64_t* dst_start,
                                 int64_t* offsets_local, dst_stream_t stream) {

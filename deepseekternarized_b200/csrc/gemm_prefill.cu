@@ -968,7 +968,10 @@ extern "C" int dst_check_device_status(dst_stream_t stream) {
   int st_decode = 0;  // the decode kernel keeps a status word of its own
   const int rc = dst::decode_take_status(&st_decode);
   if (rc != DST_OK) return rc;
-  return (st != 0 || st_decode != 0) ? DST_ERR_TIMEOUT : DST_OK;
+  int st_ep = 0;  // and so does the expert-parallel barrier
+  const int rc2 = dst::ep_take_status(&st_ep);
+  if (rc2 != DST_OK) return rc2;
+  return (st != 0 || st_decode != 0 || st_ep != 0) ? DST_ERR_TIMEOUT : DST_OK;
 }
 
 // ------------------------------------------------------------------------------------------ no-allocation entry

@@ -428,11 +428,23 @@ class ExpertParallelMoE:
                 if self.transport == "peer":
                     raise RuntimeError(f"peer transport unavailable: {exc}") from exc
                 ok = False
+        if ok:
+            try:  # the barrier's flag words, one int64 per rank, in symmetric memory like the row buffers
+                import torch.distributed._symmetric_memory as symm
+
+                self._flags = symm.empty((16,), dtype=torch.int64, device=x.device)
+                self._flags.zero_()
+                hdl = symm.rendezvous(self._flags, pg)
+                self._flag_ptrs = (ctypes.c_void_p * self.world)(*[hdl.get_buffer(r, (16,), torch.int64).data_ptr() for r in range(self.world)])
+                self._barrier_seq = 0
+            except Exception as exc:
+                if self.transport == "peer":
+                    raise RuntimeError(f"peer transport unavailable: {exc}") from exc
+                ok = False
         flag = torch.tensor([1 if ok else 0], device=x.device if x.is_cuda else "cpu", dtype=torch.int32)
-        self.dist.all_reduce(flag, op=self.dist.ReduceOp.MIN, group=self.pg)
+        self.dist.all_reduce(flag, op=self.dist.ReduceOp.MIN, group=self.pg)  # also: every rank's flag words are zeroed before any barrier
         if int(flag.item()) == 1:
             self._peer = bufs
-            self._sync = torch.zeros(1, device=x.device, dtype=torch.int32)
             return True
         if self.transport == "peer":
             raise RuntimeError("peer transport unavailable on some rank")
@@ -470,7 +482,7 @@ class ExpertParallelMoE:
                                             buf.ptrs["wts"], W, self.rank, row_dest.data_ptr(), kb._stream(x)))
         getattr(self.ops, "count", lambda n: None)(5)  # kernels launched here rather than through ops (placement, row destinations, push, invert, combine)
         ev("push")
-        dist.all_reduce(self._sync, group=self.pg)  # every rank's rows have landed
+        self._barrier(x)  # every rank's rows have landed
         ev("barrier")
         # the received rows: the buffers' whole capacity goes to the kernels, the row count stays on the device
         # (offsets2[-1]); the grouped GEMMs follow offsets2, the SwiGLU kernel reads the count
@@ -479,7 +491,7 @@ class ExpertParallelMoE:
         self.local.experts_forward(xs2, offsets2, buf.wts, None, out=buf.down, n_rows_dev=offsets2[-1:])
         shared = self.local.shared_forward(x)  # this rank's tokens through the (replicated) shared expert
         ev("expert GEMMs+SwiGLU")
-        dist.all_reduce(self._sync, group=self.pg)  # every rank's expert outputs are written
+        self._barrier(x)  # every rank's expert outputs are written
         ev("barrier 2")
         inv = torch.empty(T * self.top_k, dtype=torch.int64, device=x.device)
         y = torch.empty(T, hidden, dtype=torch.bfloat16, device=x.device)
@@ -490,6 +502,12 @@ class ExpertParallelMoE:
                                                    shared.data_ptr() if shared is not None else None, y.data_ptr(), W, kb._stream(x)))
         ev("combine-pull")
         return y
+
+    def _barrier(self, x: torch.Tensor) -> None:
+        """Stream-ordered barrier among the ranks: one small kernel over the symmetric flag words (bounded wait)."""
+        self._barrier_seq += 1
+        with torch.cuda.device(x.device):
+            _lib.check(B200Ops._lib().dst_ep_barrier(self._flag_ptrs, self.world, self.rank, self._barrier_seq, kb._stream(x)))
 
     def _phase_events(self):
         """With ``profile_phases`` on, returns a function that records a CUDA event after each named phase of a step

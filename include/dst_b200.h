@@ -276,6 +276,10 @@ int dst_gather_dequant_rows(const void* const* packed, const void* const* scales
  * dst_ep_combine_pull: y[t] = bf16( sum over the token's slots, in increasing expert id, of the owner's output row ).
  * Neither waits on another GPU; the caller orders the steps (a stream-ordered collective between them).
  */
+/* Barrier among the ranks of one node over peer memory, in stream order: peer_flags[r] is rank r's flag array (int64
+ * [world], zero at the start) as mapped in this process; seq = 1, 2, 3, ... counts the barriers of the job, the same on
+ * every rank. The wait for the other ranks is bounded (~2 s), after which dst_check_device_status reports DST_ERR_TIMEOUT. */
+int dst_ep_barrier(const void* const* peer_flags, int world, int rank, int64_t seq, dst_stream_t stream);
 /* Where this rank's routed rows go: offsets_all [world][E + 1] holds every rank's routing-sort offsets over the global
  * experts (an all-gather of `offsets`); writes dst_start [E] and offsets_local [experts_per_rank + 1] (the row offsets
  * of this rank's own experts in its receive buffer = the grouped GEMM's offsets). One small kernel, no host step. */
@@ -328,7 +332,7 @@ int dst_ternary_grouped_gemm_noalloc(void* out, int out_dtype, int accumulate, c
                                      const void* const* packed_tiled, const void* const* scales, int n_terms,
                                      int64_t E, int64_t T, int64_t N, int64_t K, int fmt, dst_stream_t stream);
 
-/* Reads (and clears) the device-side status words that bounded waits in the tcgen05 and decode kernels write when
+/* Reads (and clears) the device-side status words that bounded waits in the tcgen05, decode and barrier kernels write when
  * they give up. Synchronises `stream`. Returns DST_OK or DST_ERR_TIMEOUT. */
 int dst_check_device_status(dst_stream_t stream);
 
