@@ -121,6 +121,9 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
 }
 
 extern "C" size_t dst_gemm_workspace_bytes(int algo, int act_dtype, int64_t T, int64_t K) {
-  if (T <= 0 || K <= 0 || algo == DST_ALGO_GENERIC || algo == DST_ALGO_DECODE) return 0;
-  return dst::prefill_workspace_bytes(act_dtype, T, K);
+  if (T <= 0 || K <= 0 || algo == DST_ALGO_GENERIC) return 0;
+  const size_t dec = K % 128 == 0 ? dst::decode_workspace_bytes(T, K) : 0;  // optional for the decode GEMV (it is faster with it)
+  if (algo == DST_ALGO_DECODE) return dec;
+  const size_t pre = dst::prefill_workspace_bytes(act_dtype, T, K);
+  return algo == DST_ALGO_PREFILL ? pre : (pre > dec ? pre : dec);
 }

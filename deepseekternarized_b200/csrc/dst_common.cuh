@@ -50,6 +50,7 @@ struct GemmArgs {
 
 int64_t tiled_superblocks(int fmt, int64_t K);
 size_t prefill_workspace_bytes(int act_dtype, int64_t T, int64_t K);
+size_t decode_workspace_bytes(int64_t T, int64_t K);  // optional: lets the decode GEMV quantise each token once, ahead of itself
 
 int launch_generic(const GemmArgs& a, cudaStream_t stream);
 int launch_decode(const GemmArgs& a, cudaStream_t stream);    // DST_ERR_UNSUPPORTED when not covered

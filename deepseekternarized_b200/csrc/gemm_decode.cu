@@ -50,6 +50,9 @@ constexpr int DC_RING = DC_RING_SLOTS;            // slots of the slab ring
 #ifndef DC_PRODUCER_SLEEP
 #define DC_PRODUCER_SLEEP true
 #endif
+#ifndef DC_PREQ_ABOVE
+#define DC_PREQ_ABOVE 0
+#endif
 constexpr int DC_ZERO = 512;                      // bytes of zeros the lanes without a column read
 constexpr long long DC_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
@@ -66,6 +69,10 @@ struct DecodeParams {
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S;
   int xstride;  // bytes between staged activation rows: K + 64 (= 64 mod 128: two rows read together hit all banks once)
+  // activations quantised ahead of the GEMV by decode_quant_kernel (null: the GEMV's consumer warps do it per expert)
+  const uint8_t* q_rows;  // [T][2][K] s8: the hi and the lo row of every token, bytes in the staged order
+  const int* q_xsum4;     // [T][G]
+  const float* q_xexp;    // [T]
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -191,8 +198,8 @@ __device__ __forceinline__ float amax8(const int8_t*) { return 0.f; }
 //   xsum4[tok][g]           4 * sum of q over scale group g (int32); zero for token slots beyond mc
 //   xexp[tok]               s_tok * row_scale / 4 (NaN when the row holds a non-finite value)
 template <int MT, typename XT, typename Sync>
-__device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, int* xsum4, float* xexp,
-                             float* xinv, Sync&& consumer_sync) {
+__device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, size_t xstride, int* xsum4,
+                             float* xexp, float* xinv, Sync&& consumer_sync) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr bool IS_I8 = sizeof(XT) == 1;
   // pass 1: row maxima. Every consumer thread takes 128-bit pieces of every row; the warps' partial maxima meet in
@@ -266,13 +273,29 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
       }
       // lane bits: (q4 & 1) c1 c0 (m & 1) h -> byte position (g & 1) * 128 + (q4 & 1) * 64 + c * 16 + (m & 1) * 8 + h * 4
       const int pos = (g >> 1) * 256 + (g & 1) * 128 + lane * 4;
-      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m) * p.xstride + pos) = whi;
-      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m + 1) * p.xstride + pos) = wlo;
+      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m) * xstride + pos) = whi;
+      *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m + 1) * xstride + pos) = wlo;
     }
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     if (lane == 0) xsum4[m * p.G + g] = 4 * sum;
   }
   return true;
+}
+
+// The staging above done ONCE per token, ahead of the GEMV, into global memory: with more than a few rows per expert
+// the GEMV's CTAs would otherwise repeat it for every expert they touch (measured at 8 rows: a quarter to a half of
+// their instructions). One block of DC_CWARPS warps per token row.
+template <typename XT>
+__global__ void __launch_bounds__(DC_CWARPS * 32)
+decode_quant_kernel(const DecodeParams p, uint8_t* __restrict__ q_rows, int* __restrict__ q_xsum4, float* __restrict__ q_xexp) {
+  __shared__ float xinv[DC_CWARPS];
+  const int64_t t = blockIdx.x;
+  auto sync = []() -> bool {
+    __syncthreads();
+    return true;
+  };
+  // token t as a "pass" of one row: row_scale, the row pointer and the outputs are all indexed by t through m0 = t
+  stage_tokens<1>(p, static_cast<const XT*>(p.x), t, 1, q_rows + (size_t)t * 2 * p.K, (size_t)p.K, q_xsum4 + t * p.G, q_xexp + t, xinv, sync);
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
@@ -281,8 +304,14 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
 #ifndef DC_MINB
 #define DC_MINB 4
 #endif
+#ifndef DC_MINB2
+#define DC_MINB2 3
+#endif
+#ifndef DC_MINB4
+#define DC_MINB4 2
+#endif
 template <int GS, int NB, typename XT>
-__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? DC_MINB : (NB == 2 ? 4 : 2))
+__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? DC_MINB : (NB == 2 ? DC_MINB2 : DC_MINB4))
 decode_kernel(const DecodeParams p) {
   constexpr int MT = 4 * NB / GS;  // token rows per pass
   constexpr int TPB = 4 / GS;      // token rows per column block
@@ -293,7 +322,7 @@ decode_kernel(const DecodeParams p) {
   int* xsum4 = reinterpret_cast<int*>(xs + (size_t)2 * MT * p.xstride);  // [MT][G]
   float* xexp = reinterpret_cast<float*>(xsum4 + MT * p.G);      // [MT]
   float* xinv = xexp + MT;                                       // [MT][DC_CWARPS] partial row maxima
-  __shared__ uint64_t bar_stage;
+  __shared__ uint64_t bar_stage, bar_rows;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -305,6 +334,7 @@ decode_kernel(const DecodeParams p) {
       mbar_init(smem_u32(ring + s * DC_SLOT + DC_SLOT_DATA + 8), DC_CWARPS * 32);  // empty: one arrive per consumer thread
     }
     mbar_init(smem_u32(&bar_stage), DC_CWARPS);       // the consumer warps' own barrier (bounded, unlike bar.sync)
+    mbar_init(smem_u32(&bar_rows), 1);                // pre-quantised token rows have landed (expect_tx arrive of the thread that copies)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = threadIdx.x; i < DC_ZERO / 4; i += DC_THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
@@ -348,7 +378,7 @@ decode_kernel(const DecodeParams p) {
     const int col_pair = g8 >> 1, col_part = g8 & 1;
     const int tok_c = c / GS, slot_c = c % GS;  // (+ b * TPB) the token and the group slot of this lane's C columns
     const uint32_t ring_end = ring_a + DC_RING * DC_SLOT;
-    uint32_t sbase = ring_a, ph = 0, stage_ph = 0;  // the current ring slot and the parity of its "full" phase
+    uint32_t sbase = ring_a, ph = 0, stage_ph = 0, rows_ph = 0;  // the current ring slot and the parity of its "full" phase
     int staged_e = -1;
     int64_t staged_m0 = -1;
     auto consumer_sync = [&]() -> bool {
@@ -367,9 +397,24 @@ decode_kernel(const DecodeParams p) {
         const int mc = (int)(it.rb - m0 < MT ? it.rb - m0 : MT);
         if (staged_e != it.e || staged_m0 != m0) {
           // every consumer is done with the previous rows; then stage; then everyone sees the new ones
-          if (!(consumer_sync() && stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, xsum4, xexp, xinv, consumer_sync) &&
-                consumer_sync()))
+          if (!consumer_sync()) goto aborted;  // every consumer is done with the previous rows
+          if (p.q_rows != nullptr) {
+            // quantised ahead of this kernel: one thread has the rows copied in (bulk copies onto the staging barrier), the
+            // others fetch the small per-(token, group) sums and the row factors
+            if (warp == 0 && lane == 0) {
+              const uint32_t bar = smem_u32(&bar_rows);
+              mbar_arrive_expect_tx(bar, (uint32_t)mc * 2u * (uint32_t)p.K);
+              for (int m = 0; m < 2 * mc; ++m)
+                bulk_load(xs_a + (uint32_t)m * (uint32_t)p.xstride, p.q_rows + ((size_t)m0 * 2 + m) * p.K, (uint32_t)p.K, bar);
+            }
+            for (int i = threadIdx.x; i < MT * p.G; i += DC_CWARPS * 32) xsum4[i] = i < mc * p.G ? p.q_xsum4[m0 * p.G + i] : 0;
+            if (threadIdx.x < MT) xexp[threadIdx.x] = threadIdx.x < mc ? p.q_xexp[m0 + threadIdx.x] : 0.f;
+            if (!mbar_wait(smem_u32(&bar_rows), rows_ph, abort_flag)) goto aborted;
+            rows_ph ^= 1u;
+          } else if (!stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, (size_t)p.xstride, xsum4, xexp, xinv, consumer_sync)) {
             goto aborted;
+          }
+          if (!consumer_sync()) goto aborted;
           staged_e = it.e;
           staged_m0 = m0;
         }
@@ -534,6 +579,13 @@ int launch_rows(const DecodeParams& p, int64_t rows_hint, int sms, cudaStream_t 
 
 }  // namespace
 
+// Scratch of the pre-quantised activations: [T][2][K] s8 rows, [T][G] int32 sums, [T] float factors (each part 256-byte aligned).
+size_t decode_workspace_bytes(int64_t T, int64_t K) {
+  const size_t G = (size_t)(K / 128);
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  return up((size_t)T * 2 * (size_t)K) + up((size_t)T * G * 4) + up((size_t)T * 4);
+}
+
 bool decode_supports(const GemmArgs& a) {
   if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
   return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 512 == 0 &&
@@ -570,11 +622,30 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   p.NT = (int)cdiv64(a.N, 128);
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.xstride = (int)(a.K + 64);
+  p.q_rows = nullptr;
+  p.q_xsum4 = nullptr;
+  p.q_xexp = nullptr;
   // rows per expert: known on the host, or guessed from the mean (an expert with more rows takes several passes)
   const int64_t rows_hint = a.max_rows >= 0 ? a.max_rows : cdiv64(a.T, a.E);
   int dev = 0, sms = 148;
   DST_CUDA_TRY(cudaGetDevice(&dev));
   DST_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  // More than two rows per expert and a workspace: quantise every token once, ahead of the GEMV
+  if (rows_hint > DC_PREQ_ABOVE && a.workspace != nullptr && a.workspace_bytes >= decode_workspace_bytes(a.T, a.K) &&
+      (reinterpret_cast<uintptr_t>(a.workspace) & 255) == 0) {
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    uint8_t* base = static_cast<uint8_t*>(a.workspace);
+    uint8_t* q_rows = base;
+    int* q_xsum4 = reinterpret_cast<int*>(base + up((size_t)a.T * 2 * (size_t)a.K));
+    float* q_xexp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(q_xsum4) + up((size_t)a.T * (size_t)a.G * 4));
+    if (a.act_dtype == DST_ACT_BF16) decode_quant_kernel<__nv_bfloat16><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    else if (a.act_dtype == DST_ACT_F16) decode_quant_kernel<__half><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    else decode_quant_kernel<int8_t><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    DST_CUDA_TRY(cudaGetLastError());
+    p.q_rows = q_rows;
+    p.q_xsum4 = q_xsum4;
+    p.q_xexp = q_xexp;
+  }
   if (a.act_dtype == DST_ACT_BF16) return launch_rows<__nv_bfloat16>(p, rows_hint, sms, stream);
   if (a.act_dtype == DST_ACT_F16) return launch_rows<__half>(p, rows_hint, sms, stream);
   return launch_rows<int8_t>(p, rows_hint, sms, stream);

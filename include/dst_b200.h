@@ -135,7 +135,10 @@ int dst_quant_act_int8_f16(const void* x, int x_is_f32, int64_t M, int64_t K, vo
  *                DST_ERR_ALIGNMENT when it does not cover the call (AUTO falls back to GENERIC).
  *   workspace    device scratch of at least dst_gemm_workspace_bytes(...) bytes, 256-byte aligned, or
  *                NULL. The prefill kernel keeps the fp16 copy of the activations and the per-row
- *                factors there; it is free again when the launched work has finished.
+ *                factors there (it needs it unless the activations are DST_ACT_F16_NORM); the decode
+ *                GEMV uses it, when given, to quantise every token once ahead of itself instead of
+ *                once per expert and CTA (same results). It is free again when the launched work
+ *                has finished.
  *
  * Fast-kernel coverage: tiled weights, group == 128, K % 128 == 0 (TQ2 decode: K % 256 == 0), fp16 scales, bf16,
  * f16 or int8 activations. GENERIC reads canonical weights only.
