@@ -69,6 +69,13 @@ constexpr int PF_SMEM_STATIC = 512;          // allowance for the statically dec
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 __device__ int g_device_status = 0;
+// Test hooks (dst_debug_prefill_timeout): the cycle limit of the bounded waits, and a switch that makes the epilogue
+// warps keep their "accumulator drained" arrivals to themselves, so that the MMA warps' wait for the accumulator runs
+// out by design at a CTA's second tile. Nothing faults or spins unbounded: the wait gives up, the abort flag goes up,
+// every role leaves, the CTA frees its TMEM and the status word says DST_ERR_TIMEOUT.
+__device__ long long g_wait_cycles = PF_WAIT_CYCLES;
+__device__ int g_drop_drain_arrivals = 0;
+int g_debug_max_ctas = 0;  // host side: caps the grid when positive (so one CTA is sure to own several tiles)
 
 // Optional per-role cycle accounting (build with -DDST_ROLE_TIMERS): where each warp role of the tcgen05
 // kernel spends its time, summed over CTAs. Read with dst_role_timers(). Off in the shipped library.
@@ -137,7 +144,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_test(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > PF_WAIT_CYCLES) {
+      if (clock64() - t0 > g_wait_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -366,7 +373,7 @@ __device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncwarp();
-  if (lane == 0) mbar_arrive(tempty_bar);
+  if (lane == 0 && !g_drop_drain_arrivals) mbar_arrive(tempty_bar);
   return true;
 }
 
@@ -830,7 +837,8 @@ int launch_fmt(const TmaMaps& maps, PrefillParams p, cudaStream_t st) {
   long long tiles_upper = ((long long)cdiv64(p.T, p.tn_max) + p.E) * p.NT;
   if (tiles_upper >= (1LL << 30)) return DST_ERR_UNSUPPORTED;  // tile indices are 32-bit in the kernel
   if (tiles_upper < 1) tiles_upper = 1;
-  const unsigned grid = (unsigned)(tiles_upper < sms ? tiles_upper : sms);
+  unsigned grid = (unsigned)(tiles_upper < sms ? tiles_upper : sms);
+  if (g_debug_max_ctas > 0 && grid > (unsigned)g_debug_max_ctas) grid = (unsigned)g_debug_max_ctas;
   prefill_kernel<FMT, TERMS><<<grid, PF_THREADS, smem, st>>>(maps, p);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
@@ -956,6 +964,16 @@ extern "C" int dst_role_timers(unsigned long long* out, int reset) {
   return DST_OK;
 }
 #endif
+
+extern "C" int dst_debug_prefill_timeout(long long wait_cycles, int drop_drain_arrivals, int max_ctas) {
+  const long long cycles = wait_cycles > 0 ? wait_cycles : dst::PF_WAIT_CYCLES;
+  const int drop = drop_drain_arrivals ? 1 : 0;
+  DST_CUDA_TRY(cudaDeviceSynchronize());
+  DST_CUDA_TRY(cudaMemcpyToSymbol(dst::g_wait_cycles, &cycles, sizeof(cycles)));
+  DST_CUDA_TRY(cudaMemcpyToSymbol(dst::g_drop_drain_arrivals, &drop, sizeof(drop)));
+  dst::g_debug_max_ctas = max_ctas > 0 ? max_ctas : 0;
+  return DST_OK;
+}
 
 extern "C" int dst_check_device_status(dst_stream_t stream) {
   DST_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));

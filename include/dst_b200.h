@@ -339,6 +339,16 @@ int dst_ternary_grouped_gemm_noalloc(void* out, int out_dtype, int accumulate, c
  * they give up. Synchronises `stream`. Returns DST_OK or DST_ERR_TIMEOUT. */
 int dst_check_device_status(dst_stream_t stream);
 
+/*
+ * Test hook for the failure path of the tcgen05 kernel (this device, until called again with zeros): wait_cycles > 0
+ * shortens the bounded waits from ~2 s to that many clock cycles; drop_drain_arrivals != 0 makes the warps that drain
+ * the accumulator withhold their "drained" signal, so at a CTA's second tile the MMA warps' wait runs out, the CTA
+ * aborts in order (every role leaves, TMEM is freed) and dst_check_device_status reports DST_ERR_TIMEOUT; max_ctas > 0
+ * caps the grid so that one CTA is sure to own several tiles. Nothing in this path faults or waits without a bound.
+ * dst_debug_prefill_timeout(0, 0, 0) restores normal operation. Synchronises the device.
+ */
+int dst_debug_prefill_timeout(long long wait_cycles, int drop_drain_arrivals, int max_ctas);
+
 #ifdef __cplusplus
 }
 #endif

@@ -639,3 +639,31 @@ def test_decode_kernel_int8_activations_are_exact_integer_sums(kb):
     got = kb.grouped_ternary_gemm(torch.from_numpy(q).to(DEV), torch.from_numpy(xs).to(DEV), offsets, tiled,
                                   torch.from_numpy(terms[0][1]).to(DEV), K, group, "tq2", algo="decode").cpu().numpy()
     np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-6)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_gpu_usable(kb):
+    """Failure detection in the form a shared GPU allows: through the library's test hook the epilogue warps of the tcgen05
+    kernel withhold one signal and the wait limit is ~1 ms, so a wait runs out BY DESIGN at the CTA's second tile. The
+    kernel must return (no fault, no endless spin), dst_check_device_status must say DST_ERR_TIMEOUT once, and an
+    ordinary launch right afterwards must give the right answer."""
+    from deepseekternarized_b200 import _lib
+
+    lib = kb.ext()
+    N, K, M, fmt = 512, 256, 64, "tq2"  # four 128-row tiles for one CTA
+    rng = np.random.default_rng(9)
+    terms = make_terms(rng, N, K, 128, fmt, 1)
+    x = O.synth_acts(rng, (M, K))
+    tiled = kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), fmt, K)
+    sc = [torch.from_numpy(terms[0][1]).to(DEV)]
+    run = lambda: kb.ternary_gemm_bf16(bf16_tensor(x, DEV), [tiled], sc, K, 128, fmt, algo="prefill")
+    assert lib.dst_check_device_status(None) == _lib.OK
+    _lib.check(lib.dst_debug_prefill_timeout(2_000_000, 1, 1))
+    try:
+        run()  # the second tile's wait for the accumulator gives up after ~1 ms; the CTA aborts in order
+        assert lib.dst_check_device_status(None) == _lib.ERR_TIMEOUT
+        assert lib.dst_check_device_status(None) == _lib.OK  # the status word is cleared by the read
+    finally:
+        _lib.check(lib.dst_debug_prefill_timeout(0, 0, 0))
+    y = run().cpu().numpy()
+    assert lib.dst_check_device_status(None) == _lib.OK
+    check_gemm(y, x, terms, K, 128, fmt)
