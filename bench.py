@@ -279,7 +279,7 @@ def time_cuda(fn, iters: int, warmup: int = 3, repeats: int = 3, min_loop_ms: fl
             "window": (t0, time.time())}
 
 
-def gemm_microbench(device, peaks, which="all", sampler=None) -> dict:
+def gemm_microbench(device, peaks, which="all", sampler=None, only=None) -> dict:
     """Single-kernel numbers at N = 1: decode GEMV (BASELINE configs 0, 1 and 3) and prefill grouped GEMM (configs 2
     and 3, and the int8-activation mode on the config-2 shape).
 
@@ -316,6 +316,8 @@ def gemm_microbench(device, peaks, which="all", sampler=None) -> dict:
                     ("tq1", 2048, 4096, (1, 8), 1, True), ("tq1", 4096, 4096, (1, 4, 8), 1, True), ("tq1", 11008, 4096, (1, 8), 1, True),
                     ("tq2", 2048, 4096, (1, 8, 64), 2, False), ("tq2", 4096, 2048, (1, 8, 64), 2, False))  # config 3: k = 2
     for fmt, N, K, Ms, k_terms, copy in (decode_cases if which in ("all", "decode") else ()):
+        if only is not None and f"{fmt}:{N}:{K}:{k_terms}:{'copy' if copy else 'tiles'}" != only:
+            continue  # a profiler capture of one case
         wbytes = k_terms * (N * packed_cols(fmt, K) + N * (K // GROUP) * 2)  # canonical packed bytes + fp16 scales: the algorithmic bytes
         copies = max(2, int(np.ceil(400e6 / wbytes)))
         p, s = weights(copies, N, K, fmt, k_terms, copy)
@@ -480,6 +482,8 @@ def main():
     ap.add_argument("--micro-only", default=None, choices=["decode", "prefill", "all"],
                     help="run only the single-kernel numbers (decode GEMV sweep and/or prefill grouped GEMM) and print them: "
                     "for profiler captures of those kernels; not a bench line")
+    ap.add_argument("--micro-case", default=None, help="with --micro-only decode: run one decode case, named fmt:N:K:terms:tiles|copy "
+                    "(e.g. tq2:4096:4096:1:tiles), for a profiler capture")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per step over all ranks (default: BASELINE config 4)")
     ap.add_argument("--experts", type=int, default=N_EXPERTS, help="routed experts (default: BASELINE config 4); smaller "
                     "values give a reduced case for profiler captures and are named in the JSON line")
@@ -493,7 +497,7 @@ def main():
         torch.cuda.set_device(device)
         sampler = ClockSampler(0)
         sampler.start()
-        print(json.dumps({"micro_only": args.micro_only, "gemm": gemm_microbench(device, measured_peaks(), which=args.micro_only, sampler=sampler)}))
+        print(json.dumps({"micro_only": args.micro_only, "gemm": gemm_microbench(device, measured_peaks(), which=args.micro_only, sampler=sampler, only=args.micro_case)}))
         sampler.close()
         return
 

@@ -55,8 +55,9 @@ def check_layer(got: np.ndarray, want: np.ndarray, exact64: np.ndarray):
 class OracleOps:
     """The MoE layer's compute steps on the CPU oracle, torch CPU tensors in and out."""
 
-    def route(self, logits, top_k, route_scale):
-        w, idx = O.route_from_logits(logits.float().numpy(), top_k, route_scale)
+    def route(self, logits, top_k, route_scale, renorm=True, score_func="softmax", bias=None, gate_temp=1.0):
+        w, idx = O.route_from_logits(logits.float().numpy(), top_k, route_scale, score_func,
+                                     None if bias is None else bias.float().numpy(), gate_temp, renorm)
         return torch.from_numpy(w), torch.from_numpy(idx.astype(np.int32))
 
     def sort(self, ids, n_experts):
@@ -64,13 +65,14 @@ class OracleOps:
         return torch.from_numpy(order), torch.from_numpy(offsets)
 
     def gather(self, x, order, top_k):
-        return x[order // top_k].contiguous()
+        return x if order is None else x[order // top_k].contiguous()
 
     def gemm(self, x, offsets, packed, scales, K, group, fmt):
         out = None
         xf = x.float().numpy()
+        offs = np.array([0, x.size(0)], np.int64) if offsets is None else offsets.numpy()  # None: one expert over all rows
         for p, s in zip(packed, scales):
-            out = O.grouped_gemm_f32(xf, offsets.numpy(), p.numpy(), s.float().numpy(), K, group, fmt, out=out)
+            out = O.grouped_gemm_f32(xf, offs, p.numpy(), s.float().numpy(), K, group, fmt, out=out)
         return bf16_tensor(O.bf16_round(out))
 
     def swiglu(self, gu, row_weights, order, inter, limit):
@@ -85,7 +87,7 @@ class OracleOps:
             h = (w[:, None].astype(np.float32) * h).astype(np.float32)
         return bf16_tensor(O.bf16_round(h))
 
-    def combine(self, down, order, ids, T, top_k):
+    def combine(self, down, order, ids, T, top_k, add=None):
         d = down.float().numpy()
         inv = np.empty(T * top_k, np.int64)
         inv[order.numpy()] = np.arange(T * top_k)
@@ -94,6 +96,8 @@ class OracleOps:
         for t in range(T):
             for s in np.argsort(idn[t], kind="stable"):
                 y[t] += d[inv[t * top_k + s]]
+        if add is not None:
+            y += add.float().numpy()
         return bf16_tensor(O.bf16_round(y))
 
 

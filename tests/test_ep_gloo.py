@@ -83,3 +83,26 @@ def test_uneven_expert_split_is_refused():
     assert expert_owner_split(384, 8) == 48
     with pytest.raises(ValueError):
         expert_owner_split(10, 4)
+
+
+@pytest.mark.parametrize("name", ["sigmoid", "sqrtsoftplus", "softmax_limit"])
+def test_layer_options_with_oracle_ops_equal_the_reference_fixture(golden, name):
+    """The layer's host logic for the V4 engine's options (score functions, gate bias, temperature, renormalisation
+    switch, route_scale, SwiGLU clamp, shared expert, and the entry that takes the engine's own routing) on CPU with
+    the oracle as compute: the output must be the oracle layer's, which the fixture pins to the reference's V4Model.moe."""
+    from deepseekternarized_b200.moe import ExpertWeights, MoELayer
+    from tests.test_oracle_golden import variant_case
+
+    c = variant_case(golden("moe_layer_variants"), name)
+    args = (c["hidden"], c["inter"], c["group"], c["fmt"])
+    w = ExpertWeights(*stack_experts(c["experts"], c["k_terms"]), *args)
+    shared = ExpertWeights(*stack_experts([c["shared"]], c["k_terms"]), *args) if c["shared"] is not None else None
+    bias = torch.from_numpy(c["bias"]) if c["bias"] is not None else None
+    layer = MoELayer(w, c["topk"], route_scale=c["route_scale"], swiglu_limit=c["limit"], ops=OracleOps(), norm_topk_prob=c["norm"],
+                     score_func=c["score_func"], gate_bias=bias, gate_temp=c["gate_temp"], shared=shared)
+    want = O.moe_layer(c["x"], c["weights"], c["indices"], c["experts"], *args, swiglu_limit=c["limit"], shared=c["shared"])
+    y = layer(bf16_tensor(c["x"]), torch.from_numpy(c["logits"]))
+    assert O.rel_fro(y.float().numpy(), want) < 2e-3  # the routing weights are recomputed here: last-bit differences allowed
+    y2 = layer.forward_routed(bf16_tensor(c["x"]), torch.from_numpy(c["weights"]), torch.from_numpy(c["indices"]))
+    assert np.array_equal(y2.float().numpy(), want)
+    assert np.mean(O.bf16_bits(want) != c["y_bits"]) < 0.02
