@@ -127,10 +127,21 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One try_wait. With PF_SUSPEND_NS > 0 the thread may be suspended by the hardware for up to that long while the phase
+// is incomplete and is resumed when it completes, so the roles that wait long (the accumulator drain, the producers)
+// leave the issue slots to the dequant warps instead of spinning through them.
+#ifndef PF_SUSPEND_NS
+#define PF_SUSPEND_NS 0
+#endif
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
+#if PF_SUSPEND_NS > 0
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity), "r"((uint32_t)PF_SUSPEND_NS) : "memory");
+#else
   asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+#endif
   return done != 0;
 }
 // Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed. BACKOFF sleeps between
