@@ -667,3 +667,47 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_gpu_usable(kb):
     y = run().cpu().numpy()
     assert lib.dst_check_device_status(None) == _lib.OK
     check_gemm(y, x, terms, K, 128, fmt)
+
+
+def test_ep_placement_kernel_swiglu_with_device_row_count_and_barrier():
+    """The pieces that keep an expert-parallel step free of host round trips: the placement kernel against the host
+    formula (deepseekternarized_b200.moe.ep_placement), SwiGLU over a buffer of larger capacity with the row count read
+    on the device, and the peer-memory barrier with one rank (its own flag word)."""
+    import ctypes
+
+    from deepseekternarized_b200 import _lib
+    from deepseekternarized_b200.kernels import ternary_b200 as kb
+    from deepseekternarized_b200.moe import ep_placement
+
+    lib = kb.ext()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rng = np.random.default_rng(2)
+    W, E = 4, 24
+    El = E // W
+    counts = torch.from_numpy(rng.integers(0, 9, (W, E))).to(DEV)
+    offs_all = torch.cat([torch.zeros(W, 1, dtype=torch.int64, device=DEV), counts.cumsum(1)], 1).contiguous()
+    for rank in range(W):
+        want_start, want_local = ep_placement(counts, rank, El)
+        dst_start = torch.empty(E, dtype=torch.int64, device=DEV)
+        local = torch.empty(El + 1, dtype=torch.int64, device=DEV)
+        _lib.check(lib.dst_ep_placement(offs_all.data_ptr(), W, E, El, rank, dst_start.data_ptr(), local.data_ptr(), stream))
+        assert torch.equal(dst_start, want_start) and torch.equal(local, want_local)
+    # SwiGLU with the row count on the device: the first n rows equal the plain call, the rest of the buffer is not written
+    cap, n, inter = 700, 333, 256
+    gu = bf16_tensor(rng.standard_normal((cap, 2 * inter)).astype(np.float32), DEV)
+    wts = torch.from_numpy(rng.random(cap).astype(np.float32)).to(DEV)
+    h0, f0 = torch.empty(n, inter, dtype=torch.float16, device=DEV), torch.empty(n, device=DEV)
+    _lib.check(lib.dst_swiglu_norm(gu.data_ptr(), wts.data_ptr(), None, n, inter, ctypes.c_float(0.0), h0.data_ptr(), f0.data_ptr(), stream))
+    h1 = torch.full((cap, inter), 7.0, dtype=torch.float16, device=DEV)
+    f1 = torch.full((cap,), 7.0, device=DEV)
+    n_dev = torch.tensor([n], dtype=torch.int64, device=DEV)
+    _lib.check(lib.dst_swiglu_norm_dev(gu.data_ptr(), wts.data_ptr(), None, cap, n_dev.data_ptr(), inter, ctypes.c_float(0.0), h1.data_ptr(),
+                                       f1.data_ptr(), stream))
+    assert torch.equal(h1[:n], h0) and torch.equal(f1[:n], f0) and bool((h1[n:] == 7.0).all()) and bool((f1[n:] == 7.0).all())
+    # one-rank barrier: stores its own flag and returns at once; the status stays clean
+    flags = torch.zeros(16, dtype=torch.int64, device=DEV)
+    table = (ctypes.c_void_p * 1)(flags.data_ptr())
+    for seq in (1, 2, 3):
+        _lib.check(lib.dst_ep_barrier(table, 1, 0, seq, stream))
+    torch.cuda.synchronize()
+    assert int(flags[0]) == 3 and lib.dst_check_device_status(None) == _lib.OK
