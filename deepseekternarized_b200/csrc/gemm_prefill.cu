@@ -113,6 +113,8 @@ struct PrefillParams {
   int rows_hint;    // most rows an expert is expected to have (host knowledge or twice the mean), sizes tn_max
   int nb;           // depth of the stage ring (B stage in shared memory + A slot in TMEM), 2..6
   int nslab;        // slots of the packed-slab ring, 2 or 3
+  int small;        // token tiles of at most 128 rows: four warps drain the accumulator and the other four of that role join
+                    // the dequantisation as a fifth group (the MMAs of such tiles are short, the dequantisation is the limit)
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -127,39 +129,55 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// One try_wait. With PF_SUSPEND_NS > 0 the thread may be suspended by the hardware for up to that long while the phase
-// is incomplete and is resumed when it completes, so the roles that wait long (the accumulator drain, the producers)
-// leave the issue slots to the dequant warps instead of spinning through them.
-#ifndef PF_SUSPEND_NS
-#define PF_SUSPEND_NS 0
+// Up to PF_SPIN_TRIES try_waits in a loop written in PTX: three to five instructions per poll. The same loop in C++
+// compiles to about nine (convergence bookkeeping around a divergent loop), and with every role of the CTA polling
+// some barrier most of the time the polls were ~40 % of all instructions this kernel issued at 64 rows per expert
+// (per-opcode counters: 147 try_waits, 350 branches, 135 BSSY/BSYNC pairs and 138 YIELDs per 64-K stage).
+#ifndef PF_SPLIT_MIN
+#define PF_SPLIT_MIN 64
 #endif
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+#ifndef PF_SPIN_TRIES
+#define PF_SPIN_TRIES 64
+#endif
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity) {
   uint32_t done;
-#if PF_SUSPEND_NS > 0
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(bar), "r"(parity), "r"((uint32_t)PF_SUSPEND_NS) : "memory");
-#else
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-#endif
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      ".reg .u32 n;\n"
+      "mov.u32 n, %3;\n"
+      "PF_SPIN:\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "@p bra PF_SPIN_DONE;\n"
+      "sub.u32 n, n, 1;\n"
+      "setp.ne.u32 q, n, 0;\n"
+      "@q bra PF_SPIN;\n"
+      "PF_SPIN_DONE:\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done) : "r"(bar), "r"(parity), "n"(PF_SPIN_TRIES) : "memory");
   return done != 0;
 }
-// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed. BACKOFF sleeps between
-// polls: for roles that wait long, so their polling does not take issue slots from the dequant warps.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait: false when the abort flag is up or ~2 s of clock cycles have passed (checked between bursts of polls).
+// BACKOFF sleeps between bursts: for roles that wait long, so their polling does not take issue slots from the dequant warps.
 template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
-  for (uint32_t it = 1;; ++it) {
-    if (BACKOFF) __nanosleep(40);
-    if (mbar_test(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > g_wait_cycles) {
-        *abort_flag = 1;
-        return false;
-      }
+  for (;;) {
+    if (mbar_spin(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > g_wait_cycles) {
+      *abort_flag = 1;
+      return false;
     }
+    if (BACKOFF) __nanosleep(40);
   }
 }
 
@@ -420,7 +438,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
       mbar_init(smem_u32(&bar_empty[s]), 2);     // one tcgen05.commit per MMA issuer: the MMAs that read the stage are done
     }
     mbar_init(smem_u32(&bar_tfull[0]), 2);             // one tcgen05.commit per MMA issuer after the tile's last MMA
-    mbar_init(smem_u32(&bar_tempty[0]), PF_EPI_WARPS);  // every epilogue warp has drained its quarter of the accumulator
+    mbar_init(smem_u32(&bar_tempty[0]), p.small ? 4 : PF_EPI_WARPS);  // every epilogue warp has drained its share of the accumulator
     for (int a = 0; a < PF_MAX_SLABS; ++a) {
       mbar_init(smem_u32(&bar_pfull[a]), 1);         // bulk-copy producer's expect_tx arrive
       mbar_init(smem_u32(&bar_pempty[a]), 4 * SPB);  // one arrive per (stage of the superblock, warp of its group)
@@ -533,7 +551,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         if (!__all_sync(0xffffffffu, RT_WAIT(w_tempty, mbar_wait(smem_u32(&bar_tempty[0]), (tile & 1u) ^ 1u, abort_flag)))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t n_eff = (uint32_t)tile_neff(rows);
-        const bool split = n_eff >= 64u && (n_eff & 31u) == 0u;  // tiles above 256 rows are padded to 32: always split
+        const bool split = n_eff >= (uint32_t)PF_SPLIT_MIN && (n_eff & 31u) == 0u;  // tiles above 256 rows are padded to 32: always split
         const uint32_t h = split ? n_eff >> 1 : n_eff;           // token rows per MMA (a multiple of 16, at most 256)
         const bool active = split || who == 0u;
         // instruction descriptor: D f32, A f16, B f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
@@ -568,14 +586,14 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         RT_ADD(8, RT_NOW() - t_begin); RT_ADD(9, w_tempty); RT_ADD(10, w_full); RT_ADD(11, n_it); RT_ADD(12, 1); RT_ADD(13, tile);
       }
     }
-  } else if (warp < PF_DQ_WARP0) {
+  } else if (warp < PF_CTRL_WARPS + (p.small ? 4 : PF_EPI_WARPS)) {
     // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
     const int r = (warp & 3) * 32 + lane;  // a warp may only read the TMEM lanes of its own quarter (warp id % 4)
     uint32_t tile = 0;
     for (int t = (int)blockIdx.x; t < n_tiles; t += t_step, ++tile) {
       tile_seek(p, offs, tpre, t, e, nt, row0, rows);
       // the two warps of a lane quarter take alternate 32-column chunks
-      if (!drain_tile(p, tmem, ((warp - PF_CTRL_WARPS) >> 2) * 32, 32 * (PF_EPI_WARPS / 4), r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]),
+      if (!drain_tile(p, tmem, ((warp - PF_CTRL_WARPS) >> 2) * 32, p.small ? 32 : 32 * (PF_EPI_WARPS / 4), r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]),
                       abort_flag, nt, row0, rows, tile))
         break;
     }
@@ -584,7 +602,9 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     // A warp may only touch the TMEM lanes of its own quarter (warp id % 4): it owns those 32 weight rows.
     const int q = warp & 3;
     const int r = q * 32 + lane;
-    const uint32_t grp = (uint32_t)(warp - PF_DQ_WARP0) >> 2;
+    // groups 0..3: warps 12..27; with small token tiles warps 8..11 (epilogue warps otherwise) are group 4
+    const uint32_t n_groups = p.small ? PF_GROUPS + 1 : PF_GROUPS;
+    const uint32_t grp = warp >= PF_DQ_WARP0 ? (uint32_t)(warp - PF_DQ_WARP0) >> 2 : (uint32_t)PF_GROUPS;
     const int swz = (r >> 1) & 3;  // swizzle of the tiled layout: logical word w sits at physical word (((w & 3) ^ swz) << 2) | (w >> 2)
     const uint32_t lut_addr = smem_u32(lut) + (uint32_t)(lane & 15) * 4u;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
@@ -596,23 +616,23 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     bool ok = true;
     RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, w_st = 0, w_pre = 0, n_it = 0, t_begin = RT_NOW());
 
-    // scales of the row: 8 groups (16 stages) per 128-bit load, the block of the group's next stage fetched one stage ahead
+    // scales of the row: 8 groups (16 stages) per 128-bit load; when a block of 8 is taken into use the tile's next block
+    // is requested, so only a tile's first block is waited for (once per tile and warp; the per-stage cost is a compare)
     uint4 sc[TERMS], scn[TERMS];
-    int cur_t = -1, nxt_t = -1, cur_b = -1, nxt_b = -1;  // (tile, block of 8 groups) held in sc / requested into scn
-    auto load_scales = [&](int ee, int nn, int g0, uint4* dst) {
-      const bool n_ok = nn < p.N;
+    int cur_b = -1, nxt_b = -1;              // block of 8 groups held in sc / requested into scn, of the current tile
+    const __half* srow[TERMS];               // the row's scales of the current tile (null: a row beyond N, scales read as 0)
+    auto load_scales = [&](int g0, uint4* dst) {
 #pragma unroll
       for (int i = 0; i < TERMS; ++i) {
         if (i < p.n_terms) {
-          if (!n_ok || g0 >= p.G) {
+          if (srow[i] == nullptr || g0 >= p.G) {
             dst[i] = make_uint4(0u, 0u, 0u, 0u);
           } else if (vec_scales) {
-            dst[i] = *reinterpret_cast<const uint4*>(p.scale[i] + ((int64_t)ee * p.N + nn) * p.G + g0);
+            dst[i] = *reinterpret_cast<const uint4*>(srow[i] + g0);
           } else {
             uint32_t h[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              h[j] = g0 + j < p.G ? (uint32_t)__half_as_ushort(p.scale[i][((int64_t)ee * p.N + nn) * p.G + g0 + j]) : 0u;
+            for (int j = 0; j < 8; ++j) h[j] = g0 + j < p.G ? (uint32_t)__half_as_ushort(srow[i][g0 + j]) : 0u;
             dst[i] = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
           }
         }
@@ -633,6 +653,10 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         t += t_step;
         tile_seek(p, offs, tpre, t, e, nt, row0, rows);
         n = nt * 128 + r;
+#pragma unroll
+        for (int i = 0; i < TERMS; ++i)
+          if (i < p.n_terms) srow[i] = n < p.N ? p.scale[i] + ((int64_t)e * p.N + n) * p.G : nullptr;
+        cur_b = nxt_b = -1;
         in_tile = true;
         continue;
       }
@@ -643,34 +667,17 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         const uint32_t slot = p.nslab == 2 ? (gs & 1u) : gs % 3u, sround = p.nslab == 2 ? (gs >> 1) : gs / 3u;
         // scales
         const int blk = ks >> 4;
-        if (!(cur_t == t && cur_b == blk)) {
-          if (nxt_t == t && nxt_b == blk) {
+        if (blk != cur_b) {
+          if (nxt_b == blk) {
 #pragma unroll
             for (int i = 0; i < TERMS; ++i) sc[i] = scn[i];
           } else {
-            load_scales(e, n, blk * 8, sc);
+            load_scales(blk * 8, sc);
           }
-          cur_t = t;
           cur_b = blk;
-        }
-        {
-          int nks = ks + PF_GROUPS, pe = e, pn = n, pt = t;
-          if (nks >= kstages) {  // in the next tile (looked up here once per tile; e is a valid search hint)
-            nks -= kstages;
-            pt = t + t_step < n_tiles ? t + t_step : -1;
-            if (pt >= 0 && nks < kstages) {
-              int x_nt, x_row0, x_rows;
-              tile_seek(p, offs, tpre, pt, pe, x_nt, x_row0, x_rows);
-              pn = x_nt * 128 + r;
-            }
-          }
-          if (pt >= 0 && nks < kstages) {
-            const int b2 = nks >> 4;
-            if (!(pt == cur_t && b2 == cur_b) && !(pt == nxt_t && b2 == nxt_b)) {
-              load_scales(pe, pn, b2 * 8, scn);
-              nxt_t = pt;
-              nxt_b = b2;
-            }
+          if ((blk + 1) * 8 < p.G) {  // the tile's next block, needed a few of this warp's stages from now
+            load_scales((blk + 1) * 8, scn);
+            nxt_b = blk + 1;
           }
         }
         const int g = (ks >> 1) & 7;  // 64-trit stage -> 128-trit scale group, inside the 8 held in sc
@@ -742,8 +749,8 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
         RT_SPAN(w_st, t_st);
-        own += PF_GROUPS;
-        s += PF_GROUPS;
+        own += n_groups;
+        s += n_groups;
         while (s >= NB) { s -= NB; ph ^= 1u; }
     }
     if (warp == PF_DQ_WARP0 && lane == 0) {
@@ -838,6 +845,7 @@ int launch_fmt(const TmaMaps& maps, PrefillParams p, cudaStream_t st) {
   }
   if (p.tn_max == 0 || p.nb < 2) return DST_ERR_UNSUPPORTED;
   p.nslab = fixed + 3LL * p.n_terms * PF_SLAB + (long long)p.nb * p.tn_max * 128 <= budget ? 3 : 2;
+  p.small = p.tn_max <= 128 ? 1 : 0;
   const size_t smem = (size_t)(fixed + (long long)p.nslab * p.n_terms * PF_SLAB + (long long)p.nb * p.tn_max * 128);
   auto kernel = prefill_kernel<FMT, TERMS>;
   DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
