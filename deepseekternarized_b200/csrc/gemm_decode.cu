@@ -38,15 +38,17 @@
 namespace dst {
 namespace {
 
-constexpr int DC_CWARPS = 4;                     // consumer warps, 16 weight rows each
-constexpr int DC_THREADS = (DC_CWARPS + 1) * 32;  // + the producer warp
-constexpr int DC_PART = DC_CWARPS * 16 * 64;      // bytes of one item's share of a slab: 64 rows x 64 B
-constexpr int DC_SLOT_DATA = 2 * DC_PART;         // a ring slot holds the item's share of TWO superblocks (four scale groups)
-constexpr int DC_SLOT = DC_SLOT_DATA + 16;        // ... followed by its own "full" and "empty" mbarriers (one address register serves all)
+// CW consumer warps of 16 weight rows each (+ the producer warp) make a CTA; a work item is CW * 16 rows of one expert
+// over the whole of K. Few token rows: CW = 4 and several CTAs per SM. Eight or more: the staged token rows take most of
+// an SM's shared memory, so ONE CTA of 16 consumer warps shares them.
+constexpr int DC_QWARPS = 4;                      // warps per block of decode_quant_kernel
+__host__ __device__ constexpr int dc_part(int cw) { return cw * 16 * 64; }           // bytes of one item's share of a superblock: 64 B per row
+__host__ __device__ constexpr int dc_slot_data(int cw) { return 2 * dc_part(cw); }   // a ring slot holds the item's share of TWO superblocks (four scale groups)
+__host__ __device__ constexpr int dc_slot(int cw) { return dc_slot_data(cw) + 16; }  // ... followed by its own "full" and "empty" mbarriers (one address register serves all)
 #ifndef DC_RING_SLOTS
 #define DC_RING_SLOTS 4
 #endif
-constexpr int DC_RING = DC_RING_SLOTS;            // slots of the slab ring
+constexpr int DC_RING_MAX = DC_RING_SLOTS;        // slots of the slab ring (fewer, at least 2, when shared memory is short)
 #ifndef DC_PRODUCER_SLEEP
 #define DC_PRODUCER_SLEEP true
 #endif
@@ -68,6 +70,8 @@ struct DecodeParams {
   void* out;
   int out_dtype, accumulate;
   int E, T, N, K, G, NT, S;
+  int ring;     // slots of the slab ring
+  int GP;       // ints between the staged per-group sums of consecutive token rows: odd, so the four tokens a quad reads hit four banks
   int xstride;  // bytes between staged activation rows: K + 64 (= 64 mod 128: two rows read together hit all banks once)
   // activations quantised ahead of the GEMV by decode_quant_kernel (null: the GEMV's consumer warps do it per expert)
   const uint8_t* q_rows;  // [T][2][K] s8: the hi and the lo row of every token, bytes in the staged order
@@ -135,18 +139,19 @@ __device__ __forceinline__ void mma_u8s8(int* d, uint32_t a0, uint32_t a1, uint3
 }
 
 // ------------------------------------------------------------------------------------------ work items
-// Item -> (expert, 64-row half tile). Rows of the expert and passes over them (MT token rows per pass).
+// Item -> (expert, block of RI = 64, 128 or 256 weight rows starting at row n0). Token rows [ra, rb) of the expert.
 struct Item {
-  int e, nt, half;
+  int e, n0;
   int64_t ra, rb;
 };
+template <int RI>
+__host__ __device__ __forceinline__ int items_per_expert(int NT) { return (NT * 128 + RI - 1) / RI; }
+template <int RI>
 __device__ __forceinline__ Item item_of(const DecodeParams& p, long long item) {
   Item it;
-  const int nh = p.NT * 2;
-  it.e = (int)(item / nh);
-  const int ht = (int)(item - (long long)it.e * nh);
-  it.nt = ht >> 1;
-  it.half = ht & 1;
+  const int ipe = items_per_expert<RI>(p.NT);
+  it.e = (int)(item / ipe);
+  it.n0 = (int)(item - (long long)it.e * ipe) * RI;
   row_range(p.offsets, it.e, p.T, it.ra, it.rb);
   return it;
 }
@@ -195,20 +200,20 @@ __device__ __forceinline__ float amax8(const int8_t*) { return 0.f; }
 //                           position q4 * 64 + c * 16 + (m & 1) * 8 + h * 4 + b holds trit 16 (c + 4 (2 gi + h)) + tw,
 //                           tw = {2 j, 8 + 2 j, 2 j + 1, 9 + 2 j}[b], MMA m = 4 gi + j of the superblock, q4 = m / 2
 //                           (lane c's B registers b0 (h = 0) and b1 (h = 1) of MMAs 2 q4 and 2 q4 + 1 = 16 bytes)
-//   xsum4[tok][g]           4 * sum of q over scale group g (int32); zero for token slots beyond mc
+//   xsum4[tok * xsum_stride + g]  4 * sum of q over scale group g (int32); zero for token slots beyond mc
 //   xexp[tok]               s_tok * row_scale / 4 (NaN when the row holds a non-finite value)
-template <int MT, typename XT, typename Sync>
+template <int MT, int CW, typename XT, typename Sync>
 __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, int64_t m0, int mc, uint8_t* xs, size_t xstride, int* xsum4,
-                             float* xexp, float* xinv, Sync&& consumer_sync) {
+                             int xsum_stride, float* xexp, float* xinv, Sync&& consumer_sync) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr bool IS_I8 = sizeof(XT) == 1;
   // pass 1: row maxima. Every consumer thread takes 128-bit pieces of every row; the warps' partial maxima meet in
-  // xinv[m * DC_CWARPS + warp] (xinv has room for that: see the shared-memory plan in the kernel)
+  // xinv[m * CW + warp] (xinv has room for that: see the shared-memory plan in the kernel)
   if (!IS_I8) {
     for (int m = 0; m < mc; ++m) {
       const XT* row = x + (m0 + m) * p.K;
       float am = 0.f;
-      for (int i = threadIdx.x * 8; i < p.K; i += DC_CWARPS * 32 * 8) {
+      for (int i = threadIdx.x * 8; i < p.K; i += CW * 32 * 8) {
         const float a = amax8(row + i);
         am = (a > am || a != a) ? a : am;
       }
@@ -216,7 +221,7 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
         const float o = __shfl_xor_sync(0xffffffffu, am, off);
         am = (o > am || o != o) ? o : am;
       }
-      if (lane == 0) xinv[m * DC_CWARPS + warp] = am;
+      if (lane == 0) xinv[m * CW + warp] = am;
     }
     if (!consumer_sync()) return false;
   }
@@ -231,8 +236,8 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
       } else {
         float amax = 0.f;
 #pragma unroll
-        for (int w = 0; w < DC_CWARPS; ++w) {
-          const float o = xinv[lane * DC_CWARPS + w];
+        for (int w = 0; w < CW; ++w) {
+          const float o = xinv[lane * CW + w];
           amax = (o > amax || o != o) ? o : amax;
         }
         if (!(amax <= 3.0e38f)) {
@@ -248,7 +253,7 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
   }
   // pass 2: one warp per (token slot, 128-trit group): lane = position / 4 inside the group's 128 bytes
   const int c = (lane >> 2) & 3, j = ((lane >> 4) & 1) * 2 + ((lane >> 1) & 1), h = lane & 1;
-  for (int u = warp; u < MT * p.G; u += DC_CWARPS) {
+  for (int u = warp; u < MT * p.G; u += CW) {
     const int m = u / p.G, g = u - m * p.G;
     const float inv = __shfl_sync(0xffffffffu, my_inv, m);
     int sum = 0;
@@ -277,30 +282,36 @@ __device__ bool stage_tokens(const DecodeParams& p, const XT* __restrict__ x, in
       *reinterpret_cast<uint32_t*>(xs + (size_t)(2 * m + 1) * xstride + pos) = wlo;
     }
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane == 0) xsum4[m * p.G + g] = 4 * sum;
+    if (lane == 0) xsum4[m * xsum_stride + g] = 4 * sum;
   }
   return true;
 }
 
 // The staging above done ONCE per token, ahead of the GEMV, into global memory: with more than a few rows per expert
 // the GEMV's CTAs would otherwise repeat it for every expert they touch (measured at 8 rows: a quarter to a half of
-// their instructions). One block of DC_CWARPS warps per token row.
+// their instructions). One block of DC_QWARPS warps per token row.
 template <typename XT>
-__global__ void __launch_bounds__(DC_CWARPS * 32)
+__global__ void __launch_bounds__(DC_QWARPS * 32)
 decode_quant_kernel(const DecodeParams p, uint8_t* __restrict__ q_rows, int* __restrict__ q_xsum4, float* __restrict__ q_xexp) {
-  __shared__ float xinv[DC_CWARPS];
+  __shared__ float xinv[DC_QWARPS];
   const int64_t t = blockIdx.x;
   auto sync = []() -> bool {
     __syncthreads();
     return true;
   };
   // token t as a "pass" of one row: row_scale, the row pointer and the outputs are all indexed by t through m0 = t
-  stage_tokens<1>(p, static_cast<const XT*>(p.x), t, 1, q_rows + (size_t)t * 2 * p.K, (size_t)p.K, q_xsum4 + t * p.G, q_xexp + t, xinv, sync);
+  stage_tokens<1, DC_QWARPS>(p, static_cast<const XT*>(p.x), t, 1, q_rows + (size_t)t * 2 * p.K, (size_t)p.K, q_xsum4 + t * p.G, p.G, q_xexp + t, xinv, sync);
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
 // GS = scale groups that share an MMA's columns (4: one token row per pass, 2: two, 1: four per column block);
-// NB = column blocks (GS == 1 only): 4 NB token rows per pass.
+// NB = column blocks (GS == 1 only): 4 NB token rows per pass; CW = consumer warps; RW = 16-row MMA tiles per warp.
+//
+// Many rows (RW == 2): every MMA needs 256 B of token columns from shared memory, which at the MMA rate of an SM is
+// all of its shared-memory bandwidth; a warp that owns two 16-row tiles feeds both from one read. There the x1 / x4
+// field trick is dropped as well: all four fields of a byte are shifted down to plain digits (three shifts per word
+// more) and accumulate together, so the per-group epilogue has one merge less per output and the second set of
+// accumulators is gone.
 #ifndef DC_MINB
 #define DC_MINB 4
 #endif
@@ -310,18 +321,26 @@ decode_quant_kernel(const DecodeParams p, uint8_t* __restrict__ q_rows, int* __r
 #ifndef DC_MINB4
 #define DC_MINB4 2
 #endif
-template <int GS, int NB, typename XT>
-__global__ void __launch_bounds__(DC_THREADS, NB == 1 ? DC_MINB : (NB == 2 ? DC_MINB2 : DC_MINB4))
+__host__ __device__ constexpr int dc_min_blocks(int nb, int cw) { return cw > 4 ? 1 : (nb == 1 ? DC_MINB : (nb == 2 ? DC_MINB2 : DC_MINB4)); }
+
+template <int GS, int NB, int CW, int RW, typename XT>
+__global__ void __launch_bounds__((CW + 1) * 32, dc_min_blocks(NB, CW))
 decode_kernel(const DecodeParams p) {
   constexpr int MT = 4 * NB / GS;  // token rows per pass
   constexpr int TPB = 4 / GS;      // token rows per column block
+  constexpr int THREADS = (CW + 1) * 32;
+  constexpr int RI = CW * RW * 16;  // weight rows of an item
+  constexpr int PART = dc_part(CW * RW), SLOT_DATA = dc_slot_data(CW * RW), SLOT = dc_slot(CW * RW);
+  constexpr bool ONEACC = RW > 1;
+  static_assert(GS == 1 || NB == 1, "column blocks only with one scale group per MMA");
+  static_assert(RI == 64 || RI == 128 || RI == 256, "an item is half a tile, a tile or two tiles");
   extern __shared__ __align__(128) uint8_t dsm[];
-  uint8_t* ring = dsm;                                           // DC_RING x DC_SLOT: [two parts][full barrier][empty barrier]
-  uint8_t* zero = ring + DC_RING * DC_SLOT;                      // DC_ZERO
+  uint8_t* ring = dsm;                                           // p.ring x SLOT: [two parts][full barrier][empty barrier]
+  uint8_t* zero = ring + p.ring * SLOT;                          // DC_ZERO
   uint8_t* xs = zero + DC_ZERO;                                  // 2 MT staged rows
-  int* xsum4 = reinterpret_cast<int*>(xs + (size_t)2 * MT * p.xstride);  // [MT][G]
-  float* xexp = reinterpret_cast<float*>(xsum4 + MT * p.G);      // [MT]
-  float* xinv = xexp + MT;                                       // [MT][DC_CWARPS] partial row maxima
+  int* xsum4 = reinterpret_cast<int*>(xs + (size_t)2 * MT * p.xstride);  // [MT][GP]
+  float* xexp = reinterpret_cast<float*>(xsum4 + MT * p.GP);     // [MT]
+  float* xinv = xexp + MT;                                       // [MT][CW] partial row maxima
   __shared__ uint64_t bar_stage, bar_rows;
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
@@ -329,41 +348,55 @@ decode_kernel(const DecodeParams p) {
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < DC_RING; ++s) {
-      mbar_init(smem_u32(ring + s * DC_SLOT + DC_SLOT_DATA), 1);                   // full: the producer's expect_tx arrive
-      mbar_init(smem_u32(ring + s * DC_SLOT + DC_SLOT_DATA + 8), DC_CWARPS * 32);  // empty: one arrive per consumer thread
+    for (int s = 0; s < p.ring; ++s) {
+      mbar_init(smem_u32(ring + s * SLOT + SLOT_DATA), 1);            // full: the producer's expect_tx arrive
+      mbar_init(smem_u32(ring + s * SLOT + SLOT_DATA + 8), CW * 32);  // empty: one arrive per consumer thread
     }
-    mbar_init(smem_u32(&bar_stage), DC_CWARPS);       // the consumer warps' own barrier (bounded, unlike bar.sync)
+    mbar_init(smem_u32(&bar_stage), CW);              // the consumer warps' own barrier (bounded, unlike bar.sync)
     mbar_init(smem_u32(&bar_rows), 1);                // pre-quantised token rows have landed (expect_tx arrive of the thread that copies)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = threadIdx.x; i < DC_ZERO / 4; i += DC_THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
+  for (int i = threadIdx.x; i < DC_ZERO / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
   __syncthreads();
 
   // contiguous, equally sized (+-1) range of items for this CTA
-  const long long items = (long long)p.E * p.NT * 2;
+  const long long items = (long long)p.E * items_per_expert<RI>(p.NT);
   const long long i0 = items * blockIdx.x / gridDim.x, i1 = items * (blockIdx.x + 1) / gridDim.x;
 
-  if (warp == DC_CWARPS) {
+  if (warp == CW) {
     // ------------------------------------------------------------------ producer: packed slabs -> ring
     if (lane == 0) {
-      const uint32_t ring_a = smem_u32(ring), ring_end = ring_a + DC_RING * DC_SLOT;
+      const uint32_t ring_a = smem_u32(ring), ring_end = ring_a + p.ring * SLOT;
       uint32_t sbase = ring_a, ph = 0;
       bool ok = true;
       for (long long item = i0; ok && item < i1; ++item) {
-        const Item it = item_of(p, item);
+        const Item it = item_of<RI>(p, item);
         const int passes = (int)((it.rb - it.ra + MT - 1) / MT);
-        const int64_t off0 = (((int64_t)it.e * p.NT + it.nt) * p.S) * 8192 + it.half * DC_PART;
+        // the item's rows inside the slab of their tile; 256 rows: two whole tiles (the second may not exist)
+        const int tile = it.n0 >> 7;
+        const int64_t off0 = (((int64_t)it.e * p.NT + tile) * p.S) * 8192 + (it.n0 & 127) * 64;
+        const bool two = RI == 256 && tile + 1 < p.NT;
+        const int64_t tile_step = (int64_t)p.S * 8192;
         for (int ps = 0; ok && ps < passes; ++ps)
           for (int term = 0; ok && term < p.n_terms; ++term)
             for (int sb = 0; sb < p.S; sb += 2) {
-              if (!mbar_wait<DC_PRODUCER_SLEEP>(sbase + DC_SLOT_DATA + 8, ph ^ 1u, abort_flag)) { ok = false; break; }
-              const uint32_t full = sbase + DC_SLOT_DATA;
-              mbar_arrive_expect_tx(full, DC_SLOT_DATA);
+              if (!mbar_wait<DC_PRODUCER_SLEEP>(sbase + SLOT_DATA + 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+              const uint32_t full = sbase + SLOT_DATA;
               const uint8_t* src = p.tiled[term] + off0 + (int64_t)sb * 8192;
-              bulk_load(sbase, src, DC_PART, full);
-              bulk_load(sbase + DC_PART, src + 8192, DC_PART, full);
-              sbase += DC_SLOT;
+              if (RI == 256) {
+                mbar_arrive_expect_tx(full, two ? SLOT_DATA : SLOT_DATA / 2);
+                bulk_load(sbase, src, 8192, full);
+                bulk_load(sbase + PART, src + 8192, 8192, full);
+                if (two) {
+                  bulk_load(sbase + 8192, src + tile_step, 8192, full);
+                  bulk_load(sbase + PART + 8192, src + tile_step + 8192, 8192, full);
+                }
+              } else {
+                mbar_arrive_expect_tx(full, SLOT_DATA);
+                bulk_load(sbase, src, PART, full);
+                bulk_load(sbase + PART, src + 8192, PART, full);
+              }
+              sbase += SLOT;
               if (sbase == ring_end) { sbase = ring_a; ph ^= 1u; }
             }
       }
@@ -372,12 +405,13 @@ decode_kernel(const DecodeParams p) {
     // ------------------------------------------------------------------ consumers
     const int g8 = lane >> 2, c = lane & 3;
     const int swz = (g8 >> 1) & 3;
-    const uint32_t a_off = (uint32_t)((warp * 16 + g8) * 64 + ((c ^ swz) << 4));  // this lane's unit of row g8; row g8 + 8: + 512
+    // this lane's unit of row g8 of the warp's first 16-row tile; row g8 + 8: + 512; the second tile: + 1024
+    const uint32_t a_off = (uint32_t)((warp * 16 * RW + g8) * 64 + ((c ^ swz) << 4));
     const uint32_t ring_a = smem_u32(ring), zero_a = smem_u32(zero), xs_a = smem_u32(xs);
     // B column of this lane: pair g8 / 2, part g8 & 1; C columns of this lane: pair c
     const int col_pair = g8 >> 1, col_part = g8 & 1;
     const int tok_c = c / GS, slot_c = c % GS;  // (+ b * TPB) the token and the group slot of this lane's C columns
-    const uint32_t ring_end = ring_a + DC_RING * DC_SLOT;
+    const uint32_t ring_end = ring_a + p.ring * SLOT;
     uint32_t sbase = ring_a, ph = 0, stage_ph = 0, rows_ph = 0;  // the current ring slot and the parity of its "full" phase
     int staged_e = -1;
     int64_t staged_m0 = -1;
@@ -391,8 +425,8 @@ decode_kernel(const DecodeParams p) {
     };
 
     for (long long item = i0; item < i1; ++item) {
-      const Item it = item_of(p, item);
-      const int n_lo = it.nt * 128 + it.half * 64 + warp * 16 + g8, n_hi = n_lo + 8;
+      const Item it = item_of<RI>(p, item);
+      const int n_first = it.n0 + warp * 16 * RW + g8;  // this lane's output rows: n_first + 8 i, i < 2 RW
       for (int64_t m0 = it.ra; m0 < it.rb; m0 += MT) {
         const int mc = (int)(it.rb - m0 < MT ? it.rb - m0 : MT);
         if (staged_e != it.e || staged_m0 != m0) {
@@ -407,94 +441,180 @@ decode_kernel(const DecodeParams p) {
               for (int m = 0; m < 2 * mc; ++m)
                 bulk_load(xs_a + (uint32_t)m * (uint32_t)p.xstride, p.q_rows + ((size_t)m0 * 2 + m) * p.K, (uint32_t)p.K, bar);
             }
-            for (int i = threadIdx.x; i < MT * p.G; i += DC_CWARPS * 32) xsum4[i] = i < mc * p.G ? p.q_xsum4[m0 * p.G + i] : 0;
+            for (int m = warp; m < MT; m += CW)
+              for (int g = lane; g < p.G; g += 32) xsum4[m * p.GP + g] = m < mc ? p.q_xsum4[(m0 + m) * p.G + g] : 0;
             if (threadIdx.x < MT) xexp[threadIdx.x] = threadIdx.x < mc ? p.q_xexp[m0 + threadIdx.x] : 0.f;
             if (!mbar_wait(smem_u32(&bar_rows), rows_ph, abort_flag)) goto aborted;
             rows_ph ^= 1u;
-          } else if (!stage_tokens<MT>(p, static_cast<const XT*>(p.x), m0, mc, xs, (size_t)p.xstride, xsum4, xexp, xinv, consumer_sync)) {
+          } else if (!stage_tokens<MT, CW>(p, static_cast<const XT*>(p.x), m0, mc, xs, (size_t)p.xstride, xsum4, p.GP, xexp, xinv, consumer_sync)) {
             goto aborted;
           }
           if (!consumer_sync()) goto aborted;
           staged_e = it.e;
           staged_m0 = m0;
         }
-        // B pointers: for block b and phase s (= group % GS) the lane reads its column's staged row when the column's
-        // pair belongs to that phase and its token exists, else the zeros
-        uint32_t bbase[NB][GS], bstep[NB][GS];
+        // B pointers. Shared columns (GS > 1): for phase s (= group % GS) the lane reads its column's staged row when
+        // the column's pair belongs to that phase and its token exists, else the zeros. One group per MMA (GS == 1):
+        // column pair j of block b is token 4 b + j; the columns of tokens that do not exist read whatever the staged
+        // rows hold there (integers: an MMA column only reaches its own outputs, which are not stored).
+        constexpr int NPTR = GS > 1 ? GS : 1;
+        uint32_t bbase[NPTR], bstep[NPTR];
+        uint32_t bblock = 0;  // GS == 1: bytes between the staged rows of consecutive column blocks
+        if (GS > 1) {
 #pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-          for (int s = 0; s < GS; ++s) {
-            const int tok = b * TPB + col_pair / GS;
+          for (int s = 0; s < NPTR; ++s) {
+            const int tok = col_pair / GS;
             const bool act = (col_pair % GS) == s && tok < mc;
-            bbase[b][s] = act ? xs_a + (uint32_t)(2 * tok + col_part) * (uint32_t)p.xstride + (uint32_t)c * 16u : zero_a;
-            bstep[b][s] = act ? 256u : 0u;
+            bbase[s] = act ? xs_a + (uint32_t)(2 * tok + col_part) * (uint32_t)p.xstride + (uint32_t)c * 16u : zero_a;
+            bstep[s] = act ? 256u : 0u;
           }
-        float y[NB][2];
+        } else {
+          bbase[0] = xs_a + (uint32_t)(2 * col_pair + col_part) * (uint32_t)p.xstride + (uint32_t)c * 16u;
+          bstep[0] = 256u;
+          bblock = 8u * (uint32_t)p.xstride;
+        }
+        float y[RW][NB][2];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) y[b][0] = y[b][1] = 0.f;
+        for (int t = 0; t < RW; ++t)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) y[t][b][0] = y[t][b][1] = 0.f;
 
         for (int term = 0; term < p.n_terms; ++term) {
-          const __half* s_lo = p.scale[term] + ((int64_t)it.e * p.N + (n_lo < p.N ? n_lo : 0)) * p.G;
-          const __half* s_hi = p.scale[term] + ((int64_t)it.e * p.N + (n_hi < p.N ? n_hi : 0)) * p.G;
-          int accA[NB][4], accB[NB][4];
+          // scale rows of this lane's outputs (rows beyond N read row 0 and are not stored)
+          const __half* srow[2 * RW];
 #pragma unroll
-          for (int b = 0; b < NB; ++b)
+          for (int i = 0; i < 2 * RW; ++i) {
+            const int n = n_first + 8 * i;
+            srow[i] = p.scale[term] + ((int64_t)it.e * p.N + (n < p.N ? n : 0)) * p.G;
+          }
+          int accA[RW][NB][4], accB[ONEACC ? 1 : NB][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) accA[b][i] = accB[b][i] = 0;
+          for (int t = 0; t < RW; ++t)
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) accA[t][b][i] = 0;
+#pragma unroll
+          for (int b = 0; b < (ONEACC ? 1 : NB); ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) accB[b][i] = 0;
           // scales of the lane's group of the next epilogue, requested a block of groups ahead
           auto scale_at = [&](const __half* s, int grp) { return grp < p.G ? __half2float(s[grp]) : 0.f; };
-          float sl_n = scale_at(s_lo, slot_c), sh_n = scale_at(s_hi, slot_c);
+          float s_next[2 * RW];
+#pragma unroll
+          for (int i = 0; i < 2 * RW; ++i) s_next[i] = scale_at(srow[i], slot_c);
           // epilogue of the block of GS groups whose first group is g_first: this lane's group is g_first + slot_c
           auto epilogue = [&](int g_first) {
             const int g_mine = g_first + slot_c;
-            const float sl = sl_n, sh = sh_n;
-            sl_n = scale_at(s_lo, g_mine + GS);
-            sh_n = scale_at(s_hi, g_mine + GS);
+            float sc[2 * RW];
+#pragma unroll
+            for (int i = 0; i < 2 * RW; ++i) {
+              sc[i] = s_next[i];
+              s_next[i] = scale_at(srow[i], g_mine + GS);
+            }
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-              const int xs4 = g_mine < p.G ? xsum4[(b * TPB + tok_c) * p.G + g_mine] : 0;
-              // 4 * sum_k u_k q_k = 128 * (4 A_hi + B_hi) + (4 A_lo + B_lo); minus 4 * sum_k q_k
-              const int v_lo = ((((accA[b][0] << 2) + accB[b][0]) << 7) + ((accA[b][1] << 2) + accB[b][1])) - xs4;
-              const int v_hi = ((((accA[b][2] << 2) + accB[b][2]) << 7) + ((accA[b][3] << 2) + accB[b][3])) - xs4;
-              y[b][0] = fmaf(sl, (float)v_lo, y[b][0]);
-              y[b][1] = fmaf(sh, (float)v_hi, y[b][1]);
+              const int xs4 = g_mine < p.G ? xsum4[(b * TPB + tok_c) * p.GP + g_mine] : 0;
+#pragma unroll
+              for (int t = 0; t < RW; ++t) {
+                int v_lo, v_hi;
+                if (ONEACC) {
+                  // 4 * sum_k u_k q_k = 4 * (128 * A_hi + A_lo); minus 4 * sum_k q_k
+                  v_lo = (accA[t][b][0] << 9) + ((accA[t][b][1] << 2) - xs4);
+                  v_hi = (accA[t][b][2] << 9) + ((accA[t][b][3] << 2) - xs4);
+                } else {
+                  // 4 * sum_k u_k q_k = 128 * (4 A_hi + B_hi) + (4 A_lo + B_lo); minus 4 * sum_k q_k
+                  v_lo = ((((accA[t][b][0] << 2) + accB[b][0]) << 7) + ((accA[t][b][1] << 2) + accB[b][1])) - xs4;
+                  v_hi = ((((accA[t][b][2] << 2) + accB[b][2]) << 7) + ((accA[t][b][3] << 2) + accB[b][3])) - xs4;
+                }
+                y[t][b][0] = fmaf(sc[2 * t], (float)v_lo, y[t][b][0]);
+                y[t][b][1] = fmaf(sc[2 * t + 1], (float)v_hi, y[t][b][1]);
+              }
             }
           };
 
           // two superblocks (one ring slot, four scale groups) per iteration: the phase of every group (group % GS) is a
-          // compile-time value, and the barrier traffic and slot arithmetic are paid once per 2 KB of this warp's rows
+          // compile-time value, and the barrier traffic and slot arithmetic are paid once per 2 KB of a 16-row tile
           for (int sb0 = 0; sb0 < p.S; sb0 += 2) {
-            if (!mbar_wait(sbase + DC_SLOT_DATA, ph, abort_flag)) goto aborted;
+            if (!mbar_wait(sbase + SLOT_DATA, ph, abort_flag)) goto aborted;
             const uint32_t sa = sbase + a_off;
-            const uint4 w_lo2[2] = {lds128(sa), lds128(sa + DC_PART)}, w_hi2[2] = {lds128(sa + 512), lds128(sa + DC_PART + 512)};
-            mbar_arrive(sbase + DC_SLOT_DATA + 8);  // every lane arrives for itself: its four loads above are done
-            sbase += DC_SLOT;
+            // [superblock][tile]: rows g8 and g8 + 8. One tile per warp: both superblocks' words are read up front and the
+            // slot is handed back at once; two tiles: the second superblock's words are read after the first one's MMAs
+            // (registers), and the slot goes back then
+            uint4 w_lo2[2][RW], w_hi2[2][RW];
+            const uint32_t slot_bar = sbase + SLOT_DATA + 8;
+#pragma unroll
+            for (int u = 0; u < (RW == 1 ? 2 : 1); ++u)
+#pragma unroll
+              for (int t = 0; t < RW; ++t) {
+                w_lo2[u][t] = lds128(sa + u * PART + t * 1024);
+                w_hi2[u][t] = lds128(sa + u * PART + t * 1024 + 512);
+              }
+            if (RW == 1) mbar_arrive(slot_bar);  // every lane arrives for itself: its loads above are done
+            sbase += SLOT;
             if (sbase == ring_end) { sbase = ring_a; ph ^= 1u; }
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const int sb = sb0 + u;
-              const uint4 w_lo = w_lo2[u], w_hi = w_hi2[u];
+              if (RW > 1 && u == 1) {
+#pragma unroll
+                for (int t = 0; t < RW; ++t) {
+                  w_lo2[1][t] = lds128(sa + PART + t * 1024);
+                  w_hi2[1][t] = lds128(sa + PART + t * 1024 + 512);
+                }
+                mbar_arrive(slot_bar);
+              }
 #pragma unroll
               for (int gi = 0; gi < 2; ++gi) {
                 constexpr uint32_t M1 = 0x03030303u, M4 = 0x0c0c0c0cu;
                 const int phase = (u * 2 + gi) % GS;   // group % GS
                 const bool fresh = phase == 0;         // first group of an epilogue block: the accumulators restart
-                const uint32_t l0 = gi ? w_lo.z : w_lo.x, l1 = gi ? w_lo.w : w_lo.y, h0 = gi ? w_hi.z : w_hi.x, h1 = gi ? w_hi.w : w_hi.y;
-                const uint32_t l0s = l0 >> 4, l1s = l1 >> 4, h0s = h0 >> 4, h1s = h1 >> 4;
+                const uint32_t bgrp = bbase[phase] + (uint32_t)sb * bstep[phase] + (uint32_t)gi * 128u;
+                if (ONEACC) {
+                  // operands of both tiles: [tile][field][a0..a3]
+                  uint32_t op[RW][4][4];
 #pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                  const uint32_t ba = bbase[b][phase] + (uint32_t)sb * bstep[b][phase] + (uint32_t)gi * 128u;
-                  const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
-                  if (fresh) {
-                    mma_u8s8<true>(accA[b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
-                    mma_u8s8<true>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
-                  } else {
-                    mma_u8s8<false>(accA[b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
-                    mma_u8s8<false>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
+                  for (int t = 0; t < RW; ++t) {
+                    const uint4 w_lo = w_lo2[u][t], w_hi = w_hi2[u][t];
+                    const uint32_t wd[4] = {gi ? w_lo.z : w_lo.x, gi ? w_hi.z : w_hi.x, gi ? w_lo.w : w_lo.y, gi ? w_hi.w : w_hi.y};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      op[t][0][i] = wd[i] & M1;
+                      op[t][1][i] = (wd[i] >> 2) & M1;
+                      op[t][2][i] = (wd[i] >> 4) & M1;
+                      op[t][3][i] = (wd[i] >> 6) & M1;
+                    }
                   }
-                  mma_u8s8<false>(accA[b], l0s & M1, h0s & M1, l1s & M1, h1s & M1, q1.x, q1.y);
-                  mma_u8s8<false>(accB[b], l0s & M4, h0s & M4, l1s & M4, h1s & M4, q1.z, q1.w);
+#pragma unroll
+                  for (int b = 0; b < NB; ++b) {
+                    const uint32_t ba = bgrp + (uint32_t)b * bblock;
+                    const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
+#pragma unroll
+                    for (int t = 0; t < RW; ++t) {
+                      mma_u8s8<true>(accA[t][b], op[t][0][0], op[t][0][1], op[t][0][2], op[t][0][3], q0.x, q0.y);
+                      mma_u8s8<false>(accA[t][b], op[t][1][0], op[t][1][1], op[t][1][2], op[t][1][3], q0.z, q0.w);
+                      mma_u8s8<false>(accA[t][b], op[t][2][0], op[t][2][1], op[t][2][2], op[t][2][3], q1.x, q1.y);
+                      mma_u8s8<false>(accA[t][b], op[t][3][0], op[t][3][1], op[t][3][2], op[t][3][3], q1.z, q1.w);
+                    }
+                  }
+                } else {
+                  const uint4 w_lo = w_lo2[u][0], w_hi = w_hi2[u][0];
+                  const uint32_t l0 = gi ? w_lo.z : w_lo.x, l1 = gi ? w_lo.w : w_lo.y, h0 = gi ? w_hi.z : w_hi.x, h1 = gi ? w_hi.w : w_hi.y;
+                  const uint32_t l0s = l0 >> 4, l1s = l1 >> 4, h0s = h0 >> 4, h1s = h1 >> 4;
+#pragma unroll
+                  for (int b = 0; b < NB; ++b) {
+                    const uint32_t ba = bgrp + (uint32_t)b * bblock;
+                    const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
+                    if (fresh) {
+                      mma_u8s8<true>(accA[0][b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
+                      mma_u8s8<true>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
+                    } else {
+                      mma_u8s8<false>(accA[0][b], l0 & M1, h0 & M1, l1 & M1, h1 & M1, q0.x, q0.y);
+                      mma_u8s8<false>(accB[b], l0 & M4, h0 & M4, l1 & M4, h1 & M4, q0.z, q0.w);
+                    }
+                    mma_u8s8<false>(accA[0][b], l0s & M1, h0s & M1, l1s & M1, h1s & M1, q1.x, q1.y);
+                    mma_u8s8<false>(accB[b], l0s & M4, h0s & M4, l1s & M4, h1s & M4, q1.z, q1.w);
+                  }
                 }
                 if (phase == GS - 1) epilogue(sb * 2 + gi - (GS - 1));
               }
@@ -503,12 +623,14 @@ decode_kernel(const DecodeParams p) {
         }
         // the quad's lanes hold the partial sums of their group slots
 #pragma unroll
-        for (int b = 0; b < NB; ++b)
+        for (int t = 0; t < RW; ++t)
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            if (GS >= 2) y[b][i] += __shfl_xor_sync(0xffffffffu, y[b][i], 1);
-            if (GS == 4) y[b][i] += __shfl_xor_sync(0xffffffffu, y[b][i], 2);
-          }
+          for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (GS >= 2) y[t][b][i] += __shfl_xor_sync(0xffffffffu, y[t][b][i], 1);
+              if (GS == 4) y[t][b][i] += __shfl_xor_sync(0xffffffffu, y[t][b][i], 2);
+            }
         if (slot_c == 0) {
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
@@ -516,10 +638,10 @@ decode_kernel(const DecodeParams p) {
             if (tok < mc) {
               const float f = xexp[tok];
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const int n = i ? n_hi : n_lo;
+              for (int i = 0; i < 2 * RW; ++i) {
+                const int n = n_first + 8 * i;
                 if (n < p.N) {
-                  const float v = y[b][i] * f;
+                  const float v = y[i >> 1][b][i & 1] * f;
                   const int64_t o = (m0 + tok) * p.N + n;
                   if (p.out_dtype == DST_OUT_F32) {
                     float* out = static_cast<float*>(p.out);
@@ -549,32 +671,54 @@ decode_kernel(const DecodeParams p) {
   if (threadIdx.x == 0 && abort_s) atomicExch(&g_decode_status, DST_ERR_TIMEOUT);
 }
 
-template <int GS, int NB, typename XT>
-int launch_one(const DecodeParams& p, int sms, cudaStream_t stream) {
+// Shared memory of a CTA apart from its ring
+template <int GS, int NB, int CW>
+size_t decode_fixed_smem(const DecodeParams& p) {
   constexpr int MT = 4 * NB / GS;
-  const size_t smem = (size_t)DC_RING * DC_SLOT + DC_ZERO + (size_t)2 * MT * p.xstride + (size_t)MT * p.G * 4 + (size_t)MT * 4 * (1 + DC_CWARPS);
-  if (smem > 220 * 1024) return DST_ERR_UNSUPPORTED;
-  auto kernel = decode_kernel<GS, NB, XT>;
+  return DC_ZERO + (size_t)2 * MT * p.xstride + (size_t)MT * p.GP * 4 + (size_t)MT * 4 * (1 + CW);
+}
+
+template <int GS, int NB, int CW, int RW, typename XT>
+int launch_one(DecodeParams p, int sms, cudaStream_t stream) {
+  constexpr int THREADS = (CW + 1) * 32, RI = CW * RW * 16, SLOT = dc_slot(CW * RW);
+  const size_t budget = 226 * 1024, fixed = decode_fixed_smem<GS, NB, CW>(p);  // 227 KB per CTA less the static barriers
+  if (fixed + (size_t)2 * SLOT > budget) return DST_ERR_UNSUPPORTED;
+  // small CTAs: the full ring, and as many CTAs per SM as fit; the 256-row CTA: one per SM, the ring takes what is left
+  const size_t room = (budget - fixed) / SLOT;
+  p.ring = (int)(room < (size_t)DC_RING_MAX ? room : (size_t)DC_RING_MAX);
+  const size_t smem = (size_t)p.ring * SLOT + fixed;
+  auto kernel = decode_kernel<GS, NB, CW, RW, XT>;
   DST_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
-  DST_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, DC_THREADS, smem));
+  DST_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem));
   if (per_sm < 1) return DST_ERR_UNSUPPORTED;
-  const long long items = (long long)p.E * p.NT * 2;
+  const long long items = (long long)p.E * items_per_expert<RI>(p.NT);
   const long long want = (long long)sms * per_sm;
   const int grid = (int)(items < want ? items : want);
-  kernel<<<grid, DC_THREADS, smem, stream>>>(p);
+  kernel<<<grid, THREADS, smem, stream>>>(p);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }
 
+#ifndef DC_WIDE_FROM
+#define DC_WIDE_FROM 5
+#endif
 template <typename XT>
 int launch_rows(const DecodeParams& p, int64_t rows_hint, int sms, cudaStream_t stream) {
-  if (rows_hint <= 1) return launch_one<4, 1, XT>(p, sms, stream);
-  if (rows_hint <= 2) return launch_one<2, 1, XT>(p, sms, stream);
-  if (rows_hint <= 4) return launch_one<1, 1, XT>(p, sms, stream);
-  if (rows_hint <= 8) return launch_one<1, 2, XT>(p, sms, stream);
-  const int rc = launch_one<1, 4, XT>(p, sms, stream);
-  return rc == DST_ERR_UNSUPPORTED ? launch_one<1, 2, XT>(p, sms, stream) : rc;  // 16 staged rows of a long K may not fit
+  if (rows_hint <= 1) return launch_one<4, 1, 4, 1, XT>(p, sms, stream);
+  if (rows_hint <= 2) return launch_one<2, 1, 4, 1, XT>(p, sms, stream);
+  if (rows_hint < DC_WIDE_FROM && rows_hint <= 4) return launch_one<1, 1, 4, 1, XT>(p, sms, stream);
+  // five or more rows: one CTA per SM whose eight consumer warps own 32 weight rows each and share the staged token
+  // rows (8, then 16 per pass), when there is a 256-row item for every SM; else the small CTAs
+  const long long wide_items = (long long)p.E * items_per_expert<256>(p.NT);
+  if (wide_items >= sms) {
+    int rc = rows_hint <= 8 ? DST_ERR_UNSUPPORTED : launch_one<1, 4, 8, 2, XT>(p, sms, stream);
+    if (rc == DST_ERR_UNSUPPORTED) rc = launch_one<1, 2, 8, 2, XT>(p, sms, stream);
+    if (rc != DST_ERR_UNSUPPORTED) return rc;
+  }
+  if (rows_hint <= 4) return launch_one<1, 1, 4, 1, XT>(p, sms, stream);
+  const int rc = launch_one<1, 2, 4, 1, XT>(p, sms, stream);
+  return rc == DST_ERR_UNSUPPORTED ? launch_one<1, 1, 4, 1, XT>(p, sms, stream) : rc;  // 16 staged rows of a long K may not fit
 }
 
 }  // namespace
@@ -590,7 +734,7 @@ bool decode_supports(const GemmArgs& a) {
   if (a.fmt == DST_FMT_TQ1) return decode_tq1_supports(a);
   return a.weight_layout == DST_LAYOUT_TILED && a.fmt == DST_FMT_TQ2 && a.group == 128 && a.K % 512 == 0 &&
          a.scale_dtype == DST_SCALE_F16 && (a.act_dtype == DST_ACT_BF16 || a.act_dtype == DST_ACT_F16 || a.act_dtype == DST_ACT_I8) &&
-         (size_t)DC_RING * DC_SLOT + DC_ZERO + (size_t)16 * (a.K + 64) + (size_t)8 * (a.G + 8) * 4 <= 220 * 1024 &&
+         (size_t)2 * dc_slot(4) + DC_ZERO + (size_t)8 * (a.K + 64) + (size_t)4 * (a.G + 8) * 4 <= 220 * 1024 &&
          a.T < (int64_t(1) << 31);
 }
 
@@ -622,6 +766,8 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   p.NT = (int)cdiv64(a.N, 128);
   p.S = (int)tiled_superblocks(a.fmt, a.K);
   p.xstride = (int)(a.K + 64);
+  p.ring = DC_RING_MAX;
+  p.GP = p.G | 1;
   p.q_rows = nullptr;
   p.q_xsum4 = nullptr;
   p.q_xexp = nullptr;
@@ -638,9 +784,9 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
     uint8_t* q_rows = base;
     int* q_xsum4 = reinterpret_cast<int*>(base + up((size_t)a.T * 2 * (size_t)a.K));
     float* q_xexp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(q_xsum4) + up((size_t)a.T * (size_t)a.G * 4));
-    if (a.act_dtype == DST_ACT_BF16) decode_quant_kernel<__nv_bfloat16><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
-    else if (a.act_dtype == DST_ACT_F16) decode_quant_kernel<__half><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
-    else decode_quant_kernel<int8_t><<<(unsigned)a.T, DC_CWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    if (a.act_dtype == DST_ACT_BF16) decode_quant_kernel<__nv_bfloat16><<<(unsigned)a.T, DC_QWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    else if (a.act_dtype == DST_ACT_F16) decode_quant_kernel<__half><<<(unsigned)a.T, DC_QWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
+    else decode_quant_kernel<int8_t><<<(unsigned)a.T, DC_QWARPS * 32, 0, stream>>>(p, q_rows, q_xsum4, q_xexp);
     DST_CUDA_TRY(cudaGetLastError());
     p.q_rows = q_rows;
     p.q_xsum4 = q_xsum4;

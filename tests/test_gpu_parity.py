@@ -286,6 +286,36 @@ def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo, fmt):
             np.testing.assert_allclose(y[a:b], want, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("N,K,terms_k", [(1024, 1024, 1), (384, 512, 2)])
+def test_grouped_decode_sixteen_warp_ctas(kb, N, K, terms_k):
+    """Five or more rows per expert with at least one 256-row item per SM: the decode GEMV runs as one CTA of 16
+    consumer warps per SM (8 or 16 staged rows per pass). Ragged row counts around the pass sizes, empty experts, an
+    odd number of 128-row tiles (the last item has one tile only); int8 rows are exact integer group sums."""
+    E = 160
+    rng = np.random.default_rng(N + K)
+    terms = make_terms(rng, N, K, 128, "tq2", terms_k, lead=(E,))
+    for top in (8, 16, 21):
+        counts = rng.integers(max(1, top - 7), top + 1, E)
+        counts[[3, 77]] = 0
+        counts[5] = top
+        offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+        x = O.synth_acts(rng, (int(offsets[-1]), K))
+        tiled = [kb.tile_weights(torch.from_numpy(p).to(DEV), "tq2", K) for p, _ in terms]
+        scales = [torch.from_numpy(s).to(DEV) for _, s in terms]
+        y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, tiled, scales, K, 128, "tq2", algo="decode")
+        torch.cuda.synchronize()
+        assert kb.ext().dst_check_device_status(None) == 0
+        y = y.cpu().numpy()
+        assert np.isfinite(y).all()
+        for e in (0, 4, 5, 76, 78, E - 1):
+            a, b = int(offsets[e]), int(offsets[e + 1])
+            check_gemm(y[a:b], x[a:b], [(p[e], s[e]) for p, s in terms], K, 128, "tq2")
+        want = O.grouped_gemm_f32(O.bf16_round(x), offsets, terms[0][0], terms[0][1].astype(np.float32), K, 128, "tq2")
+        for p_, s_ in terms[1:]:
+            want = want + O.grouped_gemm_f32(O.bf16_round(x), offsets, p_, s_.astype(np.float32), K, 128, "tq2")
+        np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-3)
+
+
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])
 def test_prefill_many_tiles_per_cta(kb, fmt):
     """More tiles than SMs, so every persistent CTA of the tcgen05 kernel walks several tiles (ring phases, the
