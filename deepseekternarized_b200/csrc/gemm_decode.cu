@@ -333,6 +333,7 @@ decode_kernel(const DecodeParams p) {
   constexpr int PART = dc_part(CW * RW), SLOT_DATA = dc_slot_data(CW * RW), SLOT = dc_slot(CW * RW);
   constexpr bool ONEACC = RW > 1;
   static_assert(GS == 1 || NB == 1, "column blocks only with one scale group per MMA");
+  static_assert(RW == 1 || NB % 2 == 0, "two-tile warps take the column blocks in pairs");
   static_assert(RI == 64 || RI == 128 || RI == 256, "an item is half a tile, a tile or two tiles");
   extern __shared__ __align__(128) uint8_t dsm[];
   uint8_t* ring = dsm;                                           // p.ring x SLOT: [two parts][full barrier][empty barrier]
@@ -487,48 +488,67 @@ decode_kernel(const DecodeParams p) {
             const int n = n_first + 8 * i;
             srow[i] = p.scale[term] + ((int64_t)it.e * p.N + (n < p.N ? n : 0)) * p.G;
           }
-          int accA[RW][NB][4], accB[ONEACC ? 1 : NB][4];
-#pragma unroll
-          for (int t = 0; t < RW; ++t)
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) accA[t][b][i] = 0;
+          int accA[1][ONEACC ? 1 : NB][4], accB[ONEACC ? 1 : NB][4];  // the x1 and the x4 fields' sums (one tile per warp)
 #pragma unroll
           for (int b = 0; b < (ONEACC ? 1 : NB); ++b)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) accB[b][i] = 0;
-          // scales of the lane's group of the next epilogue, requested a block of groups ahead
+            for (int i = 0; i < 4; ++i) accA[0][b][i] = accB[b][i] = 0;
+          // scales of the lane's group of the next epilogue, requested ahead: a block of GS groups (shared columns), or
+          // two groups at a time, two groups ahead, as one 32-bit load per output row (GS == 1; G is a multiple of 4)
           auto scale_at = [&](const __half* s, int grp) { return grp < p.G ? __half2float(s[grp]) : 0.f; };
+          auto scale2_at = [&](const __half* s, int grp) { return grp < p.G ? *reinterpret_cast<const uint32_t*>(s + grp) : 0u; };
           float s_next[2 * RW];
+          uint32_t s2_cur[2 * RW], s2_next[2 * RW];
 #pragma unroll
-          for (int i = 0; i < 2 * RW; ++i) s_next[i] = scale_at(srow[i], slot_c);
-          // epilogue of the block of GS groups whose first group is g_first: this lane's group is g_first + slot_c
-          auto epilogue = [&](int g_first) {
+          for (int i = 0; i < 2 * RW; ++i) {
+            s_next[i] = GS > 1 ? scale_at(srow[i], slot_c) : 0.f;
+            s2_cur[i] = 0u;
+            s2_next[i] = GS == 1 ? scale2_at(srow[i], 0) : 0u;
+          }
+          // Epilogue of the block of GS groups whose first group is g_first: this lane's group is g_first + slot_c.
+          // First the group's scales (odd: g_first & 1 as a compile-time value) ...
+          float sc[2 * RW];
+          auto take_scales = [&](int g_first, bool odd) {
             const int g_mine = g_first + slot_c;
-            float sc[2 * RW];
 #pragma unroll
             for (int i = 0; i < 2 * RW; ++i) {
-              sc[i] = s_next[i];
-              s_next[i] = scale_at(srow[i], g_mine + GS);
+              if (GS > 1) {
+                sc[i] = s_next[i];
+                s_next[i] = scale_at(srow[i], g_mine + GS);
+              } else {
+                if (!odd) {
+                  s2_cur[i] = s2_next[i];
+                  s2_next[i] = scale2_at(srow[i], g_first + 2);
+                }
+                const __half2 h2 = *reinterpret_cast<const __half2*>(&s2_cur[i]);
+                sc[i] = odd ? __high2float(h2) : __low2float(h2);
+              }
             }
+          };
+          // ... then per column block: 4 * sum_k u_k q_k - 4 * sum_k q_k as one integer, converted and multiplied.
+          // x1 / x4 accumulators: 128 * (4 A_hi + B_hi) + (4 A_lo + B_lo)
+          auto epilogue = [&](int g_first) {
+            const int g_mine = g_first + slot_c;
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
               const int xs4 = g_mine < p.G ? xsum4[(b * TPB + tok_c) * p.GP + g_mine] : 0;
+              const int v_lo = ((((accA[0][b][0] << 2) + accB[b][0]) << 7) + ((accA[0][b][1] << 2) + accB[b][1])) - xs4;
+              const int v_hi = ((((accA[0][b][2] << 2) + accB[b][2]) << 7) + ((accA[0][b][3] << 2) + accB[b][3])) - xs4;
+              y[0][b][0] = fmaf(sc[0], (float)v_lo, y[0][b][0]);
+              y[0][b][1] = fmaf(sc[1], (float)v_hi, y[0][b][1]);
+            }
+          };
+          // plain digits, one accumulator set, a pair of column blocks: 4 * (128 * A_hi + A_lo)
+          auto epilogue_pair = [&](int g, int b0, const int (&acc)[RW][2][4]) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int xs4 = xsum4[((b0 + j) * TPB + tok_c) * p.GP + g];
 #pragma unroll
               for (int t = 0; t < RW; ++t) {
-                int v_lo, v_hi;
-                if (ONEACC) {
-                  // 4 * sum_k u_k q_k = 4 * (128 * A_hi + A_lo); minus 4 * sum_k q_k
-                  v_lo = (accA[t][b][0] << 9) + ((accA[t][b][1] << 2) - xs4);
-                  v_hi = (accA[t][b][2] << 9) + ((accA[t][b][3] << 2) - xs4);
-                } else {
-                  // 4 * sum_k u_k q_k = 128 * (4 A_hi + B_hi) + (4 A_lo + B_lo); minus 4 * sum_k q_k
-                  v_lo = ((((accA[t][b][0] << 2) + accB[b][0]) << 7) + ((accA[t][b][1] << 2) + accB[b][1])) - xs4;
-                  v_hi = ((((accA[t][b][2] << 2) + accB[b][2]) << 7) + ((accA[t][b][3] << 2) + accB[b][3])) - xs4;
-                }
-                y[t][b][0] = fmaf(sc[2 * t], (float)v_lo, y[t][b][0]);
-                y[t][b][1] = fmaf(sc[2 * t + 1], (float)v_hi, y[t][b][1]);
+                const int v_lo = (acc[t][j][0] << 9) + ((acc[t][j][1] << 2) - xs4);
+                const int v_hi = (acc[t][j][2] << 9) + ((acc[t][j][3] << 2) - xs4);
+                y[t][b0 + j][0] = fmaf(sc[2 * t], (float)v_lo, y[t][b0 + j][0]);
+                y[t][b0 + j][1] = fmaf(sc[2 * t + 1], (float)v_hi, y[t][b0 + j][1]);
               }
             }
           };
@@ -585,17 +605,31 @@ decode_kernel(const DecodeParams p) {
                       op[t][3][i] = (wd[i] >> 6) & M1;
                     }
                   }
+                  // two column blocks at a time, field by field: consecutive MMAs go to different accumulators (four
+                  // independent chains), so none waits for the one before it; a pair's epilogue follows its MMAs, so
+                  // it can run under the next pair's
+                  take_scales(sb * 2 + gi, gi == 1);
 #pragma unroll
-                  for (int b = 0; b < NB; ++b) {
-                    const uint32_t ba = bgrp + (uint32_t)b * bblock;
-                    const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
+                  for (int b0 = 0; b0 < NB; b0 += 2) {
+                    uint32_t bq[2][4][2];  // [block][field][b0, b1]
 #pragma unroll
-                    for (int t = 0; t < RW; ++t) {
-                      mma_u8s8<true>(accA[t][b], op[t][0][0], op[t][0][1], op[t][0][2], op[t][0][3], q0.x, q0.y);
-                      mma_u8s8<false>(accA[t][b], op[t][1][0], op[t][1][1], op[t][1][2], op[t][1][3], q0.z, q0.w);
-                      mma_u8s8<false>(accA[t][b], op[t][2][0], op[t][2][1], op[t][2][2], op[t][2][3], q1.x, q1.y);
-                      mma_u8s8<false>(accA[t][b], op[t][3][0], op[t][3][1], op[t][3][2], op[t][3][3], q1.z, q1.w);
+                    for (int j = 0; j < 2; ++j) {
+                      const uint32_t ba = bgrp + (uint32_t)(b0 + j) * bblock;
+                      const uint4 q0 = lds128(ba), q1 = lds128(ba + 64);
+                      bq[j][0][0] = q0.x; bq[j][0][1] = q0.y; bq[j][1][0] = q0.z; bq[j][1][1] = q0.w;
+                      bq[j][2][0] = q1.x; bq[j][2][1] = q1.y; bq[j][3][0] = q1.z; bq[j][3][1] = q1.w;
                     }
+                    int acc[RW][2][4];
+#pragma unroll
+                    for (int f = 0; f < 4; ++f)
+#pragma unroll
+                      for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int t = 0; t < RW; ++t) {
+                          if (f == 0) mma_u8s8<true>(acc[t][j], op[t][f][0], op[t][f][1], op[t][f][2], op[t][f][3], bq[j][f][0], bq[j][f][1]);
+                          else mma_u8s8<false>(acc[t][j], op[t][f][0], op[t][f][1], op[t][f][2], op[t][f][3], bq[j][f][0], bq[j][f][1]);
+                        }
+                    epilogue_pair(sb * 2 + gi, b0, acc);
                   }
                 } else {
                   const uint4 w_lo = w_lo2[u][0], w_hi = w_hi2[u][0];
@@ -616,7 +650,10 @@ decode_kernel(const DecodeParams p) {
                     mma_u8s8<false>(accB[b], l0s & M4, h0s & M4, l1s & M4, h1s & M4, q1.z, q1.w);
                   }
                 }
-                if (phase == GS - 1) epilogue(sb * 2 + gi - (GS - 1));
+                if (!ONEACC && phase == GS - 1) {
+                  take_scales(sb * 2 + gi - (GS - 1), gi == 1);
+                  epilogue(sb * 2 + gi - (GS - 1));
+                }
               }
             }
           }
