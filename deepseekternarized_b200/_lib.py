@@ -73,6 +73,7 @@ _SIGNATURES = {
                                           ctypes.c_void_p, ctypes.c_void_p]),
     "dst_quant_act_int8_f16": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
                                               ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_decode_row_limit": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64]),
     "dst_ternary_grouped_gemm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                                 ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,

@@ -113,12 +113,14 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
   if (act_dtype == DST_ACT_F16_NORM) return launch_prefill(a, st);  // only the tcgen05 kernel reads this format
   // AUTO: few rows per expert -> decode GEMV; many -> tcgen05 grouped GEMM; otherwise generic.
   const int64_t avg_rows = a.max_rows >= 0 ? a.max_rows : cdiv64(T, E);
-  if (avg_rows <= 16 && decode_supports(a)) return launch_decode(a, st);
+  if (avg_rows <= decode_row_limit(fmt, E, N) && decode_supports(a)) return launch_decode(a, st);
   if (prefill_supports(a)) return launch_prefill(a, st);
   if (decode_supports(a)) return launch_decode(a, st);
   if (weight_layout == DST_LAYOUT_TILED) return DST_ERR_UNSUPPORTED;
   return launch_generic(a, st);
 }
+
+extern "C" int64_t dst_decode_row_limit(int fmt, int64_t E, int64_t N) { return dst::decode_row_limit(fmt, E, N); }
 
 extern "C" size_t dst_gemm_workspace_bytes(int algo, int act_dtype, int64_t T, int64_t K) {
   if (T <= 0 || K <= 0 || algo == DST_ALGO_GENERIC) return 0;

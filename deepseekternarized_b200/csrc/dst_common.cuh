@@ -56,6 +56,7 @@ int launch_generic(const GemmArgs& a, cudaStream_t stream);
 int launch_decode(const GemmArgs& a, cudaStream_t stream);    // DST_ERR_UNSUPPORTED when not covered
 int launch_prefill(const GemmArgs& a, cudaStream_t stream);   // DST_ERR_UNSUPPORTED when not covered
 bool decode_supports(const GemmArgs& a);
+int64_t decode_row_limit(int fmt, int64_t E, int64_t N);  // rows per expert up to which AUTO prefers the decode GEMV
 int launch_decode_tq1(const GemmArgs& a, cudaStream_t stream);  // TQ1 decode kernel (gemm_decode_tq1.cu); reached through launch_decode
 bool decode_tq1_supports(const GemmArgs& a);
 bool prefill_supports(const GemmArgs& a);

@@ -611,6 +611,7 @@ decode_kernel(const DecodeParams p) {
                   take_scales(sb * 2 + gi, gi == 1);
 #pragma unroll
                   for (int b0 = 0; b0 < NB; b0 += 2) {
+                    if (b0 > 0 && b0 * TPB >= mc) continue;  // a short last pass: no token rows in this pair of blocks
                     uint32_t bq[2][4][2];  // [block][field][b0, b1]
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
@@ -765,6 +766,14 @@ size_t decode_workspace_bytes(int64_t T, int64_t K) {
   const size_t G = (size_t)(K / 128);
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   return up((size_t)T * 2 * (size_t)K) + up((size_t)T * G * 4) + up((size_t)T * 4);
+}
+
+// Up to how many token rows per expert the decode GEMV beats the tcgen05 kernel (measured on 4096 x 4096 experts): 32
+// where the many-row CTAs apply (TQ2 tiles, a 256-row item for every SM; two passes of 16 rows), else 16.
+int64_t decode_row_limit(int fmt, int64_t E, int64_t N) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return fmt == DST_FMT_TQ2 && E * ((N + 255) / 256) >= sms ? 32 : 16;
 }
 
 bool decode_supports(const GemmArgs& a) {

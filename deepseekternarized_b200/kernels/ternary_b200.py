@@ -185,6 +185,12 @@ def _offsets(offsets, E: int, T: int, device, validate: bool):
     return dev, host
 
 
+def _decode_row_limit(E: int, N: int) -> int:
+    """Rows per expert up to which the 2-bit decode copy of TQ1 weights is the faster path (the library's AUTO rule for
+    TQ2 tiles)."""
+    return int(_require("auto").dst_decode_row_limit(_lib.FMT_TQ2, E, N))
+
+
 def _grouped(lib, x, row_scale, offsets, packed_terms, scale_terms, K, group, fmt, out, accumulate, algo,
              validate_offsets=True, act_code=None):
     """Shared launcher. packed_terms[i] [E, N, Kp] uint8, scale_terms[i] [E, N, G]."""
@@ -202,7 +208,7 @@ def _grouped(lib, x, row_scale, offsets, packed_terms, scale_terms, K, group, fm
             raise RuntimeError("inconsistent ternary GEMM shapes")
         # few rows per expert and a 2-bit copy of the TQ1 trits on the device: the decode GEMV reads that copy
         if fmt == "tq1" and algo in ("auto", "decode") and act_code != _lib.ACT_F16_NORM and all(p.decode is not None for p in packed_terms) \
-                and x.size(0) <= 16 * packed_terms[0].E:
+                and x.size(0) <= _decode_row_limit(packed_terms[0].E, packed_terms[0].N) * packed_terms[0].E:
             packed_terms, fmt, code, algo = [p.decode for p in packed_terms], "tq2", _lib.FMT_TQ2, "decode"
     elif algo != "generic" and fast_path_covers(K, group, scale_terms[0].dtype, x.dtype) and all(
             p.is_cuda and p.dtype == torch.uint8 and p.dim() == 3 for p in packed_terms) and (

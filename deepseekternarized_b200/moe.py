@@ -118,8 +118,12 @@ class B200Ops:
         return kb.sort_by_expert(ids.reshape(-1), n_experts)
 
     def _norm_ok(self, weights, rows: int) -> bool:
-        return (self.fused_norm and self.algo in ("auto", "prefill") and isinstance(weights[0], kb.TiledWeights)
-                and rows > 16 * weights[0].E)
+        if not (self.fused_norm and self.algo in ("auto", "prefill") and isinstance(weights[0], kb.TiledWeights)):
+            return False
+        w = weights[0]
+        # few rows per expert stay bf16 for the decode GEMV (TQ2 tiles, or TQ1 with its 2-bit decode copy)
+        decode_rows = kb._decode_row_limit(w.E, w.N) if self.algo == "auto" and (w.fmt == "tq2" or w.decode is not None) else 16
+        return rows > decode_rows * w.E
 
     def gather(self, x: torch.Tensor, order: torch.Tensor | None, top_k: int, for_weights=None):
         """Rows ``x[order // top_k]`` (``order`` None: the rows as they are)."""

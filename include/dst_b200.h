@@ -158,6 +158,13 @@ int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate, const voi
 /* Scratch bytes dst_ternary_grouped_gemm needs for `algo` (AUTO: the largest any kernel may need). */
 size_t dst_gemm_workspace_bytes(int algo, int act_dtype, int64_t T, int64_t K);
 
+/* Token rows per expert up to which DST_ALGO_AUTO sends tiled weights of `fmt` (E experts of N rows) to the
+ * decode GEMV rather than the tcgen05 kernel: 16, or 32 where the decode GEMV's many-row form applies. A caller
+ * that keeps a second, decode-friendly copy of its weights (the Python layer's 2-bit copy of TQ1 trits) picks
+ * the copy by the same rule. No reference counterpart: the reference has one kernel for every row count
+ * (boilerplate/kernels/csrc/ternary_cuda_kernel.cu:44-99). */
+int64_t dst_decode_row_limit(int fmt, int64_t E, int64_t N);
+
 /*
  * Routing sort: flattened expert ids [n] (int64 or int32) -> the stable order that sorts them by
  * expert and offsets[E+1] (int64). Ids outside [0, E) are counted in *bad_count (device int32, may

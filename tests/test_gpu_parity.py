@@ -290,11 +290,11 @@ def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo, fmt):
 def test_grouped_decode_sixteen_warp_ctas(kb, N, K, terms_k):
     """Five or more rows per expert with at least one 256-row item per SM: the decode GEMV runs as one CTA of 16
     consumer warps per SM (8 or 16 staged rows per pass). Ragged row counts around the pass sizes, empty experts, an
-    odd number of 128-row tiles (the last item has one tile only); int8 rows are exact integer group sums."""
+    odd number of 128-row tiles (the last item has one tile only)."""
     E = 160
     rng = np.random.default_rng(N + K)
     terms = make_terms(rng, N, K, 128, "tq2", terms_k, lead=(E,))
-    for top in (8, 16, 21):
+    for top, algo in ((8, "decode"), (16, "decode"), (21, "decode"), (30, "auto")):  # 30 rows: two passes, chosen by AUTO
         counts = rng.integers(max(1, top - 7), top + 1, E)
         counts[[3, 77]] = 0
         counts[5] = top
@@ -302,7 +302,7 @@ def test_grouped_decode_sixteen_warp_ctas(kb, N, K, terms_k):
         x = O.synth_acts(rng, (int(offsets[-1]), K))
         tiled = [kb.tile_weights(torch.from_numpy(p).to(DEV), "tq2", K) for p, _ in terms]
         scales = [torch.from_numpy(s).to(DEV) for _, s in terms]
-        y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, tiled, scales, K, 128, "tq2", algo="decode")
+        y = kb.grouped_ternary_gemm_bf16(bf16_tensor(x, DEV), offsets, tiled, scales, K, 128, "tq2", algo=algo)
         torch.cuda.synchronize()
         assert kb.ext().dst_check_device_status(None) == 0
         y = y.cpu().numpy()
