@@ -292,7 +292,7 @@ def gemm_microbench(device, peaks, which="all", sampler=None, only=None) -> dict
     from deepseekternarized_b200.ternary.ops import quant_act_int8
     from deepseekternarized_b200.ternary.pack import pack, packed_cols
 
-    out = {"decode": [], "prefill": []}
+    out = {"decode": [], "prefill": [], "table_lookup": []}
     g = torch.Generator(device=device).manual_seed(SEED + 99)
 
     def clocks(t):
@@ -334,6 +334,32 @@ def gemm_microbench(device, peaks, which="all", sampler=None, only=None) -> dict
                 line["device_copy"] = "tq2"
             out["decode"].append(line)
         del p, s
+    # Ternary lookup-table rows (the engram tables: 256-wide rows, group 128, TQ1, one or two stacked terms; a step of
+    # 16 384 tokens looks up 24 rows per token). Table and output are larger than L2; GB/s counts packed row + scales + id
+    # + the bf16 row written, per looked-up row.
+    if which in ("all", "tables") and only is None:
+        from deepseekternarized_b200.ternary.ops import LookupTable, PackedTerm, gather_dequant_rows
+
+        V, K, n_ids = 4 * 1024 * 1024, 256, 24 * TOKENS
+        ids = torch.randint(0, V, (n_ids,), generator=g, device=device)
+        for fmt, k_terms in (("tq1", 2), ("tq1", 1), ("tq2", 1)):
+            Kp = packed_cols(fmt, K)
+            hi = 243 if fmt == "tq1" else 256
+            terms = []
+            for i in range(k_terms):
+                pk = torch.randint(0, hi, (V, Kp), generator=g, device=device, dtype=torch.uint8)
+                if fmt == "tq2":  # no 2-bit field holds the value 3
+                    pk = pk & ~((pk >> 1) & pk & 0x55 | (((pk >> 1) & pk & 0x55) << 1))
+                terms.append(PackedTerm(pk, torch.exp(torch.randn(V, K // GROUP, generator=g, device=device) * 0.3 - 4.0).half()))
+            byts = n_ids * (k_terms * (Kp + (K // GROUP) * 2) + 8 + K * 2)
+            table = LookupTable(terms, K, fmt, GROUP)
+            for layout, fn in (("canonical arrays", lambda: gather_dequant_rows(terms, ids, K, fmt, GROUP, check=False)),
+                               (f"one {table.record}-byte record per row", lambda: table.rows(ids, check=False))):
+                t = time_cuda(fn, 20)
+                gbs = byts / t["ms"] / 1e6
+                out["table_lookup"].append({"fmt": fmt, "terms": k_terms, "layout": layout, "table_rows": V, "K": K, "rows_looked_up": n_ids,
+                                            "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "clocks": clocks(t), **t})
+            del terms, table
     # config 2: 4096 tokens, 384 experts, top-6 -> 24576 rows; gate+up (N 4096, K 4096) and down (N 4096, K 2048);
     # then the same shapes with two stacked TQ2 terms (config 3 prefill) and with int8 activations (the policy default)
     E, rows = N_EXPERTS, 4096 * TOP_K
@@ -479,7 +505,7 @@ def main():
     ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel decode/prefill numbers")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true", help="skip the parity check of the last timed step's output")
-    ap.add_argument("--micro-only", default=None, choices=["decode", "prefill", "all"],
+    ap.add_argument("--micro-only", default=None, choices=["decode", "prefill", "tables", "all"],
                     help="run only the single-kernel numbers (decode GEMV sweep and/or prefill grouped GEMM) and print them: "
                     "for profiler captures of those kernels; not a bench line")
     ap.add_argument("--micro-case", default=None, help="with --micro-only decode: run one decode case, named fmt:N:K:terms:tiles|copy "

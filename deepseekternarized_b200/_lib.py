@@ -133,6 +133,9 @@ _SIGNATURES = {
     "dst_gather_dequant_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "dst_gather_dequant_rows_strided": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "dst_check_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "dst_debug_prefill_timeout": (ctypes.c_int, [ctypes.c_longlong, ctypes.c_int, ctypes.c_int]),
 }

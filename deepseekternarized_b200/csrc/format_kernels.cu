@@ -89,9 +89,12 @@ int grid_for(int64_t total, int block) {
 // Ternary lookup table rows: out[i, :] = bf16( sum over terms of trit * scale ), fp32 products added in term order
 // (boilerplate/engine/model.py:458-464: unpack(packed[ids]) * scale[ids].repeat_interleave(group), summed, -> bf16).
 // One block per looked-up row; an id outside [0, V) is counted and its row written as zeros.
+// Row r of term t starts at packed[t] + r * pstride bytes and its scales at element r * sstride of scale[t] (canonical
+// arrays: Kp and G; one record per row holding all terms: the record's size in bytes and in scale elements).
 template <int FMT>
 __global__ void gather_dequant_kernel(Terms terms, int scale_dtype, const int64_t* __restrict__ ids, int64_t V, int64_t K, int64_t Kp,
-                                      int64_t G, int64_t group, __nv_bfloat16* __restrict__ out, int32_t* __restrict__ bad_count) {
+                                      int64_t pstride, int64_t sstride, int64_t group, __nv_bfloat16* __restrict__ out,
+                                      int32_t* __restrict__ bad_count) {
   constexpr int PER = FMT == 2 ? 4 : 5;
   const int64_t i = blockIdx.x;
   const int64_t row = ids[i];
@@ -106,13 +109,13 @@ __global__ void gather_dequant_kernel(Terms terms, int scale_dtype, const int64_
 #pragma unroll
     for (int j = 0; j < PER; ++j) acc[j] = 0.f;
     for (int t = 0; t < terms.n; ++t) {
-      const uint32_t v = terms.packed[t][row * Kp + b];
+      const uint32_t v = terms.packed[t][row * pstride + b];
       const uint32_t f = FMT == 2 ? v : tq1_fields(v);
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int64_t k = b * PER + j;
         if (k < K) {
-          const float val = (float)((int)((f >> (2 * j)) & 3u) - 1) * scale_to_float(terms.scale[t], row * G + k / group, scale_dtype);
+          const float val = (float)((int)((f >> (2 * j)) & 3u) - 1) * scale_to_float(terms.scale[t], row * sstride + k / group, scale_dtype);
           acc[j] = t == 0 ? val : acc[j] + val;
         }
       }
@@ -122,6 +125,107 @@ __global__ void gather_dequant_kernel(Terms terms, int scale_dtype, const int64_
       const int64_t k = b * PER + j;
       if (k < K) o[k] = __float2bfloat16_rn(acc[j]);
     }
+  }
+}
+
+// The same lookup for K % 8 == 0 and group % 8 == 0 (the engram tables: K = 256, group 128): one thread per eight
+// adjacent outputs = one 16-byte store, a warp per 256-wide row. TQ2: the eight trits are one aligned 16-bit load.
+// TQ1: they lie in two or three bytes; the bytes' digit fields (a 256-entry table in shared memory) laid side by side
+// are 15 two-bit digits in one word, shifted down to the first wanted trit. A thread takes ROWS looked-up rows at a
+// time and issues all their loads (ids, then packed bytes and scales of every term) before it uses any: the lookup is
+// a chain of dependent random reads, and only many of them in flight fill the memory system.
+template <int FMT, int ROWS, int TERMS>
+__global__ void __launch_bounds__(256)
+gather_dequant8_kernel(Terms terms, int scale_dtype, const int64_t* __restrict__ ids, int64_t n_ids, int64_t V, int K, int Kp,
+                       int64_t pstride, int64_t sstride, int group, __nv_bfloat16* __restrict__ out, int32_t* __restrict__ bad_count) {
+  __shared__ uint16_t lut[256];
+  if (FMT == 1) {
+    for (int v = threadIdx.x; v < 256; v += blockDim.x) lut[v] = (uint16_t)tq1_fields((uint32_t)v);
+    __syncthreads();
+  }
+  const int per_row = K >> 3;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t i0 = (tid / per_row) * ROWS;  // this thread's first looked-up row; the block of ROWS rows is its warp's (K = 256)
+  if (i0 >= n_ids) return;
+  const int c = (int)(tid % per_row), k = c << 3;
+  const int b0 = k / 5, r = k - 5 * b0, g = k / group;
+  int64_t row[ROWS];
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) row[j] = i0 + j < n_ids ? ids[i0 + j] : -1;
+  uint32_t raw[ROWS][TERMS];  // TQ2: the 16 bits; TQ1: three bytes
+  float sc[ROWS][TERMS];
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) {
+    const bool ok = row[j] >= 0 && row[j] < V;
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+      raw[j][t] = 0u;
+      sc[j][t] = 0.f;
+      if (ok) {
+        const uint8_t* pr = terms.packed[t] + row[j] * pstride;
+        if (FMT == 2) {
+          raw[j][t] = *reinterpret_cast<const uint16_t*>(pr + (k >> 2));
+        } else {
+          uint32_t w = pr[b0];
+          if (b0 + 1 < Kp) w |= (uint32_t)pr[b0 + 1] << 8;
+          if (r > 2 && b0 + 2 < Kp) w |= (uint32_t)pr[b0 + 2] << 16;  // trits 5 b0 + 10 ... are wanted from r = 3 on
+          raw[j][t] = w;  // a byte not read holds trits beyond the eight wanted ones (K % 8 == 0 keeps those inside the row)
+        }
+        sc[j][t] = scale_to_float(terms.scale[t], row[j] * sstride + g, scale_dtype);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < ROWS; ++j) {
+    if (i0 + j >= n_ids) break;
+    uint4* o = reinterpret_cast<uint4*>(out + (i0 + j) * K + k);
+    if (row[j] < 0 || row[j] >= V) {
+      if (c == 0 && bad_count) atomicAdd(bad_count, 1);
+      *o = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    float acc[8];
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+      uint32_t f;  // eight 2-bit digits u = trit + 1
+      if (FMT == 2) {
+        f = raw[j][t];
+      } else {
+        const uint32_t w = raw[j][t];
+        f = ((uint32_t)lut[w & 0xff] | ((uint32_t)lut[(w >> 8) & 0xff] << 10) | ((uint32_t)lut[(w >> 16) & 0xff] << 20)) >> (2 * r);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float val = (float)((int)((f >> (2 * q)) & 3u) - 1) * sc[j][t];
+        acc[q] = t == 0 ? val : acc[q] + val;
+      }
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      w[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *o = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+template <int FMT, int TERMS>
+void launch_gather8(const Terms& terms, int scale_dtype, const int64_t* ids, int64_t n_ids, int64_t V, int K, int Kp, int64_t pstride,
+                    int64_t sstride, int group, __nv_bfloat16* out, int32_t* bad_count, cudaStream_t st) {
+  constexpr int ROWS = 4;
+  const int64_t threads = ((n_ids + ROWS - 1) / ROWS) * (K / 8);
+  gather_dequant8_kernel<FMT, ROWS, TERMS><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(terms, scale_dtype, ids, n_ids, V, K, Kp, pstride,
+                                                                                           sstride, group, out, bad_count);
+}
+template <int FMT>
+void launch_gather8(const Terms& terms, int scale_dtype, const int64_t* ids, int64_t n_ids, int64_t V, int K, int Kp, int64_t pstride,
+                    int64_t sstride, int group, __nv_bfloat16* out, int32_t* bad_count, cudaStream_t st) {
+  switch (terms.n) {
+    case 1: return launch_gather8<FMT, 1>(terms, scale_dtype, ids, n_ids, V, K, Kp, pstride, sstride, group, out, bad_count, st);
+    case 2: return launch_gather8<FMT, 2>(terms, scale_dtype, ids, n_ids, V, K, Kp, pstride, sstride, group, out, bad_count, st);
+    case 3: return launch_gather8<FMT, 3>(terms, scale_dtype, ids, n_ids, V, K, Kp, pstride, sstride, group, out, bad_count, st);
+    default: return launch_gather8<FMT, 4>(terms, scale_dtype, ids, n_ids, V, K, Kp, pstride, sstride, group, out, bad_count, st);
   }
 }
 
@@ -193,26 +297,49 @@ extern "C" int dst_quant_act_int8_f16(const void* x, int x_is_f32, int64_t M, in
   return DST_OK;
 }
 
-extern "C" int dst_gather_dequant_rows(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
-                                       const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt, void* out_bf16,
-                                       int32_t* bad_count, dst_stream_t stream) {
+extern "C" int dst_gather_dequant_rows_strided(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
+                                               const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt,
+                                               int64_t packed_row_stride, int64_t scale_row_stride, void* out_bf16, int32_t* bad_count,
+                                               dst_stream_t stream) {
   if ((fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2) || K <= 0 || group <= 0 || V < 0 || n_ids < 0) return DST_ERR_BAD_ARG;
   if (n_terms < 1 || n_terms > DST_MAX_TERMS || scale_dtype < DST_SCALE_F16 || scale_dtype > DST_SCALE_BF16) return DST_ERR_BAD_ARG;
+  const int64_t Kp = dst_packed_cols(fmt, K), G = (K + group - 1) / group;
+  if (packed_row_stride < Kp || scale_row_stride < G) return DST_ERR_BAD_ARG;
   if (n_ids == 0) return DST_OK;
   if (!packed || !scales || !ids || !out_bf16) return DST_ERR_BAD_ARG;
   if (n_ids > 0x7fffffff || K > (int64_t(1) << 24)) return DST_ERR_BAD_SHAPE;
   dst::Terms terms;
   terms.n = n_terms;
+  bool even = packed_row_stride % 2 == 0;  // TQ2 rows are read 16 bits at a time
   for (int i = 0; i < n_terms; ++i) {
     if (!packed[i] || !scales[i]) return DST_ERR_BAD_ARG;
     terms.packed[i] = static_cast<const uint8_t*>(packed[i]);
     terms.scale[i] = scales[i];
+    even = even && (reinterpret_cast<uintptr_t>(packed[i]) & 1) == 0;
   }
-  const int64_t Kp = dst_packed_cols(fmt, K), G = (K + group - 1) / group;
   auto st = static_cast<cudaStream_t>(stream);
   auto o = static_cast<__nv_bfloat16*>(out_bf16);
-  if (fmt == DST_FMT_TQ2) dst::gather_dequant_kernel<2><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, G, group, o, bad_count);
-  else dst::gather_dequant_kernel<1><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, G, group, o, bad_count);
+  // rows of whole 8-trit pieces that share a scale, output 16-byte aligned: one 16-byte store per thread
+  const bool by8 = K % 8 == 0 && group % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0 && (fmt == DST_FMT_TQ1 || even) &&
+                   n_ids * (K / 8) / 256 < 0x7fffffff;
+  if (by8) {
+    if (fmt == DST_FMT_TQ2)
+      dst::launch_gather8<2>(terms, scale_dtype, ids, n_ids, V, (int)K, (int)Kp, packed_row_stride, scale_row_stride, (int)group, o, bad_count, st);
+    else
+      dst::launch_gather8<1>(terms, scale_dtype, ids, n_ids, V, (int)K, (int)Kp, packed_row_stride, scale_row_stride, (int)group, o, bad_count, st);
+  } else if (fmt == DST_FMT_TQ2) {
+    dst::gather_dequant_kernel<2><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, packed_row_stride, scale_row_stride, group, o, bad_count);
+  } else {
+    dst::gather_dequant_kernel<1><<<(unsigned)n_ids, 128, 0, st>>>(terms, scale_dtype, ids, V, K, Kp, packed_row_stride, scale_row_stride, group, o, bad_count);
+  }
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
+}
+
+extern "C" int dst_gather_dequant_rows(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
+                                       const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt, void* out_bf16,
+                                       int32_t* bad_count, dst_stream_t stream) {
+  if ((fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2) || K <= 0 || group <= 0) return DST_ERR_BAD_ARG;
+  return dst_gather_dequant_rows_strided(packed, scales, n_terms, scale_dtype, ids, n_ids, V, K, group, fmt, dst_packed_cols(fmt, K),
+                                         (K + group - 1) / group, out_bf16, bad_count, stream);
 }

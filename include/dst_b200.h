@@ -269,6 +269,17 @@ int dst_combine_weighted(const void* down_bf16, const int64_t* order, const int3
 int dst_gather_dequant_rows(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
                             const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt, void* out_bf16,
                             int32_t* bad_count, dst_stream_t stream);
+/*
+ * The same lookup over rows that are not densely stored: row r of term t starts at packed[t] + r * packed_row_stride
+ * bytes and its scales at element r * scale_row_stride of scales[t]. With one record per table row that holds the
+ * packed bytes of every term followed by their scales (both strides = the record's size, in bytes and in scale
+ * elements), a looked-up row is ONE stretch of DRAM instead of two per term (measured on 256-wide rows: 1.2x faster
+ * for two stacked TQ1 terms, no gain for one term).
+ */
+int dst_gather_dequant_rows_strided(const void* const* packed, const void* const* scales, int n_terms, int scale_dtype,
+                                    const int64_t* ids, int64_t n_ids, int64_t V, int64_t K, int64_t group, int fmt,
+                                    int64_t packed_row_stride, int64_t scale_row_stride, void* out_bf16, int32_t* bad_count,
+                                    dst_stream_t stream);
 
 /*
  * Expert-parallel dispatch and combine over peer memory (the reference has no expert-parallel exchange of routed

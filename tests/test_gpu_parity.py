@@ -500,7 +500,7 @@ def test_sort_large_and_bad_ids(kb):
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])
 def test_table_row_lookup_against_reference_golden(golden, fmt):
     """Ternary lookup-table rows (boilerplate/engine/model.py:458-464) on the GPU: bit-exact with the reference."""
-    from deepseekternarized_b200.ternary.ops import PackedTerm, gather_dequant_rows
+    from deepseekternarized_b200.ternary.ops import LookupTable, PackedTerm, gather_dequant_rows
 
     g = golden("table_rows")
     V, K, group, k_terms = (int(v) for v in g[f"{fmt}_meta"])
@@ -511,14 +511,23 @@ def test_table_row_lookup_against_reference_golden(golden, fmt):
     assert np.array_equal(O.bf16_bits(bf16_numpy(vals)).reshape(-1, K), g[f"{fmt}_vals_bits"])
     with pytest.raises(IndexError):
         gather_dequant_rows(terms, torch.tensor([0, V], device=DEV), K, fmt, group)
-    # a larger table against the oracle
+    # larger tables against the oracle: a long row, the engram tables' row (head_dim 256, group 128, two stacked terms:
+    # boilerplate/configs/policy/experts_engram_k2.yaml), a row whose last TQ1 byte is partly padding, and a row
+    # width the 8-trit kernel does not take
     rng = np.random.default_rng(9)
-    V2, K2 = 3000, 1024
-    big = make_terms(rng, V2, K2, 128, fmt, 2)
-    ids2 = rng.integers(0, V2, 4096)
-    got = gather_dequant_rows([PackedTerm(torch.from_numpy(p).to(DEV), torch.from_numpy(s).to(DEV)) for p, s in big],
-                              torch.from_numpy(ids2).to(DEV), K2, fmt, 128)
-    assert np.array_equal(bf16_numpy(got), O.gather_dequant_rows(ids2, big, K2, 128, fmt))
+    for V2, K2, group2, k2 in ((3000, 1024, 128, 2), (5000, 256, 128, 2), (700, 136, 8, 1), (700, 100, 128, 3)):
+        big = make_terms(rng, V2, K2, group2, fmt, k2)
+        ids2 = rng.integers(0, V2, 4096)
+        ids2[:2] = (0, V2 - 1)
+        got = gather_dequant_rows([PackedTerm(torch.from_numpy(p).to(DEV), torch.from_numpy(s).to(DEV)) for p, s in big],
+                                  torch.from_numpy(ids2).to(DEV), K2, fmt, group2)
+        assert np.array_equal(bf16_numpy(got), O.gather_dequant_rows(ids2, big, K2, group2, fmt))
+        # the same table as one record per row
+        table = LookupTable([PackedTerm(torch.from_numpy(p).to(DEV), torch.from_numpy(s).to(DEV)) for p, s in big], K2, fmt, group2)
+        assert table.record % 16 == 0 and torch.equal(table.rows(torch.from_numpy(ids2).to(DEV)), got)
+        with pytest.raises(IndexError):
+            table.rows(torch.tensor([-1], device=DEV))
+        assert not table.rows(torch.tensor([V2], device=DEV), check=False).any()
 
 
 def test_expert_parallel_peer_transport_single_rank():
