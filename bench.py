@@ -280,8 +280,8 @@ def time_cuda(fn, iters: int, warmup: int = 3, repeats: int = 3, min_loop_ms: fl
 
 
 def gemm_microbench(device, peaks, which="all", sampler=None, only=None) -> dict:
-    """Single-kernel numbers at N = 1: decode GEMV (BASELINE configs 0, 1 and 3) and prefill grouped GEMM (configs 2
-    and 3, and the int8-activation mode on the config-2 shape).
+    """Single-kernel numbers at N = 1: decode GEMV (BASELINE configs 0, 1 and 3), prefill grouped GEMM (configs 2
+    and 3, and the int8-activation mode on the config-2 shape) and the ternary lookup-table rows.
 
     Decode: one launch is a grouped GEMV over `copies` distinct weight sets of the same shape (each with its own M
     rows), so one launch streams > L2 of packed bytes from HBM. GB/s counts the CANONICAL packed bytes of the format
@@ -313,7 +313,7 @@ def gemm_microbench(device, peaks, which="all", sampler=None, only=None) -> dict
     # (format, N, K, Ms, stacked terms, read TQ1 through a tiled TQ2 copy of its trits)
     decode_cases = (("tq2", 4096, 4096, (1, 16), 1, False),
                     ("tq1", 2048, 4096, (1, 8), 1, False), ("tq1", 4096, 4096, (1, 4, 8, 32), 1, False), ("tq1", 11008, 4096, (1, 8), 1, False),
-                    ("tq1", 2048, 4096, (1, 8), 1, True), ("tq1", 4096, 4096, (1, 4, 8), 1, True), ("tq1", 11008, 4096, (1, 8), 1, True),
+                    ("tq1", 2048, 4096, (1, 8), 1, True), ("tq1", 4096, 4096, (1, 4, 8, 32), 1, True), ("tq1", 11008, 4096, (1, 8), 1, True),
                     ("tq2", 2048, 4096, (1, 8, 64), 2, False), ("tq2", 4096, 2048, (1, 8, 64), 2, False))  # config 3: k = 2
     for fmt, N, K, Ms, k_terms, copy in (decode_cases if which in ("all", "decode") else ()):
         if only is not None and f"{fmt}:{N}:{K}:{k_terms}:{'copy' if copy else 'tiles'}" != only:

@@ -614,7 +614,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     uint32_t s = grp % NB, ph = (grp / NB) & 1u;
     uint32_t it0 = 0, gs0 = 0;  // first stage / first slab of the current tile
     bool ok = true;
-    RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, w_st = 0, w_pre = 0, n_it = 0, t_begin = RT_NOW());
+    RT_DECL(w_pfull = 0, w_dempty = 0, w_drain = 0, w_comp = 0, w_st = 0, w_pre = 0, n_it = 0, t_begin = RT_NOW(), w_lds = 0, w_tail = 0, t_tail = RT_NOW());
 
     // scales of the row: 8 groups (16 stages) per 128-bit load; when a block of 8 is taken into use the tile's next block
     // is requested, so only a tile's first block is waited for (once per tile and warp; the per-stage cost is a compare)
@@ -662,6 +662,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
       }
       const int ks = (int)(own - it0);
         RT_DECL(t_pre = RT_NOW());
+        RT_SPAN(w_tail, t_tail);
         const int sb = ks / SPB, sbk = ks - sb * SPB;
         const uint32_t gs = gs0 + (uint32_t)sb;
         const uint32_t slot = p.nslab == 2 ? (gs & 1u) : gs % 3u, sround = p.nslab == 2 ? (gs >> 1) : gs / 3u;
@@ -685,6 +686,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         // packed words of this row for this stage, then the slab can go back to the producer
         RT_SPAN(w_pre, t_pre);
         if (!RT_WAIT(w_pfull, mbar_wait(smem_u32(&bar_pfull[slot]), sround & 1u, abort_flag))) { ok = false; break; }
+        RT_DECL(t_lds = RT_NOW());
         uint32_t w[TERMS][4];
 #pragma unroll
         for (int i = 0; i < TERMS; ++i) {
@@ -705,6 +707,13 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
             for (int x = nsb * SPB - kstages; x > 0; --x) mbar_arrive(smem_u32(&bar_pempty[slot]));
         }
 
+#ifdef DST_ROLE_TIMERS
+#pragma unroll
+        for (int i = 0; i < TERMS; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) asm volatile("" : "+r"(w[i][j]));
+#endif
+        RT_SPAN(w_lds, t_lds);
         RT_DECL(t_c = RT_NOW());
         __half2 acc[32];
 #pragma unroll
@@ -749,13 +758,16 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
         RT_SPAN(w_st, t_st);
+#ifdef DST_ROLE_TIMERS
+        t_tail = RT_NOW();
+#endif
         own += n_groups;
         s += n_groups;
         while (s >= NB) { s -= NB; ph ^= 1u; }
     }
     if (warp == PF_DQ_WARP0 && lane == 0) {
       RT_ADD(24, RT_NOW() - t_begin); RT_ADD(25, w_pfull); RT_ADD(26, w_dempty); RT_ADD(27, n_it); RT_ADD(28, 1);
-      RT_ADD(29, w_drain); RT_ADD(30, w_comp); RT_ADD(31, w_st); RT_ADD(32, w_pre);
+      RT_ADD(29, w_drain); RT_ADD(30, w_comp); RT_ADD(31, w_st); RT_ADD(32, w_pre); RT_ADD(33, w_lds); RT_ADD(34, w_tail);
     }
   }
 
@@ -972,7 +984,8 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
 // total cycles, slab producer wait slot free, B producer wait stage free, stages, threads, slab producer total),
 // 8-13 MMA issuer (total, wait accumulator free, wait stage full, stages, threads, tiles), 24-30 one dequant warp
 // (total, wait packed slab, wait stage free, own stages, threads, accumulator drain, dequant arithmetic, TMEM store +
-// arrive, scale bookkeeping before the slab wait).
+// arrive, scale bookkeeping before the slab wait), 33 its reads of the packed words + slab hand-back, 34 loop tail and
+// head (tile lookup included). The clock reads themselves cost: a build with them runs ~20 % slower.
 extern "C" int dst_role_timers(unsigned long long* out, int reset) {
   DST_CUDA_TRY(cudaDeviceSynchronize());
   DST_CUDA_TRY(cudaMemcpyFromSymbol(out, dst::g_role_timers, sizeof(unsigned long long) * 64));
