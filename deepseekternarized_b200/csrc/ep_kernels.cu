@@ -149,44 +149,51 @@ ep_combine_kernel(PeerPtrs down, const int64_t* __restrict__ inv, const int32_t*
                   __nv_bfloat16* __restrict__ y) {
   const int64_t t = blockIdx.x;
   __shared__ const __nv_bfloat16* src[8];
-  if (threadIdx.x == 0) {  // one thread sorts: arrays indexed at run time live in local memory
-    const __nv_bfloat16* sp[8];
-    int eid[8];
-    for (int s = 0; s < top_k; ++s) {
+  if (threadIdx.x < 32) {
+    // lane s looks up slot s (the slots' chains of dependent loads run side by side), then the slots are ranked by
+    // expert id with shuffles (ids of one token are distinct; equal keys, which only slots without a row can have,
+    // keep their order)
+    const int s = threadIdx.x;
+    int eid = 0x7fffffff;
+    const __nv_bfloat16* sp = nullptr;
+    if (s < top_k) {
       const int g = ids[t * top_k + s];
       const int64_t p = inv[t * top_k + s];
-      eid[s] = g;
-      const bool ok = g >= 0 && g < E && p >= 0;
-      sp[s] = ok ? static_cast<const __nv_bfloat16*>(peer_ptr(down, g / El)) + (dst_start[g] + (p - offsets[g])) * hidden : nullptr;
+      eid = g;
+      if (g >= 0 && g < E && p >= 0)
+        sp = static_cast<const __nv_bfloat16*>(peer_ptr(down, g / El)) + (dst_start[g] + (p - offsets[g])) * hidden;
     }
-    for (int i = 1; i < top_k; ++i) {  // insertion sort by expert id (ids of one token are distinct)
-      const int e = eid[i];
-      const __nv_bfloat16* q = sp[i];
-      int j = i - 1;
-      while (j >= 0 && eid[j] > e) {
-        eid[j + 1] = eid[j];
-        sp[j + 1] = sp[j];
-        --j;
-      }
-      eid[j + 1] = e;
-      sp[j + 1] = q;
+    int rank = 0;
+    for (int j = 0; j < top_k; ++j) {
+      const int ej = __shfl_sync(0xffffffffu, eid, j);
+      rank += (ej < eid || (ej == eid && j < s)) ? 1 : 0;
     }
-    for (int s = 0; s < top_k; ++s) src[s] = sp[s];
+    if (s < top_k) src[rank] = sp;
   }
   __syncthreads();
   const int chunks = (int)(hidden >> 3);
   for (int c = threadIdx.x; c < chunks; c += 256) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < top_k; ++s) {
-      if (src[s] == nullptr) continue;
-      float f[8];
-      bf16x8_to_float(reinterpret_cast<const uint4*>(src[s])[c], f);
+    // all of the token's rows are requested before any is added: one trip over the links per chunk, not one per row
+    // (a slot without a row reads zeros: the sum starts at +0 and so is never -0, and adding +0 to it changes nothing)
+    uint4 raw[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    for (int s = 0; s < 8; ++s)
+      raw[s] = (s < top_k && src[s] != nullptr) ? reinterpret_cast<const uint4*>(src[s])[c] : make_uint4(0u, 0u, 0u, 0u);
+    uint4 radd = make_uint4(0u, 0u, 0u, 0u);
+    if (add) radd = reinterpret_cast<const uint4*>(add + t * hidden)[c];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < top_k) {
+        float f[8];
+        bf16x8_to_float(raw[s], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
     }
     if (add) {
       float f[8];
-      bf16x8_to_float(reinterpret_cast<const uint4*>(add + t * hidden)[c], f);
+      bf16x8_to_float(radd, f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }

@@ -616,17 +616,27 @@ combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __rest
   token_slots(inv, ids, t, top_k, (int64_t)gridDim.x * top_k, pos);
   const int chunks = (int)(hidden >> 3);
   for (int c = threadIdx.x; c < chunks; c += 256) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < top_k; ++s) {
-      if (pos[s] < 0) continue;
-      float f[8];
-      bf16x8_to_float(reinterpret_cast<const uint4*>(down + pos[s] * hidden)[c], f);
+    // all of the token's rows are requested before any is added: one memory latency per chunk, not one per row
+    // (a slot without a row reads zeros: the sum starts at +0 and so is never -0, and adding +0 to it changes nothing)
+    uint4 raw[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    for (int s = 0; s < 8; ++s)
+      raw[s] = (s < top_k && pos[s] >= 0) ? reinterpret_cast<const uint4*>(down + pos[s] * hidden)[c] : make_uint4(0u, 0u, 0u, 0u);
+    uint4 radd = make_uint4(0u, 0u, 0u, 0u);
+    if (add) radd = reinterpret_cast<const uint4*>(add + t * hidden)[c];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < top_k) {
+        float f[8];
+        bf16x8_to_float(raw[s], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
     }
     if (add) {
       float f[8];
-      bf16x8_to_float(reinterpret_cast<const uint4*>(add + t * hidden)[c], f);
+      bf16x8_to_float(radd, f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
