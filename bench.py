@@ -499,6 +499,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ep-combine", default="auto", choices=["auto", "scatter", "pull"],
+                    help="N > 1: how the experts' outputs return to their tokens' ranks (ExpertParallelMoE's combine)")
     ap.add_argument("--repeats", type=int, default=7, help="timed regions of --steps steps each; the median region is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--algo", default="auto")
@@ -548,7 +550,7 @@ def main():
     t_local = TOKENS // world
     weights = synth_expert_weights(n_local, rank * n_local, device)
     ops = timed_ops(args.algo)
-    layer = ExpertParallelMoE(weights, N_EXPERTS, TOP_K, ops=ops) if world > 1 else MoELayer(weights, TOP_K, ops=ops)
+    layer = ExpertParallelMoE(weights, N_EXPERTS, TOP_K, ops=ops, combine=args.ep_combine) if world > 1 else MoELayer(weights, TOP_K, ops=ops)
     x_host, logits_host = synth_tokens(t_local, rank * t_local)
     x_dev, logits_dev = x_host.to(device), logits_host.to(device)
     y_host = torch.empty(t_local, HIDDEN, dtype=torch.bfloat16).pin_memory()

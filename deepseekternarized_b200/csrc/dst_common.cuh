@@ -46,6 +46,10 @@ struct GemmArgs {
   int weight_layout;  // DST_LAYOUT_CANONICAL or DST_LAYOUT_TILED (terms.packed then points at tiled buffers)
   void* workspace;    // caller-provided scratch (may be null when the kernel needs none)
   size_t workspace_bytes;
+  // optional scatter of the output rows (tcgen05 kernel only): row r goes to row (row_target[r] & (2^48 - 1)) of
+  // peer_out[row_target[r] >> 48] (a negative target: the row is not stored); `out` is unused then
+  const int64_t* row_target;
+  void* peer_out[DST_MAX_PEERS];
 };
 
 int64_t tiled_superblocks(int fmt, int64_t K);

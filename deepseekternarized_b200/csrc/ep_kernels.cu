@@ -73,7 +73,7 @@ template <int J>  // 16-byte chunks per thread: rows of K <= 2048 J elements
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ order, const int64_t* __restrict__ dest,
                const float* __restrict__ route_weights, const int64_t* __restrict__ first_row, int top_k, int64_t K, PeerPtrs rows,
-               PeerPtrs fac, PeerPtrs wts) {
+               PeerPtrs fac, PeerPtrs wts, PeerPtrs back, int rank) {
   __shared__ float red[32];
   // Blocks walk the sorted rows starting at *first_row (the rows of the rank after this one) and wrap around: the
   // rows are sorted by destination rank, and with every rank starting at rank 0's rows all of them would store into
@@ -129,6 +129,8 @@ ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ 
   if (threadIdx.x == 0) {
     static_cast<float*>(peer_ptr(fac, d))[dr] = ldexpf(1.f, ex);
     static_cast<float*>(peer_ptr(wts, d))[dr] = route_weights[slot];
+    // where the expert's output row for this routed row is to be sent back: (this rank, its slot token * top_k + choice)
+    if (back.p[0] != nullptr) static_cast<int64_t*>(peer_ptr(back, d))[dr] = ((int64_t)rank << 48) | slot;
   }
 }
 
@@ -307,7 +309,7 @@ extern "C" int dst_ep_placement(const int64_t* offsets_all, int world, int64_t E
 extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
                                 const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
                                 const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
-                                int world, int rank, int64_t* row_dest, dst_stream_t stream) {
+                                const void* const* peer_row_origin, int world, int rank, int64_t* row_dest, dst_stream_t stream) {
   if (n_rows < 0 || E <= 0 || experts_per_rank <= 0 || top_k <= 0 || K <= 0 || world < 1 || world > DST_MAX_PEERS || rank < 0 || rank >= world)
     return DST_ERR_BAD_ARG;
   if (E > DST_MAX_EXPERTS || experts_per_rank * world < E) return DST_ERR_BAD_SHAPE;
@@ -317,9 +319,11 @@ extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const 
     return DST_ERR_BAD_ARG;
   if (n_rows > 0x7fffffff) return DST_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) != 0) return DST_ERR_ALIGNMENT;
-  PeerPtrs rows, fac, wts;
+  PeerPtrs rows, fac, wts, back;
   if (!fill_peers(rows, peer_rows_f16, world) || !fill_peers(fac, peer_row_factor, world) || !fill_peers(wts, peer_row_weight, world))
     return DST_ERR_ALIGNMENT;
+  for (int i = 0; i < DST_MAX_PEERS; ++i) back.p[i] = nullptr;
+  if (peer_row_origin != nullptr && !fill_peers(back, peer_row_origin, world)) return DST_ERR_ALIGNMENT;
   auto st = static_cast<cudaStream_t>(stream);
   auto xp = static_cast<const __nv_bfloat16*>(x_bf16);
   ep_row_dest_kernel<<<(unsigned)cdiv64(n_rows, 256), 256, 0, st>>>(offsets, dst_start, n_rows, (int)E, (int)experts_per_rank, row_dest);
@@ -328,11 +332,11 @@ extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const 
   const int64_t next_first = (int64_t)((rank + 1) % world) * experts_per_rank;
   const int64_t* first_row = next_first < E ? offsets + next_first : nullptr;
   if (K <= 2048)
-    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
+    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
   else if (K <= 4096)
-    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
+    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
   else
-    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts);
+    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

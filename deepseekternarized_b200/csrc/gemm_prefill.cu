@@ -65,7 +65,7 @@ constexpr int PF_LUT_BYTES = 256 * 16 * 4;   // TQ1: 256 byte values x 16 bank r
 constexpr int PF_SLAB = 8192;                // one (row tile, superblock) slab of packed weights
 constexpr int PF_MAX_E = 1023;               // experts per launch: two int arrays of E + 1 entries live in shared memory
 constexpr int PF_SMEM_MAX = 232448;          // 227 KB of shared memory per CTA
-constexpr int PF_SMEM_STATIC = 512;          // allowance for the statically declared barriers and flags
+constexpr int PF_SMEM_STATIC = 6144;         // allowance for the statically declared barriers, flags and the scatter form's row pointers
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 __device__ int g_device_status = 0;
@@ -115,7 +115,22 @@ struct PrefillParams {
   int nslab;        // slots of the packed-slab ring, 2 or 3
   int small;        // token tiles of at most 128 rows: four warps drain the accumulator and the other four of that role join
                     // the dequantisation as a fifth group (the MMAs of such tiles are short, the dequantisation is the limit)
+  // Scatter of the output rows (null: rows go to `out` in place). Row r is stored at row (row_target[r] & (2^48 - 1)) of
+  // peer_out[row_target[r] >> 48]: the buffers of the GPUs whose tokens the rows belong to, written from the epilogue
+  // with plain stores over NVLink while the tensor pipe works on the next tile. A negative target drops the row.
+  const int64_t* row_target;
+  void* peer_out[DST_MAX_PEERS];
 };
+
+// Entry d of the by-value pointer table, as a chain of selects over compile-time indices (indexing a parameter array
+// with a run-time value copies the table into every thread's local memory).
+__device__ __forceinline__ void* pf_peer_out(const PrefillParams& p, int d) {
+  void* r = p.peer_out[0];
+#pragma unroll
+  for (int i = 1; i < DST_MAX_PEERS; ++i)
+    if (d == i) r = p.peer_out[i];
+  return r;
+}
 
 // ------------------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -345,7 +360,7 @@ __device__ __forceinline__ __half2 pick_scale(const uint4& sc, int g) {
 // TMEM lane quarter -> registers -> global (thread = output column n, chunk column j = token row j).
 __device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem, int col_first, int col_step, int r, uint32_t tfull_bar,
                                         uint32_t tempty_bar, volatile int* abort_flag, int d_nt, int d_row0, int d_rows,
-                                        uint32_t d_tile) {
+                                        uint32_t d_tile, const uint64_t* __restrict__ row_ptr) {
   const int lane = r & 31;
   const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
   if (!mbar_wait(tfull_bar, d_tile & 1u, abort_flag)) return false;
@@ -374,7 +389,22 @@ __device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem
     }
     const int lim = n_ok ? d_rows - c0 : 0;  // token rows of this chunk that exist (and a column that exists)
     uint8_t* optr = obase + (size_t)c0 * ostep;
-    if (p.out_dtype == DST_OUT_BF16) {
+    if (row_ptr != nullptr) {
+      // scatter form: row_ptr[j] = where token row j of the tile goes (0: nowhere), looked up by this role while it
+      // waited for the accumulator; every thread stores its column of the row there
+      const size_t col = (size_t)(n_ok ? dn : 0) * esz;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
+        if (j < lim) {
+          const uint64_t rowp = row_ptr[c0 + j];
+          if (rowp != 0) {
+            if (p.out_dtype == DST_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(rowp + col) = __float2bfloat16_rn(val);
+            else *reinterpret_cast<__half*>(rowp + col) = __float2half_rn(val);
+          }
+        }
+      }
+    } else if (p.out_dtype == DST_OUT_BF16) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float val = __uint_as_float(v[j]) * __shfl_sync(0xffffffffu, rs_lane, j);
@@ -428,6 +458,8 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
       bar_pempty[PF_MAX_SLABS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ uint64_t bar_epi;                      // scatter form: the epilogue warps' own barrier, once per tile
+  __shared__ uint64_t rowptr_s[2][PF_TN_MAX];       // scatter form: destination of every token row of a tile, two tiles alternating
   volatile int* abort_flag = &abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -439,6 +471,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     }
     mbar_init(smem_u32(&bar_tfull[0]), 2);             // one tcgen05.commit per MMA issuer after the tile's last MMA
     mbar_init(smem_u32(&bar_tempty[0]), p.small ? 4 : PF_EPI_WARPS);  // every epilogue warp has drained its share of the accumulator
+    mbar_init(smem_u32(&bar_epi), p.small ? 4 : PF_EPI_WARPS);
     for (int a = 0; a < PF_MAX_SLABS; ++a) {
       mbar_init(smem_u32(&bar_pfull[a]), 1);         // bulk-copy producer's expect_tx arrive
       mbar_init(smem_u32(&bar_pempty[a]), 4 * SPB);  // one arrive per (stage of the superblock, warp of its group)
@@ -590,11 +623,29 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
     // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
     const int r = (warp & 3) * 32 + lane;  // a warp may only read the TMEM lanes of its own quarter (warp id % 4)
     uint32_t tile = 0;
+    const int epi_threads = 32 * (p.small ? 4 : PF_EPI_WARPS), epi_tid = tid - 32 * PF_CTRL_WARPS;
     for (int t = (int)blockIdx.x; t < n_tiles; t += t_step, ++tile) {
       tile_seek(p, offs, tpre, t, e, nt, row0, rows);
+      const uint64_t* row_ptr = nullptr;
+      if (p.row_target != nullptr) {
+        // scatter form: while the tile is computed, look up where its token rows go (a global load and a pointer
+        // per row, shared by the role's warps through shared memory; the buffer of the tile before stays intact for
+        // warps still draining it, and nobody passes the barrier before all are done with the tile before that)
+        uint64_t* rp = rowptr_s[tile & 1u];
+        const size_t ostep = (size_t)p.N * 2;
+        for (int j = epi_tid; j < rows; j += epi_threads) {
+          const int64_t tg = p.row_target[row0 + j];
+          rp[j] = tg >= 0 ? (uint64_t)reinterpret_cast<uintptr_t>(pf_peer_out(p, (int)(tg >> 48))) + (uint64_t)(tg & 0xFFFFFFFFFFFFLL) * ostep : 0ull;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
+        if (!mbar_wait(smem_u32(&bar_epi), tile & 1u, abort_flag)) break;
+        __syncwarp();
+        row_ptr = rp;
+      }
       // the two warps of a lane quarter take alternate 32-column chunks
       if (!drain_tile(p, tmem, ((warp - PF_CTRL_WARPS) >> 2) * 32, p.small ? 32 : 32 * (PF_EPI_WARPS / 4), r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]),
-                      abort_flag, nt, row0, rows, tile))
+                      abort_flag, nt, row0, rows, tile, row_ptr))
         break;
     }
   } else {
@@ -946,6 +997,9 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.out = a.out;
   p.out_dtype = a.out_dtype;
   p.accumulate = a.accumulate;
+  p.row_target = a.row_target;
+  for (int i = 0; i < DST_MAX_PEERS; ++i) p.peer_out[i] = a.peer_out[i];
+  if (a.row_target != nullptr && (a.out_dtype == DST_OUT_F32 || a.accumulate)) return DST_ERR_UNSUPPORTED;
   p.E = (int)a.E;
   p.T = (int)a.T;
   p.N = (int)a.N;

@@ -607,6 +607,18 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ down, const int
   }
 }
 
+// inv for expert outputs that were sent back to their tokens' slots (the scatter form of the expert-parallel step):
+// slot f = order[p] holds its row at position f itself, unless the routing sort dropped it (dest[p] < 0). inv is
+// preset to -1 by the caller.
+__global__ void returned_slots_kernel(const int64_t* __restrict__ order, const int64_t* __restrict__ dest, int64_t n,
+                                      int64_t* __restrict__ inv) {
+  const int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (p < n) {
+    const int64_t f = order[p];
+    if (f >= 0 && f < n && dest[p] >= 0) inv[f] = f;
+  }
+}
+
 // combine_kernel for hidden % 8 == 0: 128-bit loads and stores.
 __global__ void __launch_bounds__(256)
 combine_vec_kernel(const __nv_bfloat16* __restrict__ down, const int64_t* __restrict__ inv, const int32_t* __restrict__ ids, int top_k,
@@ -902,6 +914,27 @@ extern "C" int dst_combine_add(const void* down_bf16, const int64_t* order, cons
   else
     combine_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(down_bf16), inv, ids, top_k, hidden, add,
                                                static_cast<__nv_bfloat16*>(y_bf16));
+  DST_CUDA_TRY(cudaGetLastError());
+  return DST_OK;
+}
+
+extern "C" int dst_ep_combine_returned(const void* rows_bf16, const int64_t* order, const int64_t* row_dest, const int32_t* ids, int64_t T,
+                                       int top_k, int64_t hidden, int64_t* inv, const void* add_bf16, void* y_bf16, dst_stream_t stream) {
+  if (T < 0 || top_k <= 0 || top_k > 8 || hidden <= 0) return DST_ERR_BAD_ARG;
+  if (hidden % 8 != 0) return DST_ERR_UNSUPPORTED;
+  if (T == 0) return DST_OK;
+  if (!rows_bf16 || !order || !row_dest || !ids || !inv || !y_bf16) return DST_ERR_BAD_ARG;
+  if (T > 0x7fffffff / top_k) return DST_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(rows_bf16) & 15) != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(add_bf16) & 15) != 0)
+    return DST_ERR_ALIGNMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t n = T * top_k;
+  DST_CUDA_TRY(cudaMemsetAsync(inv, 0xff, (size_t)n * sizeof(int64_t), st));  // -1: no row
+  returned_slots_kernel<<<(unsigned)cdiv64(n, 256), 256, 0, st>>>(order, row_dest, n, inv);
+  DST_CUDA_TRY(cudaGetLastError());
+  combine_vec_kernel<<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows_bf16), inv, ids, top_k, hidden,
+                                                 static_cast<const __nv_bfloat16*>(add_bf16), static_cast<__nv_bfloat16*>(y_bf16));
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

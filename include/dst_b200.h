@@ -294,9 +294,29 @@ int dst_gather_dequant_rows_strided(const void* const* packed, const void* const
  * int64 [n_rows] scratch the call fills (each row's owner and row there, found once by a small kernel of its own);
  * `rank` is this rank's index: it starts with the rows of the rank after it, so the ranks do not all store into the
  * same GPU at the same time.
+ * peer_row_origin (may be NULL): per rank an int64 [cap] array; the push also records there, beside every row it
+ * delivers, (rank << 48) | slot, slot = order[p] = token * top_k + choice: the row_target of the scatter GEMM below.
  * dst_ep_combine_pull: y[t] = bf16( sum over the token's slots, in increasing expert id, of the owner's output row ).
  * Neither waits on another GPU; the caller orders the steps (a stream-ordered collective between them).
+ *
+ * The fused form of the way back (GEMM + combine transfer in one kernel): dst_ternary_grouped_gemm_scatter is the
+ * tcgen05 grouped GEMM whose epilogue stores output row r at row (row_target[r] & (2^48 - 1)) of the two-byte-typed
+ * buffer peer_out[row_target[r] >> 48] [rows, N] (a negative target: not stored), with plain stores over NVLink
+ * while the tensor pipe works on the next tile; with row_target = the origins the push recorded, the second expert
+ * GEMM delivers every output row to slot token * top_k + choice of the rank that owns the token, and after a barrier
+ * dst_ep_combine_returned sums each token's slots locally (same order, same values as dst_ep_combine_pull_add).
+ * Tiled weights only; DST_ERR_UNSUPPORTED where the tcgen05 kernel does not cover the call.
  */
+int dst_ternary_grouped_gemm_scatter(void* const* peer_out, int n_peers, const int64_t* row_target, int out_dtype, const void* x,
+                                     int act_dtype, const float* row_scale, const int64_t* offsets, const int64_t* offsets_host,
+                                     const void* const* packed, const void* const* scales, int n_terms, int scale_dtype, int64_t E,
+                                     int64_t T, int64_t N, int64_t K, int64_t group, int fmt, void* workspace, size_t workspace_bytes,
+                                     dst_stream_t stream);
+/* y[t] = bf16( sum over the token's slots, in increasing expert id, of rows_bf16[t * top_k + slot] (+ add_bf16[t]) ):
+ * the rows as the scatter GEMM delivered them. order / row_dest: the routing sort's order and the row destinations
+ * dst_ep_push_rows filled (a negative destination: the slot has no row). inv: int64 [T * top_k] scratch. */
+int dst_ep_combine_returned(const void* rows_bf16, const int64_t* order, const int64_t* row_dest, const int32_t* ids, int64_t T,
+                            int top_k, int64_t hidden, int64_t* inv, const void* add_bf16, void* y_bf16, dst_stream_t stream);
 /* Barrier among the ranks of one node over peer memory, in stream order: peer_flags[r] is rank r's flag array (int64
  * [world], zero at the start) as mapped in this process; seq = 1, 2, 3, ... counts the barriers of the job, the same on
  * every rank. The wait for the other ranks is bounded (~2 s), after which dst_check_device_status reports DST_ERR_TIMEOUT. */
@@ -309,7 +329,7 @@ int dst_ep_placement(const int64_t* offsets_all, int world, int64_t E, int64_t e
 int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const int64_t* offsets, const float* route_weights,
                      const int64_t* dst_start, int64_t n_rows, int64_t E, int64_t experts_per_rank, int top_k, int64_t K,
                      const void* const* peer_rows_f16, const void* const* peer_row_factor, const void* const* peer_row_weight,
-                     int world, int rank, int64_t* row_dest, dst_stream_t stream);
+                     const void* const* peer_row_origin, int world, int rank, int64_t* row_dest, dst_stream_t stream);
 int dst_ep_combine_pull(const void* const* peer_down_bf16, const int64_t* order, const int32_t* ids, const int64_t* offsets,
                         const int64_t* dst_start, int64_t T, int64_t experts_per_rank, int top_k, int64_t hidden, int64_t* inv,
                         void* y_bf16, int world, dst_stream_t stream);

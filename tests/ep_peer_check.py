@@ -35,8 +35,10 @@ def main():
     El, tl = E // world, T // world
     w_local = ExpertWeights(*stack_experts(experts[rank * El:(rank + 1) * El], 1, dev), hidden, inter, group, fmt).prepare()
     ok = True
-    for transport in ("peer", "nccl"):
-        ep = ExpertParallelMoE(w_local, E, topk, transport=transport)
+    # both ways back of the peer transport (the second GEMM scattering its rows to the tokens' ranks; the rows pulled from
+    # the owners), then NCCL all-to-all
+    for transport, combine in (("peer", "scatter"), ("peer", "pull"), ("nccl", "auto")):
+        ep = ExpertParallelMoE(w_local, E, topk, transport=transport, combine=combine)
         for step in range(3):  # both buffer sets of the peer transport, and a reuse
             y = ep(bf16_tensor(x[rank * tl:(rank + 1) * tl], dev), torch.from_numpy(logits[rank * tl:(rank + 1) * tl]).to(dev))
         ys = [torch.empty_like(y) for _ in range(world)]
@@ -46,7 +48,7 @@ def main():
             y1 = MoELayer(w_all, topk)(bf16_tensor(x, dev), torch.from_numpy(logits).to(dev))
             same = torch.equal(torch.cat(ys), y1)
             ok = ok and same
-            print(f"transport {transport}: world {world}, identical to the single-device layer: {same}", flush=True)
+            print(f"transport {transport} ({combine}): world {world}, identical to the single-device layer: {same}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

@@ -548,7 +548,8 @@ def test_expert_parallel_peer_transport_single_rank():
 def test_ep_peer_kernels_with_emulated_ranks(W):
     """The peer-memory dispatch / combine entries for 4 and 8 ranks on ONE GPU: every "rank" has its own buffers on
     this device and the ranks' steps run one after the other (none of the kernels waits on another rank), with the
-    same placement arithmetic, pointer tables and grouped GEMMs as ExpertParallelMoE. Result = the single-device layer."""
+    same placement arithmetic, pointer tables and grouped GEMMs as ExpertParallelMoE. Both ways back (the owners' rows
+    pulled; the second GEMM's epilogue scattering them to the tokens' ranks) = the single-device layer."""
     import ctypes
 
     from deepseekternarized_b200 import _lib
@@ -566,8 +567,10 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
     ops, lib = B200Ops(), kb.ext()
     cap = tl * topk * W
     bufs = [dict(rows=torch.empty(cap, hidden, dtype=torch.float16, device=DEV), fac=torch.empty(cap, device=DEV),
-                 wts=torch.empty(cap, device=DEV), down=torch.empty(cap, hidden, dtype=torch.bfloat16, device=DEV)) for _ in range(W)]
-    ptrs = {k: (ctypes.c_void_p * W)(*[b[k].data_ptr() for b in bufs]) for k in ("rows", "fac", "wts", "down")}
+                 wts=torch.empty(cap, device=DEV), down=torch.empty(cap, hidden, dtype=torch.bfloat16, device=DEV),
+                 origin=torch.full((cap,), -1, dtype=torch.int64, device=DEV),
+                 back=torch.full((tl * topk, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)) for _ in range(W)]
+    ptrs = {k: (ctypes.c_void_p * W)(*[b[k].data_ptr() for b in bufs]) for k in ("rows", "fac", "wts", "down", "origin", "back")}
     stream = kb._stream(x)
     routed = []
     for r in range(W):  # route and sort per rank; all-gather of the counts = stack
@@ -576,12 +579,13 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
         routed.append((w.reshape(-1).contiguous(), ids, order, offsets))
     counts_all = torch.stack([o[3].diff() for o in routed])
     place = [ep_placement(counts_all, r, El) for r in range(W)]
+    dests = [torch.empty(tl * topk, dtype=torch.int64, device=DEV) for _ in range(W)]
     for r in range(W):  # push
         w, ids, order, offsets = routed[r]
         xr = x[r * tl:(r + 1) * tl].contiguous()
         _lib.check(lib.dst_ep_push_rows(xr.data_ptr(), order.data_ptr(), offsets.data_ptr(), w.data_ptr(), place[r][0].data_ptr(),
-                                        order.numel(), E, El, topk, hidden, ptrs["rows"], ptrs["fac"], ptrs["wts"], W, r,
-                                        torch.empty(order.numel(), dtype=torch.int64, device=DEV).data_ptr(), stream))
+                                        order.numel(), E, El, topk, hidden, ptrs["rows"], ptrs["fac"], ptrs["wts"], ptrs["origin"], W, r,
+                                        dests[r].data_ptr(), stream))
     for r in range(W):  # experts of rank r on the rows it received
         offsets2 = place[r][1]
         R = int(offsets2[-1])
@@ -589,6 +593,9 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
         if R:
             MoELayer(wl, topk).experts_forward(kb.NormRows(bufs[r]["rows"][:R], bufs[r]["fac"][:R]), offsets2, bufs[r]["wts"][:R], None,
                                                out=bufs[r]["down"][:R])
+            # the fused way back: the second GEMM stores every output row into the slot of the rank that owns the token
+            MoELayer(wl, topk).experts_forward(kb.NormRows(bufs[r]["rows"], bufs[r]["fac"]), offsets2, bufs[r]["wts"], None,
+                                               n_rows_dev=offsets2[-1:], scatter=(ptrs["back"], W, bufs[r]["origin"]))
     ys = []
     for r in range(W):  # pull + combine
         w, ids, order, offsets = routed[r]
@@ -598,6 +605,12 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
         _lib.check(lib.dst_ep_combine_pull(ptrs["down"], order.data_ptr(), ids32.data_ptr(), offsets.data_ptr(), place[r][0].data_ptr(),
                                            tl, El, topk, hidden, inv.data_ptr(), y.data_ptr(), W, stream))
         ys.append(y)
+        y2 = torch.empty(tl, hidden, dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.dst_ep_combine_returned(bufs[r]["back"].data_ptr(), order.data_ptr(), dests[r].data_ptr(), ids32.data_ptr(), tl, topk,
+                                               hidden, inv.data_ptr(), None, y2.data_ptr(), stream))
+        assert torch.equal(y2, y)
+    torch.cuda.synchronize()
+    assert lib.dst_check_device_status(None) == 0
     w_all = ExpertWeights(*stack_experts(experts, 1, DEV), hidden, inter, group, fmt).prepare()
     want = torch.cat([MoELayer(w_all, topk)(x[r * tl:(r + 1) * tl].contiguous(), logits[r * tl:(r + 1) * tl].contiguous()) for r in range(W)])
     assert torch.equal(torch.cat(ys), want)
