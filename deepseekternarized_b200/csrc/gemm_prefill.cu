@@ -64,6 +64,7 @@ constexpr int PF_MAX_SLABS = 3;
 constexpr int PF_LUT_BYTES = 256 * 16 * 4;   // TQ1: 256 byte values x 16 bank replicas x 4 B
 constexpr int PF_SLAB = 8192;                // one (row tile, superblock) slab of packed weights
 constexpr int PF_MAX_E = 1023;               // experts per launch: two int arrays of E + 1 entries live in shared memory
+constexpr int PF_EPI_TILE = 2048;             // bytes of an epilogue warp's transposition tile (32 token rows x 32 columns x 2 bytes)
 constexpr int PF_SMEM_MAX = 232448;          // 227 KB of shared memory per CTA
 constexpr int PF_SMEM_STATIC = 6144;         // allowance for the statically declared barriers, flags and the scatter form's row pointers
 constexpr long long PF_WAIT_CYCLES = 4000000000LL;  // ~2 s
@@ -113,6 +114,7 @@ struct PrefillParams {
   int rows_hint;    // most rows an expert is expected to have (host knowledge or twice the mean), sizes tn_max
   int nb;           // depth of the stage ring (B stage in shared memory + A slot in TMEM), 2..6
   int nslab;        // slots of the packed-slab ring, 2 or 3
+  int wide_drain;   // 16-bit outputs, N % 8 == 0, 16-byte aligned rows: the accumulator is drained with 128-bit stores (drain_tile_wide)
   int small;        // token tiles of at most 128 rows: four warps drain the accumulator and the other four of that role join
                     // the dequantisation as a fifth group (the MMAs of such tiles are short, the dequantisation is the limit)
   // Scatter of the output rows (null: rows go to `out` in place). Row r is stored at row (row_target[r] & (2^48 - 1)) of
@@ -243,6 +245,20 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),         \
                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])    \
                : "r"(taddr))
+
+// 16 TMEM lanes x 32 columns in the layout of an MMA accumulator fragment: registers 4 b + {0, 1} = lane t / 4 of the 16,
+// columns 8 b + 2 (t % 4) + {0, 1}; registers 4 b + {2, 3} = lane t / 4 + 8, the same columns (t = lane of the warp).
+#define TMEM_LD_16x256_X4(v, taddr)                                                                                        \
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"    \
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),           \
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])      \
+               : "r"(taddr))
+// Four 8 x 8 matrices of 16-bit elements from registers (thread t: row t / 4, columns 2 (t % 4) + {0, 1} of each) to
+// shared memory, TRANSPOSED: lanes 8 k .. 8 k + 7 give the addresses of the eight 16-byte rows of matrix k.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.x4.trans.m8n8.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
 
 // ------------------------------------------------------------------------------------------ tile walk
 // Token rows a tile of `rows` rows occupies in the MMA N dimension: a multiple of 16 up to 256 (one MMA per K
@@ -436,6 +452,84 @@ __device__ __forceinline__ bool drain_tile(const PrefillParams& p, uint32_t tmem
   return true;
 }
 
+// The same drain for 16-bit outputs with N % 8 == 0: 128-bit stores. A thread of the plain drain owns one output
+// column and stores 2 bytes per token row, ~5 instructions each, and the drain of the single accumulator is on the
+// critical path (a fifth of the second expert GEMM's time). Here the accumulator is read as MMA-style fragments
+// (16 lanes x 256 bits), scaled, packed to pairs and turned by stmatrix.trans into a [32 token rows][32 columns] tile
+// in this warp's 2 KB of shared memory (16-byte pieces XOR-swizzled by the row pair: no bank conflicts either way);
+// every lane then moves four 16-byte pieces = eight adjacent columns of a token row each to global memory. The
+// scatter form (row_ptr) needs one destination lookup per piece instead of one per element.
+__device__ __forceinline__ bool drain_tile_wide(const PrefillParams& p, uint32_t tmem, int col_first, int col_step, int warp_q, int lane,
+                                                uint32_t tfull_bar, uint32_t tempty_bar, volatile int* abort_flag, int d_nt, int d_row0,
+                                                int d_rows, uint32_t d_tile, const uint64_t* __restrict__ row_ptr, uint8_t* tile_smem) {
+  if (!mbar_wait(tfull_bar, d_tile & 1u, abort_flag)) return false;
+  __syncwarp();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const int n_eff = tile_neff(d_rows);
+  const int n0 = d_nt * 128 + warp_q * 32;  // first output column of this warp's lane quarter
+  const int t0 = lane & 3, t1 = lane >> 2;
+  const uint32_t tile_a = smem_u32(tile_smem);
+  // stmatrix: lane L addresses row r = L % 8 of matrix k = L / 8 of a group of four: (token block 2 x + k / 2, columns 16 h + 8 (k % 2) ..)
+  const int st_r = lane & 7, st_g = (lane >> 3) & 1, st_b = lane >> 4;
+  // read-back: piece q = 32 i + lane -> token row 8 i + lane / 4, columns 8 (lane % 4) ..
+  const int rb_p = lane & 3, rb_t = lane >> 2;
+  const size_t ostep = (size_t)p.N * 2;
+  for (int c0 = col_first; c0 < n_eff; c0 += col_step) {
+    const float rs_lane = (p.row_scale && c0 + lane < d_rows) ? p.row_scale[d_row0 + c0 + lane] : 1.f;
+    float rs[8];  // of the token rows 8 b + 2 t0 + {0, 1} of the chunk
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      rs[2 * b] = __shfl_sync(0xffffffffu, rs_lane, 8 * b + 2 * t0);
+      rs[2 * b + 1] = __shfl_sync(0xffffffffu, rs_lane, 8 * b + 2 * t0 + 1);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // lanes 16 h .. 16 h + 15 of the quarter = output columns n0 + 16 h ..
+      uint32_t v[16];
+      TMEM_LD_16x256_X4(v, tmem + ((uint32_t)(warp_q * 32 + 16 * h) << 16) + (uint32_t)c0);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      uint32_t m[8];  // m[2 b + g]: token block b, columns 16 h + 8 g ..: (row = column t1, pair = token rows 2 t0, 2 t0 + 1)
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const float lo = __uint_as_float(v[4 * b + 2 * g]) * rs[2 * b], hi = __uint_as_float(v[4 * b + 2 * g + 1]) * rs[2 * b + 1];
+          if (p.out_dtype == DST_OUT_BF16) {
+            const __nv_bfloat162 q = __floats2bfloat162_rn(lo, hi);
+            m[2 * b + g] = *reinterpret_cast<const uint32_t*>(&q);
+          } else {
+            const __half2 q = __floats2half2_rn(lo, hi);
+            m[2 * b + g] = *reinterpret_cast<const uint32_t*>(&q);
+          }
+        }
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {  // token blocks 2 x, 2 x + 1
+        const int tok = 8 * (2 * x + st_b) + st_r, piece = 2 * h + st_g;
+        stmatrix_x4_trans(tile_a + (uint32_t)(tok * 64 + ((piece ^ ((tok >> 1) & 3)) << 4)), m[4 * x], m[4 * x + 1], m[4 * x + 2], m[4 * x + 3]);
+      }
+    }
+    __syncwarp();
+    const int n = n0 + 8 * rb_p;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int tok = 8 * i + rb_t;
+      const uint4 q = *reinterpret_cast<const uint4*>(tile_smem + tok * 64 + ((rb_p ^ ((tok >> 1) & 3)) << 4));
+      if (c0 + tok < d_rows && n < p.N) {
+        if (row_ptr != nullptr) {
+          const uint64_t rowp = row_ptr[c0 + tok];
+          if (rowp != 0) *reinterpret_cast<uint4*>(rowp + (size_t)n * 2) = q;
+        } else {
+          *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (size_t)(d_row0 + c0 + tok) * ostep + (size_t)n * 2) = q;
+        }
+      }
+    }
+    __syncwarp();  // the tile is read before the next chunk overwrites it
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncwarp();
+  if (lane == 0 && !g_drop_drain_arrivals) mbar_arrive(tempty_bar);
+  return true;
+}
+
 // ------------------------------------------------------------------------------------------ the kernel
 // Shared memory map (dynamic, 1024-byte aligned), per CTA:
 //   [0, nb * tn_max * 128)          B stage ring: tn_max token rows x 64 fp16 per stage; stage s pairs with A slot s in TMEM
@@ -454,6 +548,7 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
   uint8_t* lut = slabs + (size_t)p.nslab * p.n_terms * PF_SLAB;  // TQ1 only
   int* offs = reinterpret_cast<int*>(lut + (FMT == 1 ? PF_LUT_BYTES : 0));
   int* tpre = offs + (PF_MAX_E + 1);
+  uint8_t* epi_tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tpre + (PF_MAX_E + 1)) + 127) & ~static_cast<uintptr_t>(127));  // PF_EPI_WARPS x 2 KB
   __shared__ uint64_t bar_full[PF_MAX_STAGES], bar_empty[PF_MAX_STAGES], bar_tfull[1], bar_tempty[1], bar_pfull[PF_MAX_SLABS],
       bar_pempty[PF_MAX_SLABS];
   __shared__ uint32_t tmem_base_s;
@@ -644,9 +739,15 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         row_ptr = rp;
       }
       // the two warps of a lane quarter take alternate 32-column chunks
-      if (!drain_tile(p, tmem, ((warp - PF_CTRL_WARPS) >> 2) * 32, p.small ? 32 : 32 * (PF_EPI_WARPS / 4), r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]),
-                      abort_flag, nt, row0, rows, tile, row_ptr))
+      const int col_first = ((warp - PF_CTRL_WARPS) >> 2) * 32, col_step = p.small ? 32 : 32 * (PF_EPI_WARPS / 4);
+      if (p.wide_drain) {
+        if (!drain_tile_wide(p, tmem, col_first, col_step, warp & 3, lane, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]), abort_flag, nt,
+                             row0, rows, tile, row_ptr, epi_tiles + (warp - PF_CTRL_WARPS) * PF_EPI_TILE))
+          break;
+      } else if (!drain_tile(p, tmem, col_first, col_step, r, smem_u32(&bar_tfull[0]), smem_u32(&bar_tempty[0]), abort_flag, nt, row0,
+                             rows, tile, row_ptr)) {
         break;
+      }
     }
   } else {
     // ------------------------------------------------------------------ dequant producers (weights)
@@ -891,7 +992,7 @@ int launch_fmt(const TmaMaps& maps, PrefillParams p, cudaStream_t st) {
   // bytes, each A slot 32 TMEM columns next to tn_max accumulator columns), which is what hides the TMA latency
   // when the MMAs of a stage are short. Then a third packed-slab slot if there is room for it.
   const long long budget = PF_SMEM_MAX - PF_SMEM_STATIC;
-  const long long fixed = 1024 + (FMT == 1 ? PF_LUT_BYTES : 0) + 2 * (PF_MAX_E + 1) * 4;
+  const long long fixed = 1024 + (FMT == 1 ? PF_LUT_BYTES : 0) + 2 * (PF_MAX_E + 1) * 4 + (p.wide_drain ? 128 + PF_EPI_WARPS * PF_EPI_TILE : 0);
   const long long slab2 = 2LL * p.n_terms * PF_SLAB;
   int tn_cap = (p.rows_hint + 31) / 32 * 32;
   tn_cap = tn_cap < 64 ? 64 : (tn_cap > PF_TN_MAX ? PF_TN_MAX : tn_cap);
@@ -999,6 +1100,11 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.accumulate = a.accumulate;
   p.row_target = a.row_target;
   for (int i = 0; i < DST_MAX_PEERS; ++i) p.peer_out[i] = a.peer_out[i];
+  // 128-bit stores from the epilogue: two-byte outputs, whole 8-column pieces, 16-byte aligned rows
+  p.wide_drain = (a.out_dtype != DST_OUT_F32 && !a.accumulate && a.N % 8 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) ? 1 : 0;
+  if (a.row_target != nullptr)
+    for (int i = 0; i < DST_MAX_PEERS; ++i)
+      if ((reinterpret_cast<uintptr_t>(a.peer_out[i]) & 15) != 0) p.wide_drain = 0;
   if (a.row_target != nullptr && (a.out_dtype == DST_OUT_F32 || a.accumulate)) return DST_ERR_UNSUPPORTED;
   p.E = (int)a.E;
   p.T = (int)a.T;
