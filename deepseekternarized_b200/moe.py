@@ -414,8 +414,7 @@ class ExpertParallelMoE:
         ``combine`` (peer transport): "scatter" = the second expert GEMM's epilogue stores every output row into the
         slot of the rank that owns the token, over NVLink, while the tensor pipe works on the next tile, and the
         combine is local; "pull" = the GEMM writes locally and each rank reads its tokens' rows from the owners;
-        "auto" = "scatter" from four ranks on (the scatter epilogue costs the second GEMM about a quarter more time,
-        the pull costs a pass over the links that nothing overlaps: measured at 2 ranks 3.52 against 3.40 ms per step).
+        "auto" = "scatter" (measured per step: 3.22 against 3.37 ms at 2 ranks).
         Router options and ``shared`` as in ``MoELayer`` (``gate_bias`` over the GLOBAL experts; the shared expert is
         replicated: every rank applies it to its own tokens)."""
         import torch.distributed as dist
@@ -438,7 +437,7 @@ class ExpertParallelMoE:
         self.transport = transport
         if combine not in ("auto", "scatter", "pull"):
             raise ValueError("combine must be 'auto', 'scatter' or 'pull'")
-        self.combine = ("scatter" if self.world >= 4 else "pull") if combine == "auto" else combine
+        self.combine = "scatter" if combine == "auto" else combine
         self._peer = None  # [_PeerBuffers, _PeerBuffers] once set up
         self._step = 0
 
