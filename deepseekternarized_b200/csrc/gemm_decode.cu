@@ -2,9 +2,9 @@
 //
 //     out[m, n] = row_scale[m] * sum_i sum_g scale_i[e, n, g] * sum_{k in g} x[m, k] * trit_i[e, n, k]
 //
-// Every packed byte crosses HBM once: one thread per CTA streams the 64-row halves of the tiled layout's 8 KB slabs
-// (layout_kernels.cu), two at a time, into a shared-memory ring with cp.async.bulk + mbarrier; four consumer warps
-// read them from there with 128-bit loads. The multiply-adds are exact integer arithmetic on mma.sync.m16n8k32 (u8 x s8 -> s32)
+// Every packed byte crosses HBM once: one thread per CTA streams the item's rows of the tiled layout's 8 KB slabs
+// (layout_kernels.cu), two superblocks at a time, into a shared-memory ring with cp.async.bulk + mbarrier; the consumer
+// warps read them from there with 128-bit loads. The multiply-adds are exact integer arithmetic on mma.sync.m16n8k32 (u8 x s8 -> s32)
 // fed straight from registers:
 //
 //   A fragment  a weight row's packed word ANDed with a byte-wise 2-bit field mask IS the operand: four u8 digits
@@ -26,13 +26,15 @@
 //               boilerplate/kernels/csrc/boilerplate_cpu.cpp:116-124) runs once per four groups, each lane of a
 //               quad doing one of them; the quad's partial results are added with two shuffles at the end of K.
 //
-// One consumer warp owns 16 weight rows; a work item is (expert, 64-row half tile) over the whole of K, dealt to
-// CTAs in contiguous, equally sized ranges so an expert's token rows are staged once per CTA and item run.
+// Up to four token rows per expert: four consumer warps of 16 weight rows each and several CTAs per SM; a work item
+// is (expert, 64-row half tile) over the whole of K. Five or more: the staged token rows take most of an SM's shared
+// memory, so one CTA per SM of eight consumer warps that own two 16-row tiles each (a 256-row item; see the kernel).
+// Items are dealt to CTAs in contiguous, equally sized ranges so an expert's token rows are staged once per CTA and run.
 // Every mbarrier wait is bounded by elapsed clock cycles; on expiry the CTA raises its abort flag, all warps leave
 // and the kernel records DST_ERR_TIMEOUT in the status word dst_check_device_status reads.
 //
 // Coverage: TQ2 tiled weights, group 128, K % 512 == 0 (a ring slot is two 256-trit superblocks), fp16 scales, bf16 / fp16 / int8 activations, any row
-// count per expert (rows are processed up to 16 at a time; beyond that the weights are streamed again).
+// count per expert (rows are processed up to 16 at a time; beyond that the weights are streamed again, from L2).
 #include "dst_common.cuh"
 
 namespace dst {

@@ -287,10 +287,10 @@ def test_grouped_decode_sizes_with_empty_and_ragged_experts(kb, algo, fmt):
 
 
 @pytest.mark.parametrize("N,K,terms_k", [(1024, 1024, 1), (384, 512, 2)])
-def test_grouped_decode_sixteen_warp_ctas(kb, N, K, terms_k):
-    """Five or more rows per expert with at least one 256-row item per SM: the decode GEMV runs as one CTA of 16
-    consumer warps per SM (8 or 16 staged rows per pass). Ragged row counts around the pass sizes, empty experts, an
-    odd number of 128-row tiles (the last item has one tile only)."""
+def test_grouped_decode_many_row_ctas(kb, N, K, terms_k):
+    """Five or more rows per expert with at least one 256-row item per SM: the decode GEMV runs as one CTA per SM whose
+    eight consumer warps own two MMA tiles each (8 or 16 staged rows per pass). Ragged row counts around the pass
+    sizes, empty experts, an odd number of 128-row tiles (the last item has one tile only)."""
     E = 160
     rng = np.random.default_rng(N + K)
     terms = make_terms(rng, N, K, 128, "tq2", terms_k, lead=(E,))
