@@ -40,9 +40,10 @@
 namespace dst {
 namespace {
 
-// CW consumer warps of 16 weight rows each (+ the producer warp) make a CTA; a work item is CW * 16 rows of one expert
-// over the whole of K. Few token rows: CW = 4 and several CTAs per SM. Eight or more: the staged token rows take most of
-// an SM's shared memory, so ONE CTA of 16 consumer warps shares them.
+// CW consumer warps of RW 16-row MMA tiles each (+ the producer warp) make a CTA; a work item is CW * RW * 16 rows of one
+// expert over the whole of K. Few token rows: CW = 4, RW = 1 and several CTAs per SM. Five or more: the staged token rows
+// take most of an SM's shared memory, so ONE CTA of 8 consumer warps with two tiles each shares them (cw below counts
+// 16-row tiles: CW * RW).
 constexpr int DC_QWARPS = 4;                      // warps per block of decode_quant_kernel
 __host__ __device__ constexpr int dc_part(int cw) { return cw * 16 * 64; }           // bytes of one item's share of a superblock: 64 B per row
 __host__ __device__ constexpr int dc_slot_data(int cw) { return 2 * dc_part(cw); }   // a ring slot holds the item's share of TWO superblocks (four scale groups)
