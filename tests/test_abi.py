@@ -106,5 +106,17 @@ def test_other_entries_reject_bad_arguments(lib):
     assert lib.dst_tile_weights(None, 1, 8, 0, 2, None, None) == _lib.ERR_BAD_ARG
     assert lib.dst_tile_weights(0x1000, 1, 8, 64, 2, 0x1004, None) == _lib.ERR_ALIGNMENT
     assert lib.dst_untile_weights(None, 0, 8, 64, 1, None, None) == _lib.OK
+    # the scatter form of the grouped GEMM: a destination table and at least one two-byte-typed buffer
+    peers = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    args = (0x1000, 0, None, None, None, 0x1000, 0x1000, 1, 0, 4, 64, 128, 128, 128, 1, None, 0, None)
+    assert lib.dst_ternary_grouped_gemm_scatter(None, 2, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, None, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 0, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, 0x1000, 0, *args) == _lib.ERR_UNSUPPORTED  # fp32 rows
+    assert lib.dst_ep_combine_returned(None, None, None, None, 4, 9, 8, None, None, None, None) == _lib.ERR_BAD_ARG
+    assert lib.dst_ep_combine_returned(None, None, None, None, 0, 6, 8, None, None, None, None) == _lib.OK
+    assert lib.dst_ep_combine_returned(None, None, None, None, 4, 6, 12, None, None, None, None) == _lib.ERR_UNSUPPORTED
+    assert lib.dst_gather_dequant_rows_strided(None, None, 1, 0, None, 4, 10, 256, 128, 1, 10, 2, None, None, None) == _lib.ERR_BAD_ARG  # rows overlap
+    assert lib.dst_decode_row_limit(1, 384, 4096) == 16 and lib.dst_decode_row_limit(2, 1, 4096) == 16
     assert lib.dst_gemm_workspace_bytes(_lib.ALGO_GENERIC, 0, 100, 4096) == 0
     assert lib.dst_gemm_workspace_bytes(_lib.ALGO_PREFILL, 0, 100, 4096) >= 100 * 4096 * 2 + 400
