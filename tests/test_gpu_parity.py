@@ -340,6 +340,27 @@ def test_prefill_many_tiles_per_cta(kb, fmt):
         check_gemm(y[a:b], x[a:b], [(terms[0][0][e], terms[0][1][e])], K, 128, fmt)
 
 
+@pytest.mark.parametrize("N", [200, 196, 384])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_prefill_sixteen_bit_outputs_equal_rounded_fp32_outputs(kb, N, out_dtype):
+    """16-bit outputs of the tcgen05 kernel leave through transposed tiles and 128-bit stores when N % 8 == 0 (else one
+    store per element): either way they are the fp32 outputs rounded once. Ragged experts around the tile sizes, one
+    empty, columns that end inside a 128-column tile."""
+    E, K = 9, 512
+    rng = np.random.default_rng(N)
+    terms = make_terms(rng, N, K, 128, "tq1", 1, lead=(E,))
+    counts = np.array([40, 0, 257, 31, 320, 1, 96, 300, 17])
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = bf16_tensor(O.synth_acts(rng, (int(offsets[-1]), K)), DEV)
+    tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), "tq1", K)]
+    sc = [torch.from_numpy(terms[0][1]).to(DEV)]
+    y32 = kb.grouped_ternary_gemm_bf16(x, offsets, tiled, sc, K, 128, "tq1", algo="prefill", out_dtype=torch.float32)
+    y16 = kb.grouped_ternary_gemm_bf16(x, offsets, tiled, sc, K, 128, "tq1", algo="prefill", out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    assert kb.ext().dst_check_device_status(None) == 0
+    assert torch.equal(y16, y32.to(out_dtype))
+
+
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])
 def test_prefill_more_experts_than_one_launch_holds(kb, fmt):
     """The tcgen05 kernel keeps per-expert tables for at most 1023 experts in shared memory; a call with more is
