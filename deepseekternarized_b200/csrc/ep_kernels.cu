@@ -10,11 +10,15 @@
 //                      format (power of two per row, DST_ACT_F16_NORM) and STORES it, with its row factor and its
 //                      routing weight, straight into the destination GPU's buffers: gather + conversion +
 //                      dispatch in one pass, no staging copy, no re-sort on the receiver.
-//   ep_combine_kernel  per token, LOADS its top_k expert outputs from the GPUs that computed them, in increasing
-//                      expert id, sums in fp32 and writes bf16: inverse dispatch + combine in one pass.
+//                      Beside every row it also records where the row came from (rank, slot): the destination table
+//                      of the scattering second expert GEMM (gemm_prefill.cu), which sends every output row back
+//                      from its epilogue; the combine is then local (moe_kernels.cu, returned_slots_kernel).
+//   ep_combine_kernel  the other way back: per token, LOADS its top_k expert outputs from the GPUs that computed
+//                      them, in increasing expert id, sums in fp32 and writes bf16.
+//   ep_barrier_kernel  the ranks' stream-ordered barrier over symmetric flag words; its wait is bounded.
 //
-// The buffers are mapped into every rank (torch symmetric memory); the steps are separated by stream-ordered
-// collectives on the host side, so no kernel here waits on another GPU. No TMA, no multicast.
+// The buffers are mapped into every rank (torch symmetric memory). Only the barrier kernel waits on another GPU.
+// Plain loads and stores: no TMA copies here.
 #include "dst_common.cuh"
 
 namespace dst {
