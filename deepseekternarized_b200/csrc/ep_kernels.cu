@@ -19,6 +19,8 @@
 //
 // The buffers are mapped into every rank (torch symmetric memory). Only the barrier kernel waits on another GPU.
 // Plain loads and stores: no TMA copies here.
+#include <algorithm>
+
 #include "dst_common.cuh"
 
 namespace dst {
@@ -76,14 +78,24 @@ __global__ void ep_row_dest_kernel(const int64_t* __restrict__ offsets, const in
 template <int J>  // 16-byte chunks per thread: rows of K <= 2048 J elements
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int64_t* __restrict__ order, const int64_t* __restrict__ dest,
-               const float* __restrict__ route_weights, const int64_t* __restrict__ first_row, int top_k, int64_t K, PeerPtrs rows,
-               PeerPtrs fac, PeerPtrs wts, PeerPtrs back, int rank) {
+               const float* __restrict__ route_weights, const int64_t* __restrict__ own0, const int64_t* __restrict__ own1, int top_k,
+               int64_t K, PeerPtrs rows, PeerPtrs fac, PeerPtrs wts, PeerPtrs back, int rank) {
   __shared__ float red[32];
-  // Blocks walk the sorted rows starting at *first_row (the rows of the rank after this one) and wrap around: the
-  // rows are sorted by destination rank, and with every rank starting at rank 0's rows all of them would store into
-  // the same GPU at the same time (measured at 8 ranks: 300 GB/s per sender instead of the link's 770).
-  int64_t p = (int64_t)blockIdx.x + (first_row ? *first_row : 0);
-  if (p >= (int64_t)gridDim.x) p -= (int64_t)gridDim.x;
+  // The rows are sorted by destination rank. Blocks take the rows of the OTHER ranks in order starting with the rank
+  // after this one (with every rank starting at rank 0's rows all of them would store into the same GPU at the same
+  // time: measured at 8 ranks 300 GB/s per sender instead of the link's 770), and this rank's own rows [*own0, *own1)
+  // spread evenly among them, so the local copies run under the transfers instead of after them.
+  const int64_t n = (int64_t)gridDim.x, b = (int64_t)blockIdx.x;
+  const int64_t o0 = own0 ? *own0 : 0, o1 = own1 ? *own1 : 0;
+  const int64_t L = o1 > o0 ? o1 - o0 : 0;
+  const int64_t before = b * L / n, upto = (b + 1) * L / n;  // own rows among the blocks before this one / up to it
+  int64_t p;
+  if (upto > before) {
+    p = o0 + before;
+  } else {
+    p = o1 + (b - upto);
+    if (p >= n) p -= n;
+  }
   const int64_t dst = dest[p];
   if (dst < 0) return;  // a row of an id the routing sort dropped
   int64_t slot = order[p];
@@ -332,15 +344,15 @@ extern "C" int dst_ep_push_rows(const void* x_bf16, const int64_t* order, const 
   auto xp = static_cast<const __nv_bfloat16*>(x_bf16);
   ep_row_dest_kernel<<<(unsigned)cdiv64(n_rows, 256), 256, 0, st>>>(offsets, dst_start, n_rows, (int)E, (int)experts_per_rank, row_dest);
   DST_CUDA_TRY(cudaGetLastError());
-  // start at the rows of the next rank's first expert (offsets[that expert] <= n_rows; beyond the experts: row 0)
-  const int64_t next_first = (int64_t)((rank + 1) % world) * experts_per_rank;
-  const int64_t* first_row = next_first < E ? offsets + next_first : nullptr;
+  // this rank's own rows in the sorted order: [offsets[rank * El], offsets[min((rank + 1) * El, E)])
+  const int64_t* own0 = offsets + std::min<int64_t>((int64_t)rank * experts_per_rank, E);
+  const int64_t* own1 = offsets + std::min<int64_t>((int64_t)(rank + 1) * experts_per_rank, E);
   if (K <= 2048)
-    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
+    ep_push_kernel<1><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, own0, own1, top_k, K, rows, fac, wts, back, rank);
   else if (K <= 4096)
-    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
+    ep_push_kernel<2><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, own0, own1, top_k, K, rows, fac, wts, back, rank);
   else
-    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, first_row, top_k, K, rows, fac, wts, back, rank);
+    ep_push_kernel<4><<<(unsigned)n_rows, 256, 0, st>>>(xp, order, row_dest, route_weights, own0, own1, top_k, K, rows, fac, wts, back, rank);
   DST_CUDA_TRY(cudaGetLastError());
   return DST_OK;
 }

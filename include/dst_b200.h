@@ -293,7 +293,7 @@ int dst_gather_dequant_rows_strided(const void* const* packed, const void* const
  * (DST_ACT_F16_NORM) -> the owner's buffers (rows, factor, routing weight route_weights[order[p]]). row_dest is an
  * int64 [n_rows] scratch the call fills (each row's owner and row there, found once by a small kernel of its own);
  * `rank` is this rank's index: it starts with the rows of the rank after it, so the ranks do not all store into the
- * same GPU at the same time.
+ * same GPU at the same time, and spreads its own rows among the others', so the local copies run under the transfers.
  * peer_row_origin (may be NULL): per rank an int64 [cap] array; the push also records there, beside every row it
  * delivers, (rank << 48) | slot, slot = order[p] = token * top_k + choice: the row_target of the scatter GEMM below.
  * dst_ep_combine_pull: y[t] = bf16( sum over the token's slots, in increasing expert id, of the owner's output row ).
