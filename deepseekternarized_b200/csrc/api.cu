@@ -43,7 +43,7 @@ static int grouped_gemm(void* out, int out_dtype, int accumulate, const void* x,
                         const int64_t* offsets, const int64_t* offsets_host, const void* const* packed, int weight_layout,
                         const void* const* scales, int n_terms, int scale_dtype, int64_t E, int64_t T, int64_t N, int64_t K,
                         int64_t group, int fmt, int algo, void* workspace, size_t workspace_bytes, dst_stream_t stream,
-                        const int64_t* row_target, void* const* peer_out, int n_peers) {
+                        const int64_t* row_target, void* const* peer_out, int n_peers, int64_t peer_rows) {
   using namespace dst;
   if (K <= 0 || group <= 0 || (fmt != DST_FMT_TQ1 && fmt != DST_FMT_TQ2)) return DST_ERR_BAD_ARG;
   if (out_dtype < DST_OUT_F32 || out_dtype > DST_OUT_F16 || act_dtype < DST_ACT_BF16 || act_dtype > DST_ACT_F16_NORM ||
@@ -97,6 +97,8 @@ static int grouped_gemm(void* out, int out_dtype, int accumulate, const void* x,
   a.workspace_bytes = workspace ? workspace_bytes : 0;
   a.row_target = row_target;
   for (int i = 0; i < n_peers; ++i) a.peer_out[i] = peer_out[i];
+  a.n_peer_out = n_peers;
+  a.peer_rows = peer_rows;
   if (offsets_host) {
     int64_t widest = 0;
     for (int64_t e = 0; e < E; ++e) widest = std::max(widest, offsets_host[e + 1] - offsets_host[e]);
@@ -129,22 +131,22 @@ extern "C" int dst_ternary_grouped_gemm(void* out, int out_dtype, int accumulate
                                         int64_t group, int fmt, int algo, void* workspace, size_t workspace_bytes,
                                         dst_stream_t stream) {
   return grouped_gemm(out, out_dtype, accumulate, x, act_dtype, row_scale, offsets, offsets_host, packed, weight_layout, scales, n_terms,
-                      scale_dtype, E, T, N, K, group, fmt, algo, workspace, workspace_bytes, stream, nullptr, nullptr, 0);
+                      scale_dtype, E, T, N, K, group, fmt, algo, workspace, workspace_bytes, stream, nullptr, nullptr, 0, 0);
 }
 
-extern "C" int dst_ternary_grouped_gemm_scatter(void* const* peer_out, int n_peers, const int64_t* row_target, int out_dtype,
+extern "C" int dst_ternary_grouped_gemm_scatter(void* const* peer_out, int n_peers, int64_t peer_rows, const int64_t* row_target, int out_dtype,
                                                 const void* x, int act_dtype, const float* row_scale, const int64_t* offsets,
                                                 const int64_t* offsets_host, const void* const* packed, const void* const* scales,
                                                 int n_terms, int scale_dtype, int64_t E, int64_t T, int64_t N, int64_t K,
                                                 int64_t group, int fmt, void* workspace, size_t workspace_bytes,
                                                 dst_stream_t stream) {
-  if (!peer_out || !row_target || n_peers < 1 || n_peers > DST_MAX_PEERS) return DST_ERR_BAD_ARG;
+  if (!peer_out || !row_target || n_peers < 1 || n_peers > DST_MAX_PEERS || peer_rows < 0) return DST_ERR_BAD_ARG;
   if (out_dtype != DST_OUT_BF16 && out_dtype != DST_OUT_F16) return DST_ERR_UNSUPPORTED;  // two-byte rows only
   for (int i = 0; i < n_peers; ++i)
     if (!peer_out[i] || (reinterpret_cast<uintptr_t>(peer_out[i]) & 1) != 0) return DST_ERR_BAD_ARG;
   return grouped_gemm(peer_out[0], out_dtype, 0, x, act_dtype, row_scale, offsets, offsets_host, packed, DST_LAYOUT_TILED, scales, n_terms,
                       scale_dtype, E, T, N, K, group, fmt, DST_ALGO_PREFILL, workspace, workspace_bytes, stream, row_target, peer_out,
-                      n_peers);
+                      n_peers, peer_rows);
 }
 
 extern "C" int64_t dst_decode_row_limit(int fmt, int64_t E, int64_t N) { return dst::decode_row_limit(fmt, E, N); }

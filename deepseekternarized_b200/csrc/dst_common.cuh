@@ -50,6 +50,8 @@ struct GemmArgs {
   // peer_out[row_target[r] >> 48] (a negative target: the row is not stored); `out` is unused then
   const int64_t* row_target;
   void* peer_out[DST_MAX_PEERS];
+  int n_peer_out;     // targets naming a buffer >= n_peer_out or a row >= peer_rows are not stored
+  int64_t peer_rows;
 };
 
 int64_t tiled_superblocks(int fmt, int64_t K);

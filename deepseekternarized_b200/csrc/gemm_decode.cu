@@ -792,8 +792,8 @@ int launch_decode(const GemmArgs& a, cudaStream_t stream) {
   if (a.fmt == DST_FMT_TQ1) return launch_decode_tq1(a, stream);
   if (!decode_supports(a)) return DST_ERR_UNSUPPORTED;
   for (int i = 0; i < a.terms.n; ++i)
-    if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 1) != 0)
-      return DST_ERR_ALIGNMENT;
+    if ((reinterpret_cast<uintptr_t>(a.terms.packed[i]) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.terms.scale[i]) & 3) != 0)
+      return DST_ERR_ALIGNMENT;  // slabs are bulk-copied (16 bytes); scales are read two groups (32 bits) at a time
   if ((reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return DST_ERR_ALIGNMENT;  // rows are read with 128-bit loads
   DecodeParams p;
   for (int i = 0; i < DST_MAX_TERMS; ++i) {

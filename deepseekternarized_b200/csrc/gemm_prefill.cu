@@ -122,6 +122,8 @@ struct PrefillParams {
   // with plain stores over NVLink while the tensor pipe works on the next tile. A negative target drops the row.
   const int64_t* row_target;
   void* peer_out[DST_MAX_PEERS];
+  int n_peer_out;      // a target that names a buffer >= n_peer_out or a row >= peer_rows is dropped as well
+  int64_t peer_rows;
 };
 
 // Entry d of the by-value pointer table, as a chain of selects over compile-time indices (indexing a parameter array
@@ -730,7 +732,9 @@ prefill_kernel(const __grid_constant__ TmaMaps xmaps, const PrefillParams p) {
         const size_t ostep = (size_t)p.N * 2;
         for (int j = epi_tid; j < rows; j += epi_threads) {
           const int64_t tg = p.row_target[row0 + j];
-          rp[j] = tg >= 0 ? (uint64_t)reinterpret_cast<uintptr_t>(pf_peer_out(p, (int)(tg >> 48))) + (uint64_t)(tg & 0xFFFFFFFFFFFFLL) * ostep : 0ull;
+          const int64_t dr = tg & 0xFFFFFFFFFFFFLL;
+          const bool ok = tg >= 0 && (tg >> 48) < p.n_peer_out && dr < p.peer_rows;  // nothing is stored outside the buffers
+          rp[j] = ok ? (uint64_t)reinterpret_cast<uintptr_t>(pf_peer_out(p, (int)(tg >> 48))) + (uint64_t)dr * ostep : 0ull;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
@@ -1100,6 +1104,8 @@ int launch_prefill(const GemmArgs& a, cudaStream_t stream) {
   p.accumulate = a.accumulate;
   p.row_target = a.row_target;
   for (int i = 0; i < DST_MAX_PEERS; ++i) p.peer_out[i] = a.peer_out[i];
+  p.n_peer_out = a.n_peer_out;
+  p.peer_rows = a.peer_rows;
   // 128-bit stores from the epilogue: two-byte outputs, whole 8-column pieces, 16-byte aligned rows
   p.wide_drain = (a.out_dtype != DST_OUT_F32 && !a.accumulate && a.N % 8 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) ? 1 : 0;
   if (a.row_target != nullptr)

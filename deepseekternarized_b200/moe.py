@@ -149,10 +149,11 @@ class B200Ops:
         return kb.grouped_ternary_gemm_bf16(x, offsets, packed, scales, K, group, fmt, out_dtype=torch.bfloat16,
                                             algo=self.algo, out=out, validate_offsets=False)
 
-    def gemm_scatter(self, x, offsets, packed, scales, K, group, fmt, peer_out, n_peers: int, row_target: torch.Tensor) -> None:
+    def gemm_scatter(self, x, offsets, packed, scales, K, group, fmt, peer_out, n_peers: int, peer_rows: int,
+                     row_target: torch.Tensor) -> None:
         """The grouped GEMM over fp16-normalised rows whose epilogue stores bf16 output row r at row
-        ``row_target[r] & (2**48 - 1)`` of the buffer ``peer_out[row_target[r] >> 48]`` (``dst_ternary_grouped_gemm_scatter``):
-        tiled weights, the tcgen05 kernel."""
+        ``row_target[r] & (2**48 - 1)`` of the buffer ``peer_out[row_target[r] >> 48]`` of ``peer_rows`` rows
+        (``dst_ternary_grouped_gemm_scatter``): tiled weights, the tcgen05 kernel."""
         lib = self._lib()
         if not isinstance(x, kb.NormRows) or not all(isinstance(p, kb.TiledWeights) for p in packed):
             raise RuntimeError("the scatter GEMM takes fp16-normalised rows and tiled weights")
@@ -161,7 +162,7 @@ class B200Ops:
         sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in scales])
         E, N = packed[0].E, packed[0].N
         with torch.cuda.device(x.data.device):
-            _lib.check(lib.dst_ternary_grouped_gemm_scatter(peer_out, n_peers, row_target.data_ptr(), kb._OUT[torch.bfloat16], x.data.data_ptr(),
+            _lib.check(lib.dst_ternary_grouped_gemm_scatter(peer_out, n_peers, peer_rows, row_target.data_ptr(), kb._OUT[torch.bfloat16], x.data.data_ptr(),
                                                             _lib.ACT_F16_NORM, x.factor.data_ptr(), offsets.data_ptr(), None, pk, sc, n,
                                                             kb._SCALE[scales[0].dtype], E, x.data.size(0), N, K, group, kb._fmt_code(fmt),
                                                             None, 0, kb._stream(x.data)))
@@ -294,7 +295,8 @@ class MoELayer:
         ``weights``: the experts to run (default: the routed ones); ``offsets`` None = one expert over all rows;
         ``n_rows_dev``: device int64 with the number of rows that exist when ``xs`` is a buffer of larger capacity
         (the grouped GEMMs follow ``offsets``, whose last entry is that number); ``scatter`` = (peer_out, n_peers,
-        row_target): the second GEMM stores its rows where ``row_target`` says (``B200Ops.gemm_scatter``), nothing is returned."""
+        peer_rows, row_target): the second GEMM stores its rows where ``row_target`` says (``B200Ops.gemm_scatter``), nothing
+        is returned."""
         w = self.w if weights is None else weights
         gu = self.ops.gemm(xs, offsets, w.w13_packed, w.w13_scale, w.hidden, w.group, w.fmt)
         if n_rows_dev is not None:
@@ -528,7 +530,7 @@ class ExpertParallelMoE:
         self.last_dispatch_rows = offsets2[-1:]
         xs2 = kb.NormRows(buf.rows, buf.fac)
         self.local.experts_forward(xs2, offsets2, buf.wts, None, out=buf.down, n_rows_dev=offsets2[-1:],
-                                   scatter=(buf.ptrs["back"], W, buf.origin) if fused else None)
+                                   scatter=(buf.ptrs["back"], W, buf.back.size(0), buf.origin) if fused else None)
         shared = self.local.shared_forward(x)  # this rank's tokens through the (replicated) shared expert
         ev("expert GEMMs+SwiGLU")
         self._barrier(x)  # every rank's expert outputs are written

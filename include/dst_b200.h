@@ -301,13 +301,14 @@ int dst_gather_dequant_rows_strided(const void* const* packed, const void* const
  *
  * The fused form of the way back (GEMM + combine transfer in one kernel): dst_ternary_grouped_gemm_scatter is the
  * tcgen05 grouped GEMM whose epilogue stores output row r at row (row_target[r] & (2^48 - 1)) of the two-byte-typed
- * buffer peer_out[row_target[r] >> 48] [rows, N] (a negative target: not stored), with plain stores over NVLink
+ * buffer peer_out[row_target[r] >> 48] [peer_rows, N] (a negative target, a buffer index >= n_peers or a row >= peer_rows:
+ * not stored), with plain stores over NVLink
  * while the tensor pipe works on the next tile; with row_target = the origins the push recorded, the second expert
  * GEMM delivers every output row to slot token * top_k + choice of the rank that owns the token, and after a barrier
  * dst_ep_combine_returned sums each token's slots locally (same order, same values as dst_ep_combine_pull_add).
  * Tiled weights only; DST_ERR_UNSUPPORTED where the tcgen05 kernel does not cover the call.
  */
-int dst_ternary_grouped_gemm_scatter(void* const* peer_out, int n_peers, const int64_t* row_target, int out_dtype, const void* x,
+int dst_ternary_grouped_gemm_scatter(void* const* peer_out, int n_peers, int64_t peer_rows, const int64_t* row_target, int out_dtype, const void* x,
                                      int act_dtype, const float* row_scale, const int64_t* offsets, const int64_t* offsets_host,
                                      const void* const* packed, const void* const* scales, int n_terms, int scale_dtype, int64_t E,
                                      int64_t T, int64_t N, int64_t K, int64_t group, int fmt, void* workspace, size_t workspace_bytes,

@@ -109,10 +109,11 @@ def test_other_entries_reject_bad_arguments(lib):
     # the scatter form of the grouped GEMM: a destination table and at least one two-byte-typed buffer
     peers = (ctypes.c_void_p * 2)(0x1000, 0x2000)
     args = (0x1000, 0, None, None, None, 0x1000, 0x1000, 1, 0, 4, 64, 128, 128, 128, 1, None, 0, None)
-    assert lib.dst_ternary_grouped_gemm_scatter(None, 2, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
-    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, None, 1, *args) == _lib.ERR_BAD_ARG
-    assert lib.dst_ternary_grouped_gemm_scatter(peers, 0, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
-    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, 0x1000, 0, *args) == _lib.ERR_UNSUPPORTED  # fp32 rows
+    assert lib.dst_ternary_grouped_gemm_scatter(None, 2, 64, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, 64, None, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 0, 64, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, -1, 0x1000, 1, *args) == _lib.ERR_BAD_ARG
+    assert lib.dst_ternary_grouped_gemm_scatter(peers, 2, 64, 0x1000, 0, *args) == _lib.ERR_UNSUPPORTED  # fp32 rows
     assert lib.dst_ep_combine_returned(None, None, None, None, 4, 9, 8, None, None, None, None) == _lib.ERR_BAD_ARG
     assert lib.dst_ep_combine_returned(None, None, None, None, 0, 6, 8, None, None, None, None) == _lib.OK
     assert lib.dst_ep_combine_returned(None, None, None, None, 4, 6, 12, None, None, None, None) == _lib.ERR_UNSUPPORTED

@@ -565,6 +565,41 @@ def test_expert_parallel_peer_transport_single_rank():
     assert res.returncode == 0 and "EP_PEER_CHECK PASS" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
 
 
+def test_scatter_gemm_stores_nothing_outside_its_buffers(kb):
+    """The scattering form of the tcgen05 grouped GEMM: rows go where their targets say (a permutation here), and a
+    negative target, a buffer index beyond the table or a row beyond the buffer is dropped, not stored."""
+    import ctypes
+
+    from deepseekternarized_b200.moe import B200Ops
+
+    E, N, K, rows_per = 3, 256, 512, 70
+    rng = np.random.default_rng(12)
+    terms = make_terms(rng, N, K, 128, "tq1", 1, lead=(E,))
+    T = E * rows_per
+    tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), "tq1", K)]
+    sc = [torch.from_numpy(terms[0][1]).to(DEV)]
+    xh = torch.from_numpy((O.synth_acts(rng, (T, K)) * 30).astype(np.float16)).to(DEV)
+    x = kb.NormRows(xh, torch.full((T,), 0.5, device=DEV))
+    offs = torch.arange(E + 1, device=DEV, dtype=torch.int64) * rows_per
+    ops = B200Ops()
+    plain = ops.gemm(x, offs, tiled, sc, K, 128, "tq1")
+    target = torch.randperm(T, device=DEV)
+    dropped = {3: -1, 5: (1 << 48) | 5, 7: T + 5, 100: (15 << 48), 209: -7}
+    kept = torch.ones(T, dtype=torch.bool, device=DEV)
+    for r, v in dropped.items():
+        target[r] = v
+        kept[r] = False
+    out = torch.full((T + 8, N), -3.0, dtype=torch.bfloat16, device=DEV)  # eight rows of margin behind the buffer
+    peer = (ctypes.c_void_p * 1)(out.data_ptr())
+    ops.gemm_scatter(x, offs, tiled, sc, K, 128, "tq1", peer, 1, T, target)
+    torch.cuda.synchronize()
+    assert kb.ext().dst_check_device_status(None) == 0
+    assert torch.equal(out[target[kept]], plain[kept])
+    written = torch.zeros(T + 8, dtype=torch.bool, device=DEV)
+    written[target[kept]] = True
+    assert (out[~written] == -3.0).all()
+
+
 @pytest.mark.parametrize("W", [4, 8])
 def test_ep_peer_kernels_with_emulated_ranks(W):
     """The peer-memory dispatch / combine entries for 4 and 8 ranks on ONE GPU: every "rank" has its own buffers on
@@ -616,7 +651,7 @@ def test_ep_peer_kernels_with_emulated_ranks(W):
                                                out=bufs[r]["down"][:R])
             # the fused way back: the second GEMM stores every output row into the slot of the rank that owns the token
             MoELayer(wl, topk).experts_forward(kb.NormRows(bufs[r]["rows"], bufs[r]["fac"]), offsets2, bufs[r]["wts"], None,
-                                               n_rows_dev=offsets2[-1:], scatter=(ptrs["back"], W, bufs[r]["origin"]))
+                                               n_rows_dev=offsets2[-1:], scatter=(ptrs["back"], W, tl * topk, bufs[r]["origin"]))
     ys = []
     for r in range(W):  # pull + combine
         w, ids, order, offsets = routed[r]
