@@ -377,21 +377,26 @@ def ep_placement(counts_all: torch.Tensor, rank: int, experts_per_rank: int):
 class _PeerBuffers:
     """Symmetric-memory buffers of one step parity: receive rows / factors / weights and the expert outputs."""
 
-    def __init__(self, cap: int, hidden: int, device, group):
+    def __init__(self, cap: int, hidden: int, device, group, fused: bool):
         import torch.distributed._symmetric_memory as symm
 
         self.cap = cap
         self.rows = symm.empty((cap, hidden), dtype=torch.float16, device=device)
         self.fac = symm.empty((cap,), dtype=torch.float32, device=device)
         self.wts = symm.empty((cap,), dtype=torch.float32, device=device)
-        self.down = symm.empty((cap, hidden), dtype=torch.bfloat16, device=device)
         world = group.size()
-        # the way back in the fused form: where every received row came from (written by the sender beside the row), and
-        # this rank's own slots token * top_k + choice, which the owners' second GEMM fills (cap / world of them)
-        self.origin = symm.empty((cap,), dtype=torch.int64, device=device)
-        self.back = symm.empty((cap // world, hidden), dtype=torch.bfloat16, device=device)
+        if fused:
+            # the way back fused into the second GEMM: where every received row came from (written by the sender beside
+            # the row), and this rank's own slots token * top_k + choice, which the owners' GEMM fills (cap / world of them)
+            self.down = None
+            self.origin = symm.empty((cap,), dtype=torch.int64, device=device)
+            self.back = symm.empty((cap // world, hidden), dtype=torch.bfloat16, device=device)
+            names = ("rows", "fac", "wts", "origin", "back")
+        else:
+            self.down = symm.empty((cap, hidden), dtype=torch.bfloat16, device=device)  # the experts' outputs, pulled by the tokens' ranks
+            names = ("rows", "fac", "wts", "down")
         self.ptrs = {}
-        for name in ("rows", "fac", "wts", "down", "origin", "back"):
+        for name in names:
             t = getattr(self, name)
             hdl = symm.rendezvous(t, group)
             arr = (ctypes.c_void_p * world)(*[hdl.get_buffer(r, tuple(t.shape), t.dtype).data_ptr() for r in range(world)])
@@ -462,7 +467,7 @@ class ExpertParallelMoE:
                 capt = torch.tensor([cap], device=x.device, dtype=torch.int64)
                 self.dist.all_reduce(capt, op=self.dist.ReduceOp.MAX, group=self.pg)
                 pg = self.pg if self.pg is not None else self.dist.group.WORLD
-                bufs = [_PeerBuffers(int(capt.item()), x.size(1), x.device, pg) for _ in range(2)]
+                bufs = [_PeerBuffers(int(capt.item()), x.size(1), x.device, pg, self.combine == "scatter") for _ in range(2)]
             except Exception as exc:  # symmetric memory not available on this system
                 if self.transport == "peer":
                     raise RuntimeError(f"peer transport unavailable: {exc}") from exc
@@ -519,8 +524,7 @@ class ExpertParallelMoE:
             ev("offsets all-gather+placement")
             _lib.check(lib.dst_ep_push_rows(x.data_ptr(), order.data_ptr(), offsets.data_ptr(), wflat.data_ptr(), dst_start.data_ptr(),
                                             order.numel(), self.E, El, self.top_k, hidden, buf.ptrs["rows"], buf.ptrs["fac"],
-                                            buf.ptrs["wts"], buf.ptrs["origin"] if fused else None, W, self.rank, row_dest.data_ptr(),
-                                            kb._stream(x)))
+                                            buf.ptrs["wts"], buf.ptrs.get("origin"), W, self.rank, row_dest.data_ptr(), kb._stream(x)))
         getattr(self.ops, "count", lambda n: None)(5)  # kernels launched here rather than through ops (placement, row destinations, push, invert, combine)
         ev("push")
         self._barrier(x)  # every rank's rows have landed
