@@ -109,6 +109,38 @@ def test_ep_placement_matches_brute_force():
         assert np.array_equal(offsets_local.numpy(), want_offsets[r])
 
 
+def test_ep_push_block_order_visits_every_row_once():
+    """The push kernel's block -> sorted-row mapping (csrc/ep_kernels.cu, ep_push_kernel): the rows of the other ranks
+    in cyclic order starting behind this rank's own rows [o0, o1), the own rows spread evenly among them. Restated
+    here in integers: it must be a permutation of the rows, keep both sub-sequences in order, and never run more than
+    one own row behind or ahead of an even spread."""
+    import random
+
+    def row_of_block(b, n, o0, o1):
+        L = max(o1 - o0, 0)
+        before, upto = b * L // n, (b + 1) * L // n
+        if upto > before:
+            return o0 + before
+        p = o1 + (b - upto)
+        return p - n if p >= n else p
+
+    rnd = random.Random(4)
+    cases = [(1, 0, 0), (1, 0, 1), (7, 0, 7), (7, 3, 3), (12, 0, 4), (12, 8, 12), (98304, 12288, 24576)]
+    cases += [(n, *sorted((rnd.randint(0, n), rnd.randint(0, n)))) for n in (2, 5, 33, 1000, 4097) for _ in range(4)]
+    for n, o0, o1 in cases:
+        rows = [row_of_block(b, n, o0, o1) for b in range(n)]
+        assert sorted(rows) == list(range(n)), (n, o0, o1)
+        own = [r for r in rows if o0 <= r < o1]
+        assert own == list(range(o0, o1))
+        others = [r for r in rows if not (o0 <= r < o1)]
+        assert others == [(o1 + i) % n for i in range(n - (o1 - o0))]
+        L = o1 - o0
+        seen = 0
+        for b, r in enumerate(rows):
+            seen += o0 <= r < o1
+            assert abs(seen - (b + 1) * L / n) <= 1.0
+
+
 def test_host_pipeline_has_no_cpu_path():
     from deepseekternarized_b200.moe import HostPipeline
 
