@@ -141,6 +141,40 @@ def test_ep_push_block_order_visits_every_row_once():
             assert abs(seen - (b + 1) * L / n) <= 1.0
 
 
+def test_lookup_kernel_tq1_window_arithmetic():
+    """The eight-trit window of the table-lookup kernel (csrc/format_kernels.cu, gather_dequant8_kernel): trits
+    k .. k + 7 of a TQ1 row are read from bytes k / 5 .. k / 5 + 2 (the third only from k % 5 = 3 on), whose base-3
+    digits as 2-bit fields, laid side by side and shifted down by 2 (k % 5), are the eight digits u = trit + 1."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(8)
+    K = 256
+    t = O.synth_trits(rng, (3, K))
+    packed = O.pack(t, "tq1")
+    Kp = packed.shape[1]
+
+    def fields(v):  # five base-3 digits as 2-bit fields
+        f = 0
+        for i in range(5):
+            f |= (v % 3) << (2 * i)
+            v //= 3
+        return f
+
+    for row in range(3):
+        for k in range(0, K, 8):
+            b0, r = divmod(k, 5)
+            w = fields(int(packed[row, b0]))
+            if b0 + 1 < Kp:
+                w |= fields(int(packed[row, b0 + 1])) << 10
+            if r > 2 and b0 + 2 < Kp:
+                w |= fields(int(packed[row, b0 + 2])) << 20
+            f = w >> (2 * r)
+            got = [((f >> (2 * q)) & 3) - 1 for q in range(8)]
+            assert got == t[row, k:k + 8].tolist()
+
+
 def test_host_pipeline_has_no_cpu_path():
     from deepseekternarized_b200.moe import HostPipeline
 
