@@ -316,6 +316,32 @@ def test_grouped_decode_many_row_ctas(kb, N, K, terms_k):
         np.testing.assert_allclose(y, want, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("top", [1, 4, 8, 16])
+def test_decode_without_a_workspace_quantises_inside_the_kernel(kb, top, monkeypatch):
+    """A C-ABI caller may pass no workspace to the decode GEMV: the consumer warps then quantise each expert's token rows
+    themselves (stage_tokens inside decode_kernel, all CTA shapes) instead of reading what decode_quant_kernel wrote:
+    same integers, so the same outputs bit for bit."""
+    E, N, K = 160, 512, 512
+    rng = np.random.default_rng(top)
+    terms = make_terms(rng, N, K, 128, "tq2", 1, lead=(E,))
+    counts = rng.integers(max(0, top - 3), top + 1, E)
+    offsets = np.concatenate([[0], counts.cumsum()]).astype(np.int64)
+    x = bf16_tensor(O.synth_acts(rng, (int(offsets[-1]), K)), DEV)
+    tiled = [kb.tile_weights(torch.from_numpy(terms[0][0]).to(DEV), "tq2", K)]
+    sc = [torch.from_numpy(terms[0][1]).to(DEV)]
+    with_ws = kb.grouped_ternary_gemm_bf16(x, offsets, tiled, sc, K, 128, "tq2", algo="decode")
+    lib = kb.ext()
+    real = lib.dst_gemm_workspace_bytes
+    monkeypatch.setattr(lib, "dst_gemm_workspace_bytes", lambda *a: 0)
+    try:
+        without = kb.grouped_ternary_gemm_bf16(x, offsets, tiled, sc, K, 128, "tq2", algo="decode")
+    finally:
+        monkeypatch.setattr(lib, "dst_gemm_workspace_bytes", real)
+    torch.cuda.synchronize()
+    assert lib.dst_check_device_status(None) == 0
+    assert torch.equal(with_ws, without)
+
+
 @pytest.mark.parametrize("fmt", ["tq1", "tq2"])
 def test_prefill_many_tiles_per_cta(kb, fmt):
     """More tiles than SMs, so every persistent CTA of the tcgen05 kernel walks several tiles (ring phases, the
