@@ -175,6 +175,42 @@ def test_lookup_kernel_tq1_window_arithmetic():
             assert got == t[row, k:k + 8].tolist()
 
 
+def test_wide_drain_tile_addressing():
+    """Index arithmetic of the tcgen05 kernel's 128-bit drain (csrc/gemm_prefill.cu, drain_tile_wide), restated in
+    integers: the 16 transposed 8 x 8 matrices of a 32-token x 32-column chunk land on distinct 16-byte pieces of the
+    warp's 2 KB tile, every piece (token row, eight columns) is where the read-back looks for it, and neither the
+    eight row addresses of a stored matrix nor the eight addresses of a quarter-warp's 128-bit loads share a bank."""
+    def piece_addr(tok, piece):
+        return tok * 64 + ((piece ^ ((tok >> 1) & 3)) << 4)
+
+    written = {}
+    for h in range(2):           # lane half of the quarter: columns 16 h ..
+        for x in range(2):       # one stmatrix.x4: token blocks 2 x, 2 x + 1
+            for k in range(4):   # matrix k of the instruction: lanes 8 k .. 8 k + 7 give its row addresses
+                addrs = []
+                for st_r in range(8):
+                    lane = 8 * k + st_r
+                    st_g, st_b = (lane >> 3) & 1, lane >> 4
+                    tok, piece = 8 * (2 * x + st_b) + st_r, 2 * h + st_g
+                    a = piece_addr(tok, piece)
+                    assert a % 16 == 0 and 0 <= a < 2048
+                    addrs.append(a)
+                    # row st_r of the transposed matrix = token row 8 b + st_r, columns 8 piece .. 8 piece + 7
+                    assert (tok, piece) not in written
+                    written[(tok, piece)] = a
+                banks = {(a // 4) % 32 // 4 for a in addrs}  # groups of four banks = one 16-byte piece
+                assert len(banks) == 8
+    assert len(written) == 128 and len(set(written.values())) == 128
+    for i in range(4):           # read-back: piece 32 i + lane
+        for q in range(4):       # a 128-bit load is served a quarter-warp at a time
+            addrs = []
+            for lane in range(8 * q, 8 * q + 8):
+                tok, piece = 8 * i + (lane >> 2), lane & 3
+                assert written[(tok, piece)] == piece_addr(tok, piece)
+                addrs.append(piece_addr(tok, piece))
+            assert len({(a // 4) % 32 // 4 for a in addrs}) == 8
+
+
 def test_host_pipeline_has_no_cpu_path():
     from deepseekternarized_b200.moe import HostPipeline
 
